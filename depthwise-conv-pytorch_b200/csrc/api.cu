@@ -1,0 +1,308 @@
+// C ABI of libdwconv_b200.so: argument validation, kernel-family selection, launches.
+// Declarations and the reference interfaces they replace: include/dwconv_b200.h.
+#include <atomic>
+#include <cstdint>
+#include <cstdlib>
+
+#include "common.cuh"
+#include "direct_kernels.cuh"
+#include "rows_engine.cuh"
+
+using namespace dwb;
+
+namespace {
+
+std::atomic<int> g_forced_path{DWCONV_B200_PATH_AUTO};
+thread_local int t_last_path = DWCONV_B200_PATH_AUTO;
+thread_local int t_last_cuda_error = 0;
+
+inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+inline size_t elem_size(int dtype) {
+  switch (dtype) {
+    case DWCONV_B200_F32: return 4;
+    case DWCONV_B200_F16: return 2;
+    case DWCONV_B200_F64: return 8;
+    default: return 0;
+  }
+}
+
+int check_shape(const Shape *s) {
+  if (s == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  if (s->N <= 0 || s->C <= 0 || s->H <= 0 || s->W <= 0 || s->kh <= 0 || s->kw <= 0 ||
+      s->sh <= 0 || s->sw <= 0 || s->ph < 0 || s->pw < 0 || s->Ho <= 0 || s->Wo <= 0)
+    return DWCONV_B200_BAD_ARGUMENT;
+  // Index arithmetic inside one plane is 32-bit; whole-tensor offsets are 64-bit.
+  const long long lim = 1ll << 30;
+  if ((long long)s->H * s->W >= lim || (long long)s->Ho * s->Wo >= lim ||
+      (long long)s->kh * s->kw >= (1ll << 20) || (long long)s->N * s->C >= (1ll << 31) - 1 ||
+      (long long)s->Ho * s->sh + s->kh >= lim || (long long)s->Wo * s->sw + s->kw >= lim)
+    return DWCONV_B200_TOO_LARGE;
+  return DWCONV_B200_OK;
+}
+
+int launch_status() {
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) {
+    t_last_cuda_error = (int)e;
+    (void)cudaGetLastError();  // clear the non-sticky error so later calls start clean
+    return DWCONV_B200_CUDA_ERROR;
+  }
+  return DWCONV_B200_OK;
+}
+
+inline int grid_for(long long total, int block) {
+  long long g = ceil_div_ll(total, block);
+  const long long cap = 148ll * 64;  // grid-stride beyond this
+  return (int)(g < cap ? g : cap);
+}
+
+// Number of batch slices the direct backward-filter first pass uses.
+inline int direct_filter_slices(const Shape &s) {
+  int S = ceil_div(4 * 148, s.C);
+  if (S > s.N) S = s.N;
+  if (S < 1) S = 1;
+  return S;
+}
+
+template <typename T>
+int forward_t(const void *x, const void *w, void *y, const Shape &s, cudaStream_t st, int forced) {
+  if (forced != DWCONV_B200_PATH_DIRECT) {
+    int r = rows_forward<T>((const T *)x, (const T *)w, (T *)y, s, st);
+    if (r == ROWS_SERVED) {
+      t_last_path = DWCONV_B200_PATH_ROWS;
+      return launch_status();
+    }
+    if (forced == DWCONV_B200_PATH_ROWS) return DWCONV_B200_UNSUPPORTED_SHAPE;
+  }
+  const long long total = (long long)s.N * s.C * s.Ho * s.Wo;
+  direct_forward_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T *)x, (const T *)w,
+                                                                 (T *)y, s, total);
+  t_last_path = DWCONV_B200_PATH_DIRECT;
+  return launch_status();
+}
+
+template <typename T>
+int backward_input_t(const void *dy, const void *w, void *dx, const Shape &s, cudaStream_t st,
+                     int forced) {
+  if (forced != DWCONV_B200_PATH_DIRECT) {
+    int r = rows_backward_input<T>((const T *)dy, (const T *)w, (T *)dx, s, st);
+    if (r == ROWS_SERVED) {
+      t_last_path = DWCONV_B200_PATH_ROWS;
+      return launch_status();
+    }
+    if (forced == DWCONV_B200_PATH_ROWS) return DWCONV_B200_UNSUPPORTED_SHAPE;
+  }
+  const long long total = (long long)s.N * s.C * s.H * s.W;
+  direct_backward_input_kernel<T><<<grid_for(total, 256), 256, 0, st>>>(
+      (const T *)dy, (const T *)w, (T *)dx, s, total);
+  t_last_path = DWCONV_B200_PATH_DIRECT;
+  return launch_status();
+}
+
+template <typename T>
+size_t filter_workspace_t(const Shape &s) {
+  using A = typename Elem<T>::acc_t;
+  const size_t kk = (size_t)s.kh * s.kw;
+  size_t slices = (size_t)direct_filter_slices(s);
+  const size_t rs = (size_t)rows_backward_filter_slices<T>(s);
+  if (rs > slices) slices = rs;
+  size_t b = (size_t)s.C * slices * kk * sizeof(A);
+  return b < 16 ? 16 : ((b + 15) / 16) * 16;
+}
+
+template <typename T>
+int backward_filter_t(const void *x, const void *dy, void *dw, void *ws, size_t ws_bytes,
+                      const Shape &s, cudaStream_t st, int forced) {
+  using A = typename Elem<T>::acc_t;
+  if (ws_bytes < filter_workspace_t<T>(s)) return DWCONV_B200_WORKSPACE_TOO_SMALL;
+  const int kk = s.kh * s.kw;
+  int S = 0;
+  if (forced != DWCONV_B200_PATH_DIRECT) {
+    int r = rows_backward_filter<T>((const T *)x, (const T *)dy, (A *)ws, s, st, &S);
+    if (r == ROWS_SERVED) {
+      t_last_path = DWCONV_B200_PATH_ROWS;
+      int e = launch_status();
+      if (e != DWCONV_B200_OK) return e;
+    } else {
+      if (forced == DWCONV_B200_PATH_ROWS) return DWCONV_B200_UNSUPPORTED_SHAPE;
+      S = 0;
+    }
+  }
+  if (S == 0) {
+    S = direct_filter_slices(s);
+    direct_backward_filter_partial_kernel<T><<<s.C * S, 256, 0, st>>>((const T *)x, (const T *)dy,
+                                                                      (A *)ws, s, S);
+    t_last_path = DWCONV_B200_PATH_DIRECT;
+    int e = launch_status();
+    if (e != DWCONV_B200_OK) return e;
+  }
+  backward_filter_finalize_kernel<T><<<ceil_div(s.C * kk, 256), 256, 0, st>>>((const A *)ws,
+                                                                              (T *)dw, s.C, kk, S);
+  return launch_status();
+}
+
+int check_ptrs(int dtype, const void *a, const void *b, const void *c) {
+  const size_t es = elem_size(dtype);
+  if (es == 0) return DWCONV_B200_UNSUPPORTED_DTYPE;
+  if (a == nullptr || b == nullptr || c == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  if (!aligned_to(a, es) || !aligned_to(b, es) || !aligned_to(c, es)) return DWCONV_B200_MISALIGNED;
+  return DWCONV_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dwconv_b200_version(void) { return DWCONV_B200_VERSION; }
+
+const char *dwconv_b200_status_string(int status) {
+  switch (status) {
+    case DWCONV_B200_OK: return "ok";
+    case DWCONV_B200_BAD_ARGUMENT: return "bad argument (null pointer, non-positive or inconsistent extent)";
+    case DWCONV_B200_UNSUPPORTED_DTYPE: return "unsupported dtype (expected f32, f16 or f64)";
+    case DWCONV_B200_MISALIGNED: return "pointer not aligned to its element size (workspace: 16 bytes)";
+    case DWCONV_B200_WORKSPACE_TOO_SMALL: return "workspace smaller than dwconv_b200_backward_filter_workspace_bytes";
+    case DWCONV_B200_CUDA_ERROR: return "CUDA launch failed (see dwconv_b200_last_cuda_error)";
+    case DWCONV_B200_UNSUPPORTED_SHAPE: return "the forced kernel family does not serve this shape";
+    case DWCONV_B200_TOO_LARGE: return "an extent exceeds what this entry point accepts";
+    default: return "unknown status";
+  }
+}
+
+int dwconv_b200_last_cuda_error(void) { return t_last_cuda_error; }
+
+int dwconv_b200_set_path(int path) {
+  if (path < DWCONV_B200_PATH_AUTO || path > DWCONV_B200_PATH_ROWS) return -1;
+  return g_forced_path.exchange(path);
+}
+
+int dwconv_b200_last_path(void) { return t_last_path; }
+
+int dwconv_b200_out_size(int in, int up, int pad0, int pad1, int k, int down) {
+  if (down <= 0) return 0;
+  const long long num = (long long)in * up + pad0 + pad1 - k + down;
+  if (num < 0) return 0;
+  return (int)(num / down);
+}
+
+int dwconv_b200_forward(const void *x, const void *w, void *y, int dtype,
+                        const dwconv_b200_shape *shape, void *stream) {
+  int e = check_ptrs(dtype, x, w, y);
+  if (e) return e;
+  e = check_shape(shape);
+  if (e) return e;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int forced = g_forced_path.load();
+  switch (dtype) {
+    case DWCONV_B200_F32: return forward_t<float>(x, w, y, *shape, st, forced);
+    case DWCONV_B200_F16: return forward_t<__half>(x, w, y, *shape, st, forced);
+    default: return forward_t<double>(x, w, y, *shape, st, forced);
+  }
+}
+
+int dwconv_b200_backward_input(const void *dy, const void *w, void *dx, int dtype,
+                               const dwconv_b200_shape *shape, void *stream) {
+  int e = check_ptrs(dtype, dy, w, dx);
+  if (e) return e;
+  e = check_shape(shape);
+  if (e) return e;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int forced = g_forced_path.load();
+  switch (dtype) {
+    case DWCONV_B200_F32: return backward_input_t<float>(dy, w, dx, *shape, st, forced);
+    case DWCONV_B200_F16: return backward_input_t<__half>(dy, w, dx, *shape, st, forced);
+    default: return backward_input_t<double>(dy, w, dx, *shape, st, forced);
+  }
+}
+
+size_t dwconv_b200_backward_filter_workspace_bytes(int dtype, const dwconv_b200_shape *shape) {
+  if (elem_size(dtype) == 0 || check_shape(shape) != DWCONV_B200_OK) return 0;
+  switch (dtype) {
+    case DWCONV_B200_F32: return filter_workspace_t<float>(*shape);
+    case DWCONV_B200_F16: return filter_workspace_t<__half>(*shape);
+    default: return filter_workspace_t<double>(*shape);
+  }
+}
+
+int dwconv_b200_backward_filter(const void *x, const void *dy, void *dw, void *workspace,
+                                size_t workspace_bytes, int dtype,
+                                const dwconv_b200_shape *shape, void *stream) {
+  int e = check_ptrs(dtype, x, dy, dw);
+  if (e) return e;
+  e = check_shape(shape);
+  if (e) return e;
+  if (workspace == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  if (!aligned_to(workspace, 16)) return DWCONV_B200_MISALIGNED;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int forced = g_forced_path.load();
+  switch (dtype) {
+    case DWCONV_B200_F32:
+      return backward_filter_t<float>(x, dy, dw, workspace, workspace_bytes, *shape, st, forced);
+    case DWCONV_B200_F16:
+      return backward_filter_t<__half>(x, dy, dw, workspace, workspace_bytes, *shape, st, forced);
+    default:
+      return backward_filter_t<double>(x, dy, dw, workspace, workspace_bytes, *shape, st, forced);
+  }
+}
+
+int dwconv_b200_use_dwconv2d_small(int in_h, int in_w, int kh, int kw, int up_h, int up_w,
+                                   int down_h, int down_w, int pad_h, int pad_w) {
+  const int out_h = dwconv_b200_out_size(in_h, up_h, pad_h, pad_h, kh, down_h);
+  const int out_w = dwconv_b200_out_size(in_w, up_w, pad_w, pad_w, kw, down_w);
+  return (down_h == 1 && down_w == 1 && in_h <= 32 && in_w <= 32 && in_h == out_h &&
+          in_w == out_w && pad_h >= 0 && pad_h < kh && pad_w >= 0 && pad_w < kw &&
+          kh * kw <= (in_h + 1) / 2 * in_w)
+             ? 1
+             : 0;
+}
+
+int dwconv_b200_dwconv2d(const void *in, const void *kernel, void *out, int dtype, int N, int C,
+                         int in_h, int in_w, int kh, int kw, int up_h, int up_w, int down_h,
+                         int down_w, int pad_h0, int pad_h1, int pad_w0, int pad_w1, int forward,
+                         void *stream) {
+  if (up_h <= 0 || up_w <= 0 || down_h <= 0 || down_w <= 0) return DWCONV_B200_BAD_ARGUMENT;
+  const int out_h = dwconv_b200_out_size(in_h, up_h, pad_h0, pad_h1, kh, down_h);
+  const int out_w = dwconv_b200_out_size(in_w, up_w, pad_w0, pad_w1, kw, down_w);
+  if (out_h <= 0 || out_w <= 0) return DWCONV_B200_BAD_ARGUMENT;
+  dwconv_b200_shape s;
+  s.N = N; s.C = C; s.kh = kh; s.kw = kw;
+  if (forward) {
+    // plain strided correlation: in = x, out = y
+    if (up_h != 1 || up_w != 1) return DWCONV_B200_UNSUPPORTED_SHAPE;
+    s.H = in_h; s.W = in_w; s.sh = down_h; s.sw = down_w; s.ph = pad_h0; s.pw = pad_w0;
+    s.Ho = out_h; s.Wo = out_w;
+    return dwconv_b200_forward(in, kernel, out, dtype, &s, stream);
+  }
+  // transposed: in = dy [Ho,Wo], out = dx [H,W], forward stride = up, and the
+  // leading padding k-1-p of the flipped correlation gives the forward padding p
+  if (down_h != 1 || down_w != 1) return DWCONV_B200_UNSUPPORTED_SHAPE;
+  s.H = out_h; s.W = out_w; s.sh = up_h; s.sw = up_w;
+  s.ph = kh - 1 - pad_h0; s.pw = kw - 1 - pad_w0;
+  s.Ho = in_h; s.Wo = in_w;
+  if (s.ph < 0 || s.pw < 0) return DWCONV_B200_UNSUPPORTED_SHAPE;
+  return dwconv_b200_backward_input(in, kernel, out, dtype, &s, stream);
+}
+
+int dwconv_b200_dwconv2d_small(const void *in, const void *kernel, void *out, int dtype, int N,
+                               int C, int in_h, int in_w, int kh, int kw, int up_h, int up_w,
+                               int down_h, int down_w, int pad_h, int pad_w, int forward,
+                               void *stream) {
+  return dwconv_b200_dwconv2d(in, kernel, out, dtype, N, C, in_h, in_w, kh, kw, up_h, up_w,
+                              down_h, down_w, pad_h, pad_h, pad_w, pad_w, forward, stream);
+}
+
+int dwconv_b200_dwconv2d_backward_kernel(const void *input, const void *out_grad, void *dkernel,
+                                         void *workspace, size_t workspace_bytes, int dtype,
+                                         int N, int C, int in_h, int in_w, int out_h, int out_w,
+                                         int kh, int kw, int up_h, int up_w, int down_h,
+                                         int down_w, int pad_h, int pad_w, void *stream) {
+  if (up_h != 1 || up_w != 1) return DWCONV_B200_UNSUPPORTED_SHAPE;
+  dwconv_b200_shape s;
+  s.N = N; s.C = C; s.H = in_h; s.W = in_w; s.kh = kh; s.kw = kw;
+  s.sh = down_h; s.sw = down_w; s.ph = pad_h; s.pw = pad_w; s.Ho = out_h; s.Wo = out_w;
+  return dwconv_b200_backward_filter(input, out_grad, dkernel, workspace, workspace_bytes, dtype,
+                                     &s, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,51 @@
+// Shared device/host helpers of libdwconv_b200: element traits, status plumbing.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "dwconv_b200.h"
+
+namespace dwb {
+
+using Shape = dwconv_b200_shape;
+
+// Accumulator type per element type: fp16 and fp32 accumulate in fp32, fp64 in fp64.
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  using acc_t = float;
+  static __device__ __forceinline__ float ld(const float *p) { return __ldg(p); }
+  static __device__ __forceinline__ float to_acc(float v) { return v; }
+  static __device__ __forceinline__ float from_acc(float v) { return v; }
+};
+template <> struct Elem<__half> {
+  using acc_t = float;
+  static __device__ __forceinline__ float ld(const __half *p) { return __half2float(__ldg(p)); }
+  static __device__ __forceinline__ float to_acc(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_acc(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<double> {
+  using acc_t = double;
+  static __device__ __forceinline__ double ld(const double *p) { return __ldg(p); }
+  static __device__ __forceinline__ double to_acc(double v) { return v; }
+  static __device__ __forceinline__ double from_acc(double v) { return v; }
+};
+
+// One fused multiply-add, never split by the compiler.
+__device__ __forceinline__ float fma_acc(float a, float b, float c) { return fmaf(a, b, c); }
+__device__ __forceinline__ double fma_acc(double a, double b, double c) { return fma(a, b, c); }
+
+__host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+__host__ __device__ __forceinline__ long long ceil_div_ll(long long a, long long b) {
+  return (a + b - 1) / b;
+}
+
+// Sum over the 32 lanes of a warp in a fixed butterfly order (deterministic).
+template <typename A> __device__ __forceinline__ A warp_sum(A v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+}  // namespace dwb

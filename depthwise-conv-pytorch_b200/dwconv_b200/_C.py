@@ -1,0 +1,92 @@
+"""Operator-level functions with the names, argument order and error behaviour of
+the reference's pybind11 module ``torch_dwconv._C`` (torch_dwconv/dwconv.cpp:60-67).
+
+Each function takes torch tensors, allocates the result with torch (the shared
+library never allocates) and calls the matching C entry point on the tensor's
+device and the current stream of that device.
+"""
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64}
+
+
+def _check_cuda(t, name):
+    # same text as CHECK_CUDA, torch_dwconv/dwconv.cpp:24-25
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+
+
+def _dtype_code(t, *others):
+    code = _DTYPES.get(t.dtype)
+    if code is None:
+        raise RuntimeError(f"dwconv_b200: unsupported dtype {t.dtype} (float32, float16, float64)")
+    for o in others:
+        if o.dtype != t.dtype or o.device != t.device:
+            raise RuntimeError("dwconv_b200: tensors must share dtype and device "
+                               f"({t.dtype}/{t.device} vs {o.dtype}/{o.device})")
+    return code
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def use_dwconv2d_small(input, kernel, up_h, up_w, down_h, down_w, pad_h, pad_w):
+    """torch_dwconv/dwconv.cpp:61 -- host-only shape test, works for any device."""
+    return bool(_lib.lib.dwconv_b200_use_dwconv2d_small(
+        input.shape[2], input.shape[3], kernel.shape[2], kernel.shape[3],
+        up_h, up_w, down_h, down_w, pad_h, pad_w))
+
+
+def dwconv2d(input, kernel, up_h, up_w, down_h, down_w, pad_h0, pad_h1, pad_w0, pad_w1, forward):
+    """torch_dwconv/dwconv.cpp:27-35."""
+    _check_cuda(input, "input")
+    _check_cuda(kernel, "kernel")
+    code = _dtype_code(input, kernel)
+    input = input.contiguous()
+    kernel = kernel.contiguous()
+    N, C, H, W = input.shape
+    kh, kw = kernel.shape[2], kernel.shape[3]
+    oh = _lib.lib.dwconv_b200_out_size(H, up_h, pad_h0, pad_h1, kh, down_h)
+    ow = _lib.lib.dwconv_b200_out_size(W, up_w, pad_w0, pad_w1, kw, down_w)
+    if oh <= 0 or ow <= 0:
+        raise RuntimeError(f"dwconv_b200.dwconv2d: empty output ({oh} x {ow})")
+    out = torch.empty((N, C, oh, ow), dtype=input.dtype, device=input.device)
+    with torch.cuda.device(input.device):
+        st = _lib.lib.dwconv_b200_dwconv2d(
+            input.data_ptr(), kernel.data_ptr(), out.data_ptr(), code, N, C, H, W, kh, kw,
+            up_h, up_w, down_h, down_w, pad_h0, pad_h1, pad_w0, pad_w1, 1 if forward else 0,
+            _stream(input))
+    _lib.check(st, "dwconv2d")
+    return out
+
+
+def dwconv2d_small(input, kernel, up_h, up_w, down_h, down_w, pad_h, pad_w, forward):
+    """torch_dwconv/dwconv.cpp:37-46 (symmetric padding)."""
+    return dwconv2d(input, kernel, up_h, up_w, down_h, down_w, pad_h, pad_h, pad_w, pad_w, forward)
+
+
+def dwconv2d_backward_kernel(input, out_grad, kernel, up_h, up_w, down_h, down_w, pad_h, pad_w):
+    """torch_dwconv/dwconv.cpp:48-58.  ``kernel`` only supplies the filter extent."""
+    _check_cuda(input, "input")
+    _check_cuda(out_grad, "out_grad")
+    code = _dtype_code(input, out_grad)
+    input = input.contiguous()
+    out_grad = out_grad.contiguous()
+    N, C, H, W = input.shape
+    kh, kw = kernel.shape[2], kernel.shape[3]
+    oh, ow = out_grad.shape[2], out_grad.shape[3]
+    shape = _lib.Shape(N, C, H, W, kh, kw, down_h, down_w, pad_h, pad_w, oh, ow)
+    nbytes = _lib.lib.dwconv_b200_backward_filter_workspace_bytes(code, shape)
+    if nbytes == 0:
+        raise RuntimeError("dwconv_b200.dwconv2d_backward_kernel: invalid geometry")
+    dkernel = torch.empty((C, 1, kh, kw), dtype=input.dtype, device=input.device)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=input.device)
+    with torch.cuda.device(input.device):
+        st = _lib.lib.dwconv_b200_dwconv2d_backward_kernel(
+            input.data_ptr(), out_grad.data_ptr(), dkernel.data_ptr(), ws.data_ptr(), nbytes, code,
+            N, C, H, W, oh, ow, kh, kw, up_h, up_w, down_h, down_w, pad_h, pad_w, _stream(input))
+    _lib.check(st, "dwconv2d_backward_kernel")
+    return dkernel

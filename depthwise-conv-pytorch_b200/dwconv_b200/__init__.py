@@ -1,0 +1,6 @@
+"""dwconv_b200: depthwise conv2d for B200, a drop-in for ``torch_dwconv``."""
+from .dwconv import (DepthwiseConv2d, DepthwiseConv2dFunction, check_options,  # noqa: F401
+                     depthwise_conv2d, depthwise_conv2d_fn, make_tuple, use_dwconv2d_small)
+from . import _C  # noqa: F401
+
+__all__ = ["depthwise_conv2d", "DepthwiseConv2d"]

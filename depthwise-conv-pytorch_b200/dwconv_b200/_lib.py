@@ -1,0 +1,74 @@
+"""ctypes binding of ``libdwconv_b200.so`` (declarations: ``include/dwconv_b200.h``).
+
+There is no fallback: if the library is missing, importing this module raises.
+"""
+import ctypes
+import os
+
+from .build import LIB_PATH
+
+F32, F16, F64 = 0, 1, 2
+PATH_AUTO, PATH_DIRECT, PATH_ROWS = 0, 1, 2
+OK = 0
+
+
+class Shape(ctypes.Structure):
+    """Mirror of ``dwconv_b200_shape``."""
+    _fields_ = [(n, ctypes.c_int) for n in
+                ("N", "C", "H", "W", "kh", "kw", "sh", "sw", "ph", "pw", "Ho", "Wo")]
+
+
+def _load():
+    path = os.environ.get("DWCONV_B200_LIB", LIB_PATH)
+    if not os.path.exists(path):
+        raise RuntimeError(
+            f"dwconv_b200: {path} not found. Build it with `python -m dwconv_b200.build` "
+            "(needs nvcc); there is no CPU or PyTorch fallback.")
+    lib = ctypes.CDLL(path)
+    vp, ci, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+    sp = ctypes.POINTER(Shape)
+    sig = {
+        "dwconv_b200_version": (ci, []),
+        "dwconv_b200_status_string": (ctypes.c_char_p, [ci]),
+        "dwconv_b200_last_cuda_error": (ci, []),
+        "dwconv_b200_set_path": (ci, [ci]),
+        "dwconv_b200_last_path": (ci, []),
+        "dwconv_b200_out_size": (ci, [ci] * 6),
+        "dwconv_b200_forward": (ci, [vp, vp, vp, ci, sp, vp]),
+        "dwconv_b200_backward_input": (ci, [vp, vp, vp, ci, sp, vp]),
+        "dwconv_b200_backward_filter_workspace_bytes": (sz, [ci, sp]),
+        "dwconv_b200_backward_filter": (ci, [vp, vp, vp, vp, sz, ci, sp, vp]),
+        "dwconv_b200_use_dwconv2d_small": (ci, [ci] * 10),
+        "dwconv_b200_dwconv2d": (ci, [vp, vp, vp, ci] + [ci] * 15 + [vp]),
+        "dwconv_b200_dwconv2d_small": (ci, [vp, vp, vp, ci] + [ci] * 13 + [vp]),
+        "dwconv_b200_dwconv2d_backward_kernel": (ci, [vp, vp, vp, vp, sz, ci] + [ci] * 14 + [vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+EXPORTS = (
+    "dwconv_b200_version", "dwconv_b200_status_string", "dwconv_b200_last_cuda_error",
+    "dwconv_b200_set_path", "dwconv_b200_last_path", "dwconv_b200_out_size",
+    "dwconv_b200_forward", "dwconv_b200_backward_input",
+    "dwconv_b200_backward_filter_workspace_bytes", "dwconv_b200_backward_filter",
+    "dwconv_b200_use_dwconv2d_small", "dwconv_b200_dwconv2d", "dwconv_b200_dwconv2d_small",
+    "dwconv_b200_dwconv2d_backward_kernel",
+)
+
+
+def status_string(code):
+    return lib.dwconv_b200_status_string(int(code)).decode()
+
+
+def check(code, what):
+    """Turn a non-zero status into the RuntimeError a torch extension would raise."""
+    if code != OK:
+        detail = status_string(code)
+        if code == 5:
+            detail += f" [cudaError {lib.dwconv_b200_last_cuda_error()}]"
+        raise RuntimeError(f"dwconv_b200.{what}: {detail}")

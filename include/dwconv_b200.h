@@ -1,0 +1,166 @@
+/*
+ * dwconv_b200 -- depthwise conv2d (forward, backward-input, backward-filter)
+ * for NVIDIA B200 (sm_100a).  C ABI of libdwconv_b200.so.
+ *
+ * The library is the device side of a drop-in for the `torch_dwconv` extension
+ * of rosinality/depthwise-conv-pytorch.  That extension exports four functions
+ * from a pybind11 module (torch_dwconv/dwconv.cpp:60-67); each of them has a
+ * counterpart below that takes raw device pointers, sizes and a stream instead
+ * of torch tensors, and never allocates: the caller owns inputs, outputs and
+ * the backward-filter workspace.
+ *
+ * Conventions
+ *   - activations are contiguous NCHW, filters contiguous [C,1,kh,kw];
+ *   - every pointer is a device pointer of the CURRENT device, aligned to the
+ *     element size (faster kernels are chosen when it is 16-byte aligned);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream); every
+ *     call is asynchronous on it and never synchronises;
+ *   - every call returns a dwconv_b200_status; nothing is launched unless the
+ *     arguments validated, and every launch is followed by an error check;
+ *   - fp16 data is accumulated in fp32 and rounded once; fp32 in fp32; fp64 in
+ *     fp64.  Forward and backward-input add the taps in row-major order into
+ *     a single accumulator with one fused multiply-add per tap, which is the
+ *     order of the reference kernels (torch_dwconv/dwconv_kernel.cu:164-172),
+ *     so fp32 results are bit-identical to it.  Backward-filter is a
+ *     deterministic two-pass tree reduction (the reference uses atomics,
+ *     dwconv_kernel.cu:303-305,:583).
+ *   - the library is re-entrant; it keeps no state besides once-only kernel
+ *     attribute set-up.
+ */
+#ifndef DWCONV_B200_H_
+#define DWCONV_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define DWCONV_B200_API __attribute__((visibility("default")))
+#else
+#define DWCONV_B200_API
+#endif
+
+#define DWCONV_B200_VERSION 100 /* major*10000 + minor*100 + patch */
+
+typedef enum dwconv_b200_dtype {
+  DWCONV_B200_F32 = 0,
+  DWCONV_B200_F16 = 1,
+  DWCONV_B200_F64 = 2
+} dwconv_b200_dtype;
+
+typedef enum dwconv_b200_status {
+  DWCONV_B200_OK = 0,
+  DWCONV_B200_BAD_ARGUMENT = 1,       /* null pointer, non-positive extent, inconsistent sizes */
+  DWCONV_B200_UNSUPPORTED_DTYPE = 2,
+  DWCONV_B200_MISALIGNED = 3,         /* pointer not aligned to its element size */
+  DWCONV_B200_WORKSPACE_TOO_SMALL = 4,
+  DWCONV_B200_CUDA_ERROR = 5,         /* a launch failed; see dwconv_b200_last_cuda_error */
+  DWCONV_B200_UNSUPPORTED_SHAPE = 6,  /* a forced kernel family cannot serve this shape */
+  DWCONV_B200_TOO_LARGE = 7           /* an extent exceeds what the entry point accepts */
+} dwconv_b200_status;
+
+/* Kernel families, for dwconv_b200_set_path / dwconv_b200_last_path. */
+typedef enum dwconv_b200_path {
+  DWCONV_B200_PATH_AUTO = 0,    /* choose per shape (default) */
+  DWCONV_B200_PATH_DIRECT = 1,  /* one thread per output, any shape / dtype */
+  DWCONV_B200_PATH_ROWS = 2     /* bulk-copy staged row tiles, lane-per-column warps */
+} dwconv_b200_path;
+
+/* Geometry of one depthwise convolution in forward terms.
+ * Ho = floor((H + 2*ph - kh)/sh) + 1 for symmetric padding; a caller with a
+ * different bottom/right padding passes the Ho/Wo it wants (any value with
+ * 1 <= Ho and (Ho-1)*sh - ph + kh <= H + "bottom padding" is meaningful: rows
+ * outside the input read as zero). */
+typedef struct dwconv_b200_shape {
+  int N, C, H, W; /* input  [N,C,H,W]  */
+  int kh, kw;     /* filter [C,1,kh,kw] */
+  int sh, sw;     /* stride */
+  int ph, pw;     /* top / left zero padding */
+  int Ho, Wo;     /* output [N,C,Ho,Wo] */
+} dwconv_b200_shape;
+
+DWCONV_B200_API int dwconv_b200_version(void);
+DWCONV_B200_API const char *dwconv_b200_status_string(int status);
+/* cudaError_t of the most recent failed launch on the calling thread (0 if none). */
+DWCONV_B200_API int dwconv_b200_last_cuda_error(void);
+
+/* Force a kernel family (testing / profiling).  Process-wide; returns the previous value. */
+DWCONV_B200_API int dwconv_b200_set_path(int path);
+/* Kernel family that served the calling thread's most recent call. */
+DWCONV_B200_API int dwconv_b200_last_path(void);
+
+/* Output extent of up/pad/correlate/decimate:
+ * (in*up + pad0 + pad1 - k + down) / down.
+ * Replaces make_conv2d_params, torch_dwconv/dwconv_kernel.cu:612-615. */
+DWCONV_B200_API int dwconv_b200_out_size(int in, int up, int pad0, int pad1, int k, int down);
+
+/* ------------------------------------------------------------------------
+ * Natural-form entry points (what the Python autograd function calls).
+ * ---------------------------------------------------------------------- */
+
+/* y = depthwise cross-correlation of x with w.
+ * Replaces dwconv2d(..., forward=true) and dwconv2d_small(..., forward=true),
+ * torch_dwconv/dwconv.cpp:27-46, as called at torch_dwconv/dwconv.py:28-35. */
+DWCONV_B200_API int dwconv_b200_forward(const void *x, const void *w, void *y, int dtype,
+                        const dwconv_b200_shape *shape, void *stream);
+
+/* dx = gradient of the forward w.r.t. x, given dy [N,C,Ho,Wo]; dx is [N,C,H,W]
+ * and every element of it is written (rows/columns no window reaches get 0).
+ * Replaces dwconv2d(..., forward=false) and dwconv2d_small(..., forward=false),
+ * torch_dwconv/dwconv.cpp:27-46, as called at torch_dwconv/dwconv.py:56-64. */
+DWCONV_B200_API int dwconv_b200_backward_input(const void *dy, const void *w, void *dx, int dtype,
+                               const dwconv_b200_shape *shape, void *stream);
+
+/* Scratch bytes dwconv_b200_backward_filter needs for this geometry (>= 16). */
+DWCONV_B200_API size_t dwconv_b200_backward_filter_workspace_bytes(int dtype, const dwconv_b200_shape *shape);
+
+/* dw [C,1,kh,kw] = gradient w.r.t. the filter.  `workspace` is caller-owned
+ * device scratch of at least the size reported above, 16-byte aligned; it is
+ * fully overwritten, never read before being written.
+ * Replaces dwconv2d_backward_kernel, torch_dwconv/dwconv.cpp:48-58, as called
+ * at torch_dwconv/dwconv.py:66-68 (which also zero-fills dW first,
+ * dwconv_kernel.cu:1026-1027; not needed here). */
+DWCONV_B200_API int dwconv_b200_backward_filter(const void *x, const void *dy, void *dw, void *workspace,
+                                size_t workspace_bytes, int dtype,
+                                const dwconv_b200_shape *shape, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Operator-form entry points: one per function of the reference's pybind
+ * module, same argument meaning, pointers instead of tensors.
+ * ---------------------------------------------------------------------- */
+
+/* Replaces use_dwconv2d_small, torch_dwconv/dwconv.cpp:3-5,61 and
+ * dwconv_kernel.cu:652-662.  Pure host logic; returns 0 or 1. */
+DWCONV_B200_API int dwconv_b200_use_dwconv2d_small(int in_h, int in_w, int kh, int kw, int up_h, int up_w,
+                                   int down_h, int down_w, int pad_h, int pad_w);
+
+/* Replaces dwconv2d, torch_dwconv/dwconv.cpp:27-35.  forward != 0: requires
+ * up == 1 and correlates with stride `down`; forward == 0: requires down == 1
+ * and computes the transposed operation with stride `up` (flipped filter,
+ * dwconv_kernel.cu:107-114).  `out` is [N,C,out_h,out_w] with
+ * out = dwconv_b200_out_size(in, up, pad0, pad1, k, down). */
+DWCONV_B200_API int dwconv_b200_dwconv2d(const void *in, const void *kernel, void *out, int dtype, int N, int C,
+                         int in_h, int in_w, int kh, int kw, int up_h, int up_w, int down_h,
+                         int down_w, int pad_h0, int pad_h1, int pad_w0, int pad_w1, int forward,
+                         void *stream);
+
+/* Replaces dwconv2d_small, torch_dwconv/dwconv.cpp:37-46 (symmetric padding). */
+DWCONV_B200_API int dwconv_b200_dwconv2d_small(const void *in, const void *kernel, void *out, int dtype, int N,
+                               int C, int in_h, int in_w, int kh, int kw, int up_h, int up_w,
+                               int down_h, int down_w, int pad_h, int pad_w, int forward,
+                               void *stream);
+
+/* Replaces dwconv2d_backward_kernel, torch_dwconv/dwconv.cpp:48-58: `up` must
+ * be 1, `down` is the forward stride, `pad` the forward padding. */
+DWCONV_B200_API int dwconv_b200_dwconv2d_backward_kernel(const void *input, const void *out_grad, void *dkernel,
+                                         void *workspace, size_t workspace_bytes, int dtype,
+                                         int N, int C, int in_h, int in_w, int out_h, int out_w,
+                                         int kh, int kw, int up_h, int up_w, int down_h,
+                                         int down_w, int pad_h, int pad_w, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DWCONV_B200_H_ */

@@ -1,0 +1,177 @@
+"""Host-side behaviour that needs no GPU: the library loads and exports what the header
+declares, argument validation, and the Python API's error behaviour (same texts as the
+reference, fixtures from tests/golden/make_golden.py)."""
+import ctypes
+import glob
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT, golden
+
+
+def _declared_symbols():
+    names = set()
+    for h in glob.glob(os.path.join(ROOT, "include", "*.h")):
+        src = re.sub(r"/\*.*?\*/", "", open(h).read(), flags=re.S)
+        names.update(re.findall(r"\b(dwconv_b200_\w+)\s*\(", src))
+    return sorted(names)
+
+
+def test_library_exports_every_declared_symbol():
+    from dwconv_b200 import _lib
+    declared = _declared_symbols()
+    assert len(declared) >= 14
+    for name in declared:
+        assert hasattr(_lib.lib, name), f"{name} declared in include/ but not exported"
+    assert _lib.lib.dwconv_b200_version() >= 100
+    assert set(_lib.EXPORTS) <= set(declared)
+
+
+def test_status_strings():
+    from dwconv_b200 import _lib
+    seen = {_lib.status_string(i) for i in range(8)}
+    assert len(seen) == 8 and "ok" in seen
+    assert _lib.status_string(99) == "unknown status"
+
+
+def test_out_size_and_small_test_match_reference_table():
+    from dwconv_b200 import _lib
+    for H, W, kh, kw, sh, sw, ph, pw, want in golden().meta["use_small_table"]:
+        got = _lib.lib.dwconv_b200_use_dwconv2d_small(H, W, kh, kw, 1, 1, sh, sw, ph, pw)
+        assert got == want, (H, W, kh, kw, sh, sw, ph, pw)
+    for m in golden().meta["cases"]:
+        t = golden().tensors(m["name"])
+        for ax, (n_in, k) in enumerate(((m["H"], m["kh"]), (m["W"], m["kw"]))):
+            got = _lib.lib.dwconv_b200_out_size(n_in, 1, m["padding"][ax], m["padding"][ax], k,
+                                                m["stride"][ax])
+            assert got == t["y"].shape[2 + ax]
+
+
+def test_argument_validation_returns_status_before_any_launch():
+    from dwconv_b200 import _lib
+    L = _lib.lib
+    s = _lib.Shape(1, 1, 8, 8, 3, 3, 1, 1, 1, 1, 8, 8)
+    fake = ctypes.c_void_p(0x1000)  # never dereferenced: validation fails first
+    assert L.dwconv_b200_forward(None, fake, fake, _lib.F32, s, None) == 1
+    assert L.dwconv_b200_forward(fake, fake, fake, 9, s, None) == 2
+    assert L.dwconv_b200_forward(ctypes.c_void_p(0x1002), fake, fake, _lib.F32, s, None) == 3
+    assert L.dwconv_b200_forward(fake, fake, fake, _lib.F32, None, None) == 1
+    bad = _lib.Shape(1, 1, 8, 8, 3, 3, 0, 1, 1, 1, 8, 8)
+    assert L.dwconv_b200_backward_input(fake, fake, fake, _lib.F32, bad, None) == 1
+    neg = _lib.Shape(1, 1, 8, 8, 3, 3, 1, 1, -1, 1, 8, 8)
+    assert L.dwconv_b200_forward(fake, fake, fake, _lib.F32, neg, None) == 1
+    huge = _lib.Shape(1, 1, 1 << 16, 1 << 16, 3, 3, 1, 1, 1, 1, 1 << 16, 1 << 16)
+    assert L.dwconv_b200_forward(fake, fake, fake, _lib.F32, huge, None) == 7
+    # backward-filter: workspace checks
+    need = L.dwconv_b200_backward_filter_workspace_bytes(_lib.F32, s)
+    assert need >= 16 and need % 16 == 0
+    assert L.dwconv_b200_backward_filter(fake, fake, fake, None, need, _lib.F32, s, None) == 1
+    assert L.dwconv_b200_backward_filter(fake, fake, fake, ctypes.c_void_p(0x1008), need,
+                                         _lib.F32, s, None) == 3
+    assert L.dwconv_b200_backward_filter(fake, fake, fake, fake, need - 1, _lib.F32, s, None) == 4
+    assert L.dwconv_b200_backward_filter_workspace_bytes(9, s) == 0
+    assert L.dwconv_b200_backward_filter_workspace_bytes(_lib.F32, bad) == 0
+    # operator form: the two directions it serves, and the ones it refuses
+    assert L.dwconv_b200_dwconv2d(fake, fake, fake, _lib.F32, 1, 1, 8, 8, 3, 3, 2, 2, 2, 2,
+                                  1, 1, 1, 1, 1, None) == 6
+    assert L.dwconv_b200_dwconv2d(fake, fake, fake, _lib.F32, 1, 1, 8, 8, 3, 3, 1, 1, 0, 1,
+                                  1, 1, 1, 1, 1, None) == 1
+    assert L.dwconv_b200_set_path(7) == -1
+    assert L.dwconv_b200_set_path(_lib.PATH_AUTO) == _lib.PATH_AUTO
+
+
+def test_workspace_covers_every_kernel_family():
+    from dwconv_b200 import _lib
+    for m in golden().meta["cases"]:
+        t = golden().tensors(m["name"])
+        s = _lib.Shape(m["N"], m["C"], m["H"], m["W"], m["kh"], m["kw"], *m["stride"],
+                       *m["padding"], t["y"].shape[2], t["y"].shape[3])
+        for code, acc in ((_lib.F32, 4), (_lib.F16, 4), (_lib.F64, 8)):
+            b = _lib.lib.dwconv_b200_backward_filter_workspace_bytes(code, s)
+            assert b >= m["C"] * m["kh"] * m["kw"] * acc
+
+
+def test_python_api_error_texts_match_reference():
+    import dwconv_b200 as d
+    err = golden().meta["errors"]
+
+    def expect(key, fn):
+        kind, text = err[key]
+        with pytest.raises({"ValueError": ValueError, "RuntimeError": RuntimeError}[kind]) as ei:
+            fn()
+        assert str(ei.value) == text
+
+    expect("dilation", lambda: d.check_options(4, 4, 2, None, None))
+    expect("groups", lambda: d.check_options(4, 4, 1, 2, None))
+    expect("channels", lambda: d.check_options(4, 8, 1, None, None))
+    expect("bias", lambda: d.check_options(4, 4, 1, None, True))
+    expect("padding_mode", lambda: d.check_options(4, 4, 1, None, None, "reflect"))
+    expect("tuple_len", lambda: d.make_tuple((1, 2, 3), 2))
+    expect("cpu_tensor", lambda: d.depthwise_conv2d(torch.zeros(1, 2, 40, 40),
+                                                    torch.zeros(2, 1, 3, 3)))
+    mt = err["make_tuple"]
+    assert list(d.make_tuple(3, 2)) == mt["int"]
+    assert list(d.make_tuple([3], 2)) == mt["list1"]
+    assert list(d.make_tuple((1, 2), 2)) == mt["tuple2"]
+    # same validation through the public function and the module constructor
+    x, w = torch.zeros(1, 4, 8, 8), torch.zeros(4, 1, 3, 3)
+    with pytest.raises(ValueError, match="dilations"):
+        d.depthwise_conv2d(x, w, dilation=2)
+    with pytest.raises(ValueError, match="groups"):
+        d.depthwise_conv2d(x, w, groups=2)
+    with pytest.raises(ValueError, match="bias"):
+        d.depthwise_conv2d(x, w, torch.ones(1))
+    with pytest.raises(ValueError, match="in_channels != out_channels"):
+        d.depthwise_conv2d(x, torch.zeros(8, 1, 3, 3))
+    with pytest.raises(ValueError, match="non-zero paddings"):
+        d.DepthwiseConv2d(4, 4, 3, padding_mode="circular")
+
+
+def test_cpu_tensors_never_fall_back():
+    """The reference lets small maps it cannot serve fall through to F.conv2d, which also
+    runs on CPU; this library has no such route."""
+    import dwconv_b200 as d
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        d.depthwise_conv2d(torch.zeros(1, 2, 28, 28), torch.zeros(2, 1, 3, 3), stride=2, padding=1)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        d._C.dwconv2d(torch.zeros(1, 2, 40, 40), torch.zeros(2, 1, 3, 3), 1, 1, 1, 1, 1, 1, 1, 1, True)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        d._C.dwconv2d_backward_kernel(torch.zeros(1, 2, 8, 8), torch.zeros(1, 2, 8, 8),
+                                      torch.zeros(2, 1, 3, 3), 1, 1, 1, 1, 1, 1)
+
+
+def test_module_surface_and_state_dict():
+    import dwconv_b200 as d
+    m = d.DepthwiseConv2d(6, 6, 5, stride=2, padding=2)
+    assert list(m.state_dict().keys()) == ["weight"]
+    assert tuple(m.weight.shape) == (6, 1, 5, 5)
+    assert (m.stride, m.padding, m.in_channel, m.kernel_size, m.custom) == (2, 2, 6, 5, True)
+    ref = torch.nn.Conv2d(6, 6, 5, stride=2, padding=2, groups=6, bias=False)
+    m.load_state_dict(ref.state_dict())  # same key and shape as nn.Conv2d(groups=C, bias=False)
+    x = torch.randn(2, 6, 9, 9)
+    plain = d.DepthwiseConv2d(6, 6, 5, stride=2, padding=2, custom=False)
+    plain.load_state_dict(ref.state_dict())
+    assert torch.equal(plain(x), ref(x))  # custom=False is PyTorch's own operator
+
+
+def test_compat_import_name():
+    import torch_dwconv
+    import dwconv_b200
+    assert torch_dwconv.depthwise_conv2d is dwconv_b200.depthwise_conv2d
+    assert torch_dwconv.DepthwiseConv2d is dwconv_b200.DepthwiseConv2d
+    for fn in ("use_dwconv2d_small", "dwconv2d", "dwconv2d_small", "dwconv2d_backward_kernel"):
+        assert callable(getattr(torch_dwconv._C, fn))
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    import importlib
+    import subprocess
+    import sys
+    code = ("import os,sys; os.environ['DWCONV_B200_LIB']=r'%s'; sys.path.insert(0, r'%s');"
+            "import dwconv_b200") % (str(tmp_path / "nope.so"),
+                                     os.path.join(ROOT, "depthwise-conv-pytorch_b200"))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True)
+    assert r.returncode != 0 and "no CPU or PyTorch fallback" in r.stderr

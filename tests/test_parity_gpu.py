@@ -1,0 +1,301 @@
+"""GPU parity: the CUDA library, called through its C ABI, against the CPU oracle, the
+fixtures produced by the reference package, and the reference's own test cases."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import oracle
+from conftest import NP_DT, assert_close_fp, assert_dw_close, case_names, golden
+from dwconv_b200 import _lib
+from gpu_util import (c_backward_filter, c_backward_input, c_forward, forced_path, last_path,
+                      seeded)
+
+pytestmark = pytest.mark.gpu
+
+PATHS = {"auto": _lib.PATH_AUTO, "direct": _lib.PATH_DIRECT, "rows": _lib.PATH_ROWS}
+
+
+def _check_three_ops(x, w, dy, stride, padding, dt, path, what, exact=True):
+    """Runs forward, backward-input and backward-filter through the C ABI under `path` and
+    checks them against the oracle.  Returns the outputs (None where a forced family
+    declined the shape)."""
+    kh, kw = w.shape[2:]
+    H, W = x.shape[2:]
+    out = {}
+    with forced_path(PATHS[path]):
+        st, y = c_forward(x, w, stride, padding)
+        out["y"] = (st, y, last_path())
+        st, dx = c_backward_input(dy, w, (H, W), stride, padding)
+        out["dx"] = (st, dx, last_path())
+        st, dw = c_backward_filter(x, dy, (kh, kw), stride, padding)
+        out["dw"] = (st, dw, last_path())
+    torch.cuda.synchronize()
+    res = {}
+    for key, (st, t, used) in out.items():
+        if path == "rows" and st == 6:
+            res[key] = None  # the forced family does not serve this shape; that is a status, not UB
+            continue
+        assert st == 0, f"{what}/{key}: status {st} ({_lib.status_string(st)})"
+        if path == "rows":
+            assert used == _lib.PATH_ROWS
+        if path == "direct":
+            assert used == _lib.PATH_DIRECT
+        assert not torch.isnan(t).any(), f"{what}/{key}: output not fully written"
+        res[key] = t
+    if res["y"] is not None:
+        assert_close_fp(res["y"], oracle.forward(x, w, stride, padding), dt, kh, kw, f"{what}/y")
+        if exact and dt != torch.float64:
+            assert torch.equal(res["y"].cpu(), oracle.forward_seq(x, w, stride, padding)), \
+                f"{what}/y: not bit-identical to the sequential-order oracle"
+    if res["dx"] is not None:
+        assert_close_fp(res["dx"], oracle.backward_input(dy, w, (H, W), stride, padding), dt, kh,
+                        kw, f"{what}/dx")
+        if exact and dt != torch.float64:
+            assert torch.equal(res["dx"].cpu(),
+                               oracle.backward_input_seq(dy, w, (H, W), stride, padding)), \
+                f"{what}/dx: not bit-identical to the sequential-order oracle"
+    if res["dw"] is not None:
+        assert_dw_close(res["dw"], oracle.backward_filter(x, dy, (kh, kw), stride, padding), dt,
+                        f"{what}/dw")
+    return res
+
+
+@pytest.mark.parametrize("path", ["auto", "direct", "rows"])
+@pytest.mark.parametrize("name", case_names())
+def test_golden_cases(name, path):
+    g = golden()
+    m, t = g.cases[name], g.tensors(name)
+    dt = NP_DT[m["dtype"]]
+    st, pd = tuple(m["stride"]), tuple(m["padding"])
+    x, w, dy = (t[k].cuda() for k in ("x", "w", "dy"))
+    res = _check_three_ops(x, w, dy, st, pd, dt, path, f"{name}[{path}]")
+    # and directly against what the reference package produced for these inputs
+    if res["y"] is not None:
+        if m["dist"] == "dyadic":
+            assert torch.equal(res["y"].cpu(), t["y"])
+        else:
+            assert_close_fp(res["y"], t["y"], dt, m["kh"], m["kw"], "y vs reference")
+    if res["dx"] is not None:
+        if m["dist"] == "dyadic":
+            assert torch.equal(res["dx"].cpu(), t["dx"])
+        else:
+            assert_close_fp(res["dx"], t["dx"], dt, m["kh"], m["kw"], "dx vs reference")
+    if res["dw"] is not None:
+        if m["dist"] == "dyadic":
+            assert torch.equal(res["dw"].cpu(), t["dw"])
+        else:
+            assert_dw_close(res["dw"], t["dw"], dt, "dw vs reference")
+
+
+# (C, H, W, k, stride, pad) of test/test_forward.py:20-73 (N = 32, fp32)
+REF_FORWARD_CASES = [
+    (32, 64, 64, 3, 1, 1), (32, 64, 64, 5, 1, 2), (32, 64, 64, 3, 2, 1), (32, 64, 64, 5, 2, 2),
+    (32, 64, 64, 3, 1, 0), (32, 64, 64, 5, 1, 0), (32, 64, 64, 3, 2, 0), (32, 64, 64, 5, 2, 0),
+    (32, 63, 65, 3, 1, 1), (32, 63, 65, 5, 1, 2), (32, 63, 65, 3, 2, 1), (32, 63, 65, 5, 2, 2),
+    (128, 32, 32, 3, 1, 1), (128, 32, 32, 5, 1, 2),
+]
+
+
+@pytest.mark.parametrize("case", REF_FORWARD_CASES, ids=lambda c: "x".join(map(str, c)))
+def test_reference_forward_cases(case):
+    """The 14 forward cases of the reference's test-suite, through the public function.  The
+    reference asserts max|F.conv2d - custom| < 1e-8 on CUDA, which can only hold if both add
+    the taps in the same order; here the order is pinned against the sequential oracle (bit
+    for bit), and PyTorch's CUDA result must agree to the fp32 contract tolerance."""
+    import dwconv_b200
+    C, H, W, k, s, p = case
+    x, w, dy = seeded((32, C, H, W), (k, k), s, p, torch.float32, seed=sum(case))
+    custom = dwconv_b200.depthwise_conv2d(x, w, stride=s, padding=p)
+    native = F.conv2d(x, w, stride=s, padding=p, groups=C)
+    assert (native - custom).abs().max().item() <= 1e-5 * k * k
+    assert torch.equal(custom.cpu(), oracle.forward_seq(x, w, s, p))
+    _check_three_ops(x, w, dy, s, p, torch.float32, "auto", f"ref-forward{case}")
+
+
+# (H, W, k, stride, pad) of test/test_grad.py:44-153 (fp64 gradcheck, input and filter)
+REF_GRAD_CASES = (
+    [(34, 34, k, s, p) for (k, s, p) in [(3, 1, 1), (5, 1, 2), (3, 2, 1), (5, 2, 2), (3, 1, 0),
+                                         (5, 1, 0), (3, 2, 0), (5, 2, 0)]]
+    + [(33, 35, k, s, p) for (k, s, p) in [(3, 1, 1), (5, 1, 2), (3, 2, 1), (5, 2, 2)]]
+    + [(16, 16, 3, 1, 1), (16, 16, 5, 1, 2)])
+
+
+@pytest.mark.parametrize("wrt", ["input", "kernel"])
+@pytest.mark.parametrize("case", REF_GRAD_CASES, ids=lambda c: "x".join(map(str, c)))
+def test_reference_gradcheck_cases(case, wrt):
+    """The 28 fp64 gradcheck cases of the reference (2 x 2 planes instead of 8 x 8 to keep the
+    finite-difference sweep short; geometry unchanged).  `.sum()` hands backward an expanded,
+    stride-0 grad_output, as in the reference's tests."""
+    import dwconv_b200
+    H, W, k, s, p = case
+    g = torch.Generator().manual_seed(H * 131 + W * 17 + k * 5 + s * 3 + p)
+    x = torch.randn(2, 2, H, W, generator=g).double().cuda()
+    w = torch.randn(2, 1, k, k, generator=g).double().cuda()
+    if wrt == "input":
+        x.requires_grad_(True)
+        ok = torch.autograd.gradcheck(
+            lambda xi: dwconv_b200.depthwise_conv2d(xi, w, stride=s, padding=p).sum(), x,
+            raise_exception=False)
+    else:
+        w.requires_grad_(True)
+        ok = torch.autograd.gradcheck(
+            lambda wi: dwconv_b200.depthwise_conv2d(x, wi, stride=s, padding=p).sum(), w,
+            raise_exception=False)
+    assert ok
+
+
+def test_gradcheck_full_planes_fast_mode():
+    import dwconv_b200
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(8, 8, 34, 34, generator=g).double().cuda().requires_grad_(True)
+    w = torch.randn(8, 1, 5, 5, generator=g).double().cuda().requires_grad_(True)
+    assert torch.autograd.gradcheck(
+        lambda xi, wi: dwconv_b200.depthwise_conv2d(xi, wi, stride=2, padding=2), (x, w),
+        fast_mode=True)
+
+
+SWEEP = []
+for _dt in ("f32", "f16"):
+    for (_H, _W) in [(7, 7), (14, 14), (13, 15), (28, 28), (31, 32), (32, 32), (33, 35), (56, 56),
+                     (40, 72), (112, 112), (130, 97)]:
+        for (_k, _s, _p) in [(3, 1, 1), (3, 2, 1), (5, 1, 2), (5, 2, 2), (7, 1, 3), (3, 1, 0),
+                             (2, 2, 0), (4, 1, 1), (1, 1, 0), (6, 2, 2), (7, 2, 3)]:
+            SWEEP.append((_dt, _H, _W, _k, _s, _p))
+
+
+@pytest.mark.parametrize("path", ["auto", "rows"])
+@pytest.mark.parametrize("cfg", SWEEP, ids=lambda c: "-".join(map(str, c)))
+def test_shape_sweep(cfg, path):
+    """Map sizes either side of every tiling boundary x filter / stride / padding classes,
+    several planes per channel so that plane grouping and ragged tails are exercised."""
+    dtn, H, W, k, s, p = cfg
+    dt = NP_DT[dtn]
+    N, C = 5, 3
+    x, w, dy = seeded((N, C, H, W), (k, k), s, p, dt, seed=H * 1000 + W * 10 + k + s + p)
+    _check_three_ops(x, w, dy, s, p, dt, path, f"sweep{cfg}[{path}]")
+
+
+@pytest.mark.parametrize("cfg", [
+    (2, 3, 12, 13, 3, 5, (1, 1), (1, 2)), (2, 3, 20, 9, 5, 3, (2, 1), (2, 1)),
+    (1, 2, 15, 14, 3, 3, (2, 1), (0, 1)), (3, 2, 9, 40, 1, 7, (1, 2), (0, 3)),
+    (2, 2, 5, 5, 7, 7, (1, 1), (3, 3)), (1, 2, 17, 19, 3, 3, (3, 3), (1, 1)),
+    (2, 2, 30, 30, 13, 13, (1, 1), (6, 6)), (1, 2, 32, 32, 31, 31, (1, 1), (15, 15)),
+    (1, 1, 6, 6, 3, 3, (1, 1), (3, 3)), (3, 2, 1, 1, 3, 3, (1, 1), (1, 1)),
+    (1, 3, 50, 50, 9, 9, (4, 4), (4, 4)),
+], ids=lambda c: "x".join(map(str, c[:6])))
+@pytest.mark.parametrize("dtn", ["f32", "f16", "f64"])
+def test_irregular_geometries(cfg, dtn):
+    """Rectangular filters, mixed strides and paddings, filters larger than the map, stride 3+:
+    shapes on which the reference has no kernel (dwconv_kernel.cu:808-845) or goes to PyTorch."""
+    N, C, H, W, kh, kw, st, pd = cfg
+    dt = NP_DT[dtn]
+    x, w, dy = seeded((N, C, H, W), (kh, kw), st, pd, dt, seed=kh * 7 + kw)
+    for path in ("auto", "direct"):
+        _check_three_ops(x, w, dy, st, pd, dt, path, f"irregular{cfg[:6]}[{path}]")
+
+
+def test_backward_filter_is_deterministic():
+    for (shape, k, s, p) in [((16, 24, 14, 14), 3, 1, 1), ((4, 8, 56, 56), 5, 2, 2),
+                             ((8, 6, 28, 28), 7, 1, 3)]:
+        x, w, dy = seeded(shape, (k, k), s, p, torch.float32, seed=11)
+        first = None
+        for _ in range(3):
+            st, dw = c_backward_filter(x, dy, (k, k), s, p)
+            assert st == 0
+            if first is None:
+                first = dw.clone()
+            assert torch.equal(first, dw)
+
+
+def test_misaligned_views_are_served():
+    """Tensors whose storage offset breaks 16-byte alignment (a slice of a larger buffer)
+    must still be computed correctly, through whichever kernel accepts them."""
+    N, C, H, W, k = 3, 4, 14, 14, 3
+    x, w, dy = seeded((N, C, H, W), (k, k), 1, 1, torch.float32, seed=5)
+    buf = torch.zeros(x.numel() + 3, device="cuda")
+    xo = buf[1:1 + x.numel()].view_as(x).copy_(x)
+    bufd = torch.zeros(dy.numel() + 3, device="cuda")
+    dyo = bufd[3:3 + dy.numel()].view_as(dy).copy_(dy)
+    assert xo.data_ptr() % 16 != 0 and dyo.data_ptr() % 16 != 0
+    _check_three_ops(xo, w, dyo, 1, 1, torch.float32, "auto", "misaligned")
+
+
+def test_operator_form_entry_points():
+    """dwconv2d / dwconv2d_small / dwconv2d_backward_kernel with the argument lists the
+    reference's autograd function uses (dwconv.py:28-35,57-68)."""
+    import dwconv_b200
+    C_ = dwconv_b200._C
+    for (H, W, k, s, p) in [(40, 44, 3, 2, 1), (14, 14, 3, 1, 1), (37, 41, 5, 2, 2)]:
+        x, w, dy = seeded((2, 3, H, W), (k, k), s, p, torch.float32, seed=H)
+        y = C_.dwconv2d(x, w, 1, 1, s, s, p, p, p, p, True)
+        assert torch.equal(y.cpu(), oracle.forward_seq(x, w, s, p))
+        gp = oracle.g_pad((H, W), tuple(y.shape[2:]), (k, k), (s, s), (p, p))
+        dx = C_.dwconv2d(dy, w, s, s, 1, 1, *gp, False)
+        assert torch.equal(dx.cpu(), oracle.backward_input_seq(dy, w, (H, W), s, p))
+        dw = C_.dwconv2d_backward_kernel(x, dy, w, 1, 1, s, s, p, p)
+        assert_dw_close(dw, oracle.backward_filter(x, dy, (k, k), s, p), torch.float32)
+        if s == 1:
+            ys = C_.dwconv2d_small(x, w, 1, 1, 1, 1, p, p, True)
+            assert torch.equal(ys, y)
+            dxs = C_.dwconv2d_small(dy, w, 1, 1, 1, 1, gp[0], gp[2], False)
+            assert torch.equal(dxs, dx)
+
+
+def test_autograd_matches_pytorch_autograd():
+    import dwconv_b200
+    for dt, (N, C, H, W, k, s, p) in [(torch.float32, (4, 6, 28, 28, 3, 2, 1)),
+                                      (torch.float32, (2, 5, 56, 56, 5, 1, 2)),
+                                      (torch.float16, (2, 4, 28, 28, 7, 1, 3)),
+                                      (torch.float64, (2, 3, 19, 23, 3, 1, 1))]:
+        x, w, dy = seeded((N, C, H, W), (k, k), s, p, dt, seed=k)
+        xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        xb, wb = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        ya = dwconv_b200.depthwise_conv2d(xa, wa, None, s, p)
+        ya.backward(dy)
+        yb = F.conv2d(xb, wb, stride=s, padding=p, groups=C)
+        yb.backward(dy)
+        assert_close_fp(ya, oracle.forward(x, w, s, p), dt, k, k, "y")
+        assert_close_fp(xa.grad, oracle.backward_input(dy, w, (H, W), s, p), dt, k, k, "dx")
+        assert_dw_close(wa.grad, oracle.backward_filter(x, dy, (k, k), s, p), dt, "dw")
+        assert xa.grad.dtype == dt and wa.grad.dtype == dt
+        tol = {torch.float32: 1e-4, torch.float16: 3e-2, torch.float64: 1e-9}[dt]
+        assert (ya - yb).abs().max().item() <= tol * max(1.0, yb.abs().max().item())
+        assert (xa.grad - xb.grad).abs().max().item() <= tol * max(1.0, xb.grad.abs().max().item())
+        assert (wa.grad - wb.grad).abs().max().item() <= tol * max(1.0, wb.grad.abs().max().item())
+
+
+def test_autograd_only_computes_requested_gradients():
+    import dwconv_b200
+    x, w, dy = seeded((2, 3, 14, 14), (3, 3), 1, 1, torch.float32, seed=1)
+    xr = x.clone().requires_grad_(True)
+    dwconv_b200.depthwise_conv2d(xr, w, padding=1).backward(dy)
+    assert xr.grad is not None
+    wr = w.clone().requires_grad_(True)
+    dwconv_b200.depthwise_conv2d(x, wr, padding=1).backward(dy)
+    assert wr.grad is not None and x.grad is None
+
+
+def test_non_contiguous_inputs_and_module():
+    import dwconv_b200
+    x, w, dy = seeded((2, 4, 20, 24), (3, 3), 1, 1, torch.float32, seed=2)
+    xt = x.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)  # same values, transposed strides
+    assert not xt.is_contiguous()
+    y = dwconv_b200.depthwise_conv2d(xt, w, padding=1)
+    assert torch.equal(y.cpu(), oracle.forward_seq(x, w, 1, 1))
+    mod = dwconv_b200.DepthwiseConv2d(4, 4, 3, padding=1).cuda()
+    with torch.no_grad():
+        mod.weight.copy_(w)
+    assert torch.equal(mod(x), y)
+    mod.custom = False
+    assert (mod(x) - y).abs().max().item() <= 1e-5 * 9
+
+
+def test_other_stream_and_device_guard():
+    import dwconv_b200
+    x, w, dy = seeded((2, 4, 30, 30), (3, 3), 1, 1, torch.float32, seed=9)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        y = dwconv_b200.depthwise_conv2d(x, w, padding=1)
+    side.synchronize()
+    assert torch.equal(y.cpu(), oracle.forward_seq(x, w, 1, 1))
