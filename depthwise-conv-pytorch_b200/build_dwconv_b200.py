@@ -1,16 +1,18 @@
 """Compile ``csrc/*.cu`` into ``lib/libdwconv_b200.so`` with plain ``nvcc`` for sm_100a.
 
-    python -m dwconv_b200.build [--force] [--verbose]
+    python depthwise-conv-pytorch_b200/build_dwconv_b200.py [--force] [--verbose]
 
 The shared library has no torch dependency; it is loaded with ``ctypes``
-(``dwconv_b200._lib``).  nvcc cross-compiles without a GPU.
+(``dwconv_b200._lib``).  nvcc cross-compiles without a GPU.  This module sits outside
+the ``dwconv_b200`` package on purpose: importing the package loads the library, and the
+build must be able to run when the library is missing or stale.
 """
 import glob
 import os
 import subprocess
 import sys
 
-PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG_ROOT = os.path.dirname(os.path.abspath(__file__))
 REPO_ROOT = os.path.dirname(PKG_ROOT)
 CSRC = os.path.join(PKG_ROOT, "csrc")
 LIB_DIR = os.path.join(PKG_ROOT, "lib")

@@ -32,7 +32,7 @@ def pytest_collection_modifyitems(config, items):
 @pytest.fixture(scope="session", autouse=True)
 def _built_library():
     """The shared library is built from source once per session (nvcc needs no GPU)."""
-    from dwconv_b200.build import build_library
+    from build_dwconv_b200 import build_library
     build_library()
 
 
