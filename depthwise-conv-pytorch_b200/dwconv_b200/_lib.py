@@ -5,7 +5,9 @@ There is no fallback: if the library is missing, importing this module raises.
 import ctypes
 import os
 
-from .build import LIB_PATH
+LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib",
+                        "libdwconv_b200.so")
+_BUILD_HINT = "python depthwise-conv-pytorch_b200/build_dwconv_b200.py"
 
 F32, F16, F64 = 0, 1, 2
 PATH_AUTO, PATH_DIRECT, PATH_ROWS = 0, 1, 2
@@ -22,7 +24,7 @@ def _load():
     path = os.environ.get("DWCONV_B200_LIB", LIB_PATH)
     if not os.path.exists(path):
         raise RuntimeError(
-            f"dwconv_b200: {path} not found. Build it with `python -m dwconv_b200.build` "
+            f"dwconv_b200: {path} not found. Build it with `{_BUILD_HINT}` "
             "(needs nvcc); there is no CPU or PyTorch fallback.")
     lib = ctypes.CDLL(path)
     vp, ci, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
@@ -42,9 +44,15 @@ def _load():
         "dwconv_b200_dwconv2d": (ci, [vp, vp, vp, ci] + [ci] * 15 + [vp]),
         "dwconv_b200_dwconv2d_small": (ci, [vp, vp, vp, ci] + [ci] * 13 + [vp]),
         "dwconv_b200_dwconv2d_backward_kernel": (ci, [vp, vp, vp, vp, sz, ci] + [ci] * 14 + [vp]),
+        "dwconv_b200_static_scratch_bytes": (sz, []),
+        "dwconv_b200_backward_filter_static": (ci, [vp, vp, vp, ci, sp, vp]),
     }
     for name, (res, args) in sig.items():
-        fn = getattr(lib, name)
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            raise RuntimeError(f"dwconv_b200: {path} is stale (no symbol {name}); rebuild it with "
+                               f"`{_BUILD_HINT}`") from None
         fn.restype = res
         fn.argtypes = args
     return lib
@@ -57,7 +65,8 @@ EXPORTS = (
     "dwconv_b200_forward", "dwconv_b200_backward_input",
     "dwconv_b200_backward_filter_workspace_bytes", "dwconv_b200_backward_filter",
     "dwconv_b200_use_dwconv2d_small", "dwconv_b200_dwconv2d", "dwconv_b200_dwconv2d_small",
-    "dwconv_b200_dwconv2d_backward_kernel",
+    "dwconv_b200_dwconv2d_backward_kernel", "dwconv_b200_static_scratch_bytes",
+    "dwconv_b200_backward_filter_static",
 )
 
 

@@ -160,6 +160,43 @@ DWCONV_B200_API int dwconv_b200_dwconv2d_backward_kernel(const void *input, cons
                                          int kh, int kw, int up_h, int up_w, int down_h,
                                          int down_w, int pad_h, int pad_w, void *stream);
 
+/* ------------------------------------------------------------------------
+ * Entry point for callers that must not allocate.  It has no counterpart in
+ * the reference (whose operators allocate their results and scratch through
+ * PyTorch); it exists for hosts that cannot call cudaMalloc on the path where
+ * they need the filter gradient: code running under a fixed device-memory
+ * budget handed out at start-up, real-time loops that may not block on the
+ * allocator, and plugins whose host owns all device memory.
+ *
+ * Same result as dwconv_b200_backward_filter, but the partial sums of the
+ * two-pass reduction live in a fixed array inside the library's device image
+ * instead of a caller-supplied workspace.  The array is
+ * DWCONV_B200_STATIC_SCRATCH_BYTES long; every GPU that loads the library
+ * holds one copy until the process exits.  The call allocates nothing (no
+ * cudaMalloc / cudaFree, no allocating library routine) and never synchronises.
+ *
+ *   - Limit: C * slices * kh * kw accumulators (4 bytes each, 8 for fp64) must
+ *     fit the array; the batch split `slices` is reduced down to 1 to make it
+ *     fit, and a geometry that still does not fit (C*kh*kw*4 > the array) is
+ *     rejected with DWCONV_B200_TOO_LARGE before anything is launched.
+ *   - The first call on each device looks up the array's device address (once
+ *     per device, with that device current).  Make that first call outside any
+ *     CUDA stream capture.
+ *   - Every call on a device shares the one array.  Nothing in it needs to
+ *     start at zero (each partial sum is written before it is read), so stale
+ *     contents from an earlier call are harmless; but two calls whose kernels
+ *     overlap on the GPU (different streams, or different host threads on
+ *     different streams) race on it.  Serialise them on one stream or with
+ *     events.
+ * ---------------------------------------------------------------------- */
+#define DWCONV_B200_STATIC_SCRATCH_BYTES (4u << 20)
+
+DWCONV_B200_API size_t dwconv_b200_static_scratch_bytes(void);
+
+DWCONV_B200_API int dwconv_b200_backward_filter_static(const void *x, const void *dy, void *dw,
+                                                       int dtype, const dwconv_b200_shape *shape,
+                                                       void *stream);
+
 #ifdef __cplusplus
 }
 #endif
