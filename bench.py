@@ -373,15 +373,15 @@ def gpu_arm(args, layers):
             outs[1].copy_(x.grad, non_blocking=True)
             outs[2].copy_(dw, non_blocking=True)
 
-    e2e_steps = max(3, min(args.steps, 20))
-    for _ in range(3):
+    e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 20))
+    for _ in range(3 if e2e_steps else 0):
         e2e_step()
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         e2e_step()
     torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    e2e_s = (time.perf_counter() - t0) / max(e2e_steps, 1) if e2e_steps else float("inf")
     if world > 1:
         t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -452,6 +452,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     args = ap.parse_args()
     layers = [list(l) for l in WORKLOADS[args.workload]]

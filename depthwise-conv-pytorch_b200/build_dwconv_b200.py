@@ -21,8 +21,9 @@ INCLUDE = os.path.join(REPO_ROOT, "include")
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-    "-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
 ]
+OBJ_DIR = os.path.join(PKG_ROOT, "build")
 
 
 def _sources():
@@ -41,21 +42,47 @@ def is_stale():
     return any(os.path.getmtime(f) > t for f in _deps())
 
 
+def _compile_one(nvcc, src, verbose):
+    obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
+    newest = max(os.path.getmtime(f) for f in [src] + glob.glob(os.path.join(CSRC, "*.cuh"))
+                 + glob.glob(os.path.join(INCLUDE, "*.h")))
+    if os.path.exists(obj) and os.path.getmtime(obj) >= newest:
+        return obj, ""
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
+        "-I", INCLUDE, "-I", CSRC, "-c", "-o", obj, src]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed on {os.path.basename(src)}:\n{res.stdout}{res.stderr}")
+    return obj, res.stdout + res.stderr
+
+
 def build_library(force=False, verbose=False):
-    """Build the library if a source is newer than it; returns its path."""
+    """Build the library if a source is newer than it; returns its path.
+
+    Each ``.cu`` is compiled to an object in parallel (they are independent translation
+    units), then linked into one shared library with the static CUDA runtime.
+    """
     if not force and not is_stale():
         return LIB_PATH
+    from concurrent.futures import ThreadPoolExecutor
     nvcc = os.environ.get("NVCC") or os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"),
                                                   "bin", "nvcc")
     os.makedirs(LIB_DIR, exist_ok=True)
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    if force:
+        for f in glob.glob(os.path.join(OBJ_DIR, "*.o")):
+            os.remove(f)
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        results = list(pool.map(lambda src: _compile_one(nvcc, src, verbose), _sources()))
+    if verbose:
+        sys.stderr.write("".join(log for _, log in results))
     tmp = LIB_PATH + ".tmp"
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
-        "-I", INCLUDE, "-I", CSRC, "-o", tmp] + _sources()
+    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
+           "-o", tmp] + [obj for obj, _ in results]
     res = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or res.returncode != 0:
-        sys.stderr.write(res.stdout + res.stderr)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed building libdwconv_b200.so")
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed linking libdwconv_b200.so")
     os.replace(tmp, LIB_PATH)
     return LIB_PATH
 

@@ -6,7 +6,7 @@
 
 #include "common.cuh"
 #include "direct_kernels.cuh"
-#include "rows_engine.cuh"
+#include "rows_api.cuh"
 
 using namespace dwb;
 
@@ -178,6 +178,14 @@ int dwconv_b200_set_path(int path) {
 }
 
 int dwconv_b200_last_path(void) { return t_last_path; }
+
+int dwconv_b200_device_status(void) {
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    t_last_cuda_error = (int)cudaGetLastError();
+    return -1;
+  }
+  return rows_take_device_error();
+}
 
 int dwconv_b200_out_size(int in, int up, int pad0, int pad1, int k, int down) {
   if (down <= 0) return 0;

@@ -1,0 +1,27 @@
+// Host entry points of the rows kernel family (defined in rows_conv.cu / rows_filter.cu).
+// Each returns ROWS_SERVED after enqueueing its kernel, or ROWS_DECLINED without launching
+// anything when the geometry, dtype or alignment is outside what the family covers.
+#pragma once
+
+#include "common.cuh"
+
+namespace dwb {
+
+enum { ROWS_DECLINED = 0, ROWS_SERVED = 1 };
+
+template <typename T> int rows_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st);
+template <typename T>
+int rows_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStream_t st);
+// Batch/row slices per channel the first pass would use (0: declines); sizes the workspace.
+template <typename T> int rows_backward_filter_slices(const Shape &s);
+template <typename T>
+int rows_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *partial, const Shape &s,
+                         cudaStream_t st, int *slices_out);
+
+// Reads and clears the flags kernels raise when a bounded wait expires (synchronises the
+// device).  Bit 0: forward/backward-input kernels, bit 1: backward-filter kernels.
+int rows_take_device_error();
+int rows_conv_take_error();
+int rows_filter_take_error();
+
+}  // namespace dwb

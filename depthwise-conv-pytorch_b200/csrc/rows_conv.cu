@@ -1,0 +1,151 @@
+// Rows family, forward and backward-input: variant selection and launches.
+#include "rows_plan.cuh"
+
+namespace dwb {
+
+namespace {
+
+__device__ int g_conv_error_flag;
+
+template <typename T> struct RowsDtype { static constexpr bool ok = false; };
+template <> struct RowsDtype<float> { static constexpr bool ok = true; };
+template <> struct RowsDtype<__half> { static constexpr bool ok = true; };
+
+constexpr int conv_u(int K, int S, int mode) {
+  return mode == MODE_FWD ? (S == 1 ? (K <= 5 ? 4 : 2) : 2) : (K <= 5 ? 4 : 2);
+}
+constexpr int conv_minb(int K) { return K <= 5 ? 2 : 1; }
+
+template <typename T, int K, int S, int MODE, int VI, int VO>
+int launch_conv(RowsParams p, cudaStream_t st) {
+  constexpr int U = conv_u(K, S, MODE);
+  constexpr int MINB = conv_minb(K);
+  const int lanes = max(ceil_div(p.Win, VI), ceil_div(p.Wout, VO));
+  p.LW = pick_lw(lanes);
+  if (p.LW == 0) return ROWS_DECLINED;
+  const int NSEG = ROWS_WARPS * (32 / p.LW);
+  TilePlan t;
+  if (!plan_tiles(t, K, S, MODE, U, p.Hin, p.Hout, p.Win * (int)sizeof(T), 0, NSEG,
+                  ROWS_STAGE_BYTES))
+    return ROWS_DECLINED;
+  p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;
+  const long long ntiles = (long long)ceil_div(p.NC, p.G) * p.NRT;
+  if (ntiles > (1ll << 30)) return ROWS_DECLINED;
+  p.ntiles = (int)ntiles;
+  auto kernel = rows_conv_kernel<T, K, S, MODE, VI, VO, U, MINB>;
+  static std::atomic<unsigned long long> smem_done{0};
+  if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
+  int *flag = nullptr;
+  if (cudaGetSymbolAddress((void **)&flag, g_conv_error_flag) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return ROWS_DECLINED;
+  }
+  const int grid = (int)min((long long)sm_count() * MINB, ntiles);
+  kernel<<<grid, ROWS_THREADS, ROWS_SMEM_BYTES, st>>>(p, flag);
+  return ROWS_SERVED;
+}
+
+// Picks the widest per-lane vector the widths and pointers allow.
+template <typename T, int K, int S, int MODE>
+int select_conv(const RowsParams &p, cudaStream_t st) {
+  const bool a16 = ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(p.out)) & 15) == 0;
+  if (S == 1) {
+    if (a16 && p.Win % 4 == 0 && p.Wout % 4 == 0 && p.Win <= 128 && p.Wout <= 128 && p.Win > 16)
+      return launch_conv<T, K, 1, MODE_FWD, 4, 4>(p, st);
+    if (a16 && p.Win % 2 == 0 && p.Wout % 2 == 0 && p.Win <= 64 && p.Wout <= 64 && p.Win > 8)
+      return launch_conv<T, K, 1, MODE_FWD, 2, 2>(p, st);
+    if (p.Win <= 32 && p.Wout <= 32) return launch_conv<T, K, 1, MODE_FWD, 1, 1>(p, st);
+    return ROWS_DECLINED;
+  }
+  if (MODE == MODE_FWD) {
+    if (a16 && p.Win % 4 == 0 && p.Wout % 2 == 0 && p.Win <= 128 && p.Wout <= 64 && p.Win > 16)
+      return launch_conv<T, K, 2, MODE_FWD, 4, 2>(p, st);
+    if (a16 && p.Win % 2 == 0 && p.Win <= 64 && p.Wout <= 32)
+      return launch_conv<T, K, 2, MODE_FWD, 2, 1>(p, st);
+    return ROWS_DECLINED;
+  }
+  if (a16 && p.Win % 2 == 0 && p.Wout % 4 == 0 && p.Win <= 64 && p.Wout <= 128 && p.Wout > 16)
+    return launch_conv<T, K, 2, MODE_BWD, 2, 4>(p, st);
+  if (a16 && p.Wout % 2 == 0 && p.Win <= 32 && p.Wout <= 64)
+    return launch_conv<T, K, 2, MODE_BWD, 1, 2>(p, st);
+  return ROWS_DECLINED;
+}
+
+template <typename T, int MODE>
+int select_k(const RowsParams &p, int K, int S, cudaStream_t st) {
+  switch (K * 10 + S) {
+    case 31: return select_conv<T, 3, 1, MODE_FWD>(p, st);
+    case 51: return select_conv<T, 5, 1, MODE_FWD>(p, st);
+    case 71: return select_conv<T, 7, 1, MODE_FWD>(p, st);
+    case 32: return select_conv<T, 3, 2, MODE>(p, st);
+    case 52: return select_conv<T, 5, 2, MODE>(p, st);
+    case 72: return select_conv<T, 7, 2, MODE>(p, st);
+    default: return ROWS_DECLINED;
+  }
+}
+
+// The family covers square odd filters 3/5/7, equal strides 1 or 2, padding k/2, and the
+// output extent that padding implies.
+inline bool conv_shape_ok(const Shape &s) {
+  if (s.kh != s.kw || (s.kh != 3 && s.kh != 5 && s.kh != 7)) return false;
+  if (s.sh != s.sw || (s.sh != 1 && s.sh != 2)) return false;
+  if (s.ph != s.kh / 2 || s.pw != s.kw / 2) return false;
+  if (s.Ho != (s.H + 2 * s.ph - s.kh) / s.sh + 1 || s.Wo != (s.W + 2 * s.pw - s.kw) / s.sw + 1)
+    return false;
+  return true;
+}
+
+}  // namespace
+
+template <typename T>
+int rows_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st) {
+  if constexpr (!RowsDtype<T>::ok) {
+    return ROWS_DECLINED;
+  } else {
+    if (!conv_shape_ok(s)) return ROWS_DECLINED;
+    RowsParams p{};
+    p.in = x; p.w = w; p.out = y;
+    p.NC = s.N * s.C; p.C = s.C;
+    p.Hin = s.H; p.Win = s.W; p.Hout = s.Ho; p.Wout = s.Wo;
+    p.flip = 0;
+    return select_k<T, MODE_FWD>(p, s.kh, s.sh, st);
+  }
+}
+
+template <typename T>
+int rows_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStream_t st) {
+  if constexpr (!RowsDtype<T>::ok) {
+    return ROWS_DECLINED;
+  } else {
+    if (!conv_shape_ok(s)) return ROWS_DECLINED;
+    RowsParams p{};
+    p.in = dy; p.w = w; p.out = dx;
+    p.NC = s.N * s.C; p.C = s.C;
+    p.Hin = s.Ho; p.Win = s.Wo; p.Hout = s.H; p.Wout = s.W;
+    p.flip = 1;
+    // stride 1: the transposed operation is the same correlation with the flipped filter
+    return select_k<T, MODE_BWD>(p, s.kh, s.sh, st);
+  }
+}
+
+int rows_conv_take_error() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_conv_error_flag, sizeof(int)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  if (v) {
+    const int zero = 0;
+    (void)cudaMemcpyToSymbol(g_conv_error_flag, &zero, sizeof(int));
+  }
+  return v;
+}
+
+template int rows_forward<float>(const float *, const float *, float *, const Shape &, cudaStream_t);
+template int rows_forward<__half>(const __half *, const __half *, __half *, const Shape &, cudaStream_t);
+template int rows_forward<double>(const double *, const double *, double *, const Shape &, cudaStream_t);
+template int rows_backward_input<float>(const float *, const float *, float *, const Shape &, cudaStream_t);
+template int rows_backward_input<__half>(const __half *, const __half *, __half *, const Shape &, cudaStream_t);
+template int rows_backward_input<double>(const double *, const double *, double *, const Shape &, cudaStream_t);
+
+}  // namespace dwb

@@ -86,6 +86,13 @@ DWCONV_B200_API const char *dwconv_b200_status_string(int status);
 /* cudaError_t of the most recent failed launch on the calling thread (0 if none). */
 DWCONV_B200_API int dwconv_b200_last_cuda_error(void);
 
+/* Every wait inside a kernel (on a bulk copy landing in shared memory) is bounded; a kernel
+ * whose wait expires raises a flag, finishes without hanging and leaves wrong output.
+ * This call synchronises the device, returns the flags raised since the last call (0 = none;
+ * bit 0 forward/backward-input kernels, bit 1 backward-filter kernels) and clears them.
+ * Diagnostic: not needed on the hot path.  No counterpart in the reference. */
+DWCONV_B200_API int dwconv_b200_device_status(void);
+
 /* Force a kernel family (testing / profiling).  Process-wide; returns the previous value. */
 DWCONV_B200_API int dwconv_b200_set_path(int path);
 /* Kernel family that served the calling thread's most recent call. */
