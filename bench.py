@@ -43,6 +43,10 @@ WORKLOADS = {
            (128, 144, 56, 5, 2, 2, "f32"), (128, 240, 28, 3, 2, 1, "f32"),
            (128, 480, 14, 5, 1, 2, "f32"), (128, 672, 14, 5, 2, 2, "f32"),
            (128, 1152, 7, 3, 1, 1, "f32")],
+    "c3a": [(128, 32, 112, 3, 1, 1, "f32")], "c3b": [(128, 96, 112, 3, 2, 1, "f32")],
+    "c3c": [(128, 144, 56, 5, 2, 2, "f32")], "c3d": [(128, 240, 28, 3, 2, 1, "f32")],
+    "c3e": [(128, 480, 14, 5, 1, 2, "f32")], "c3f": [(128, 672, 14, 5, 2, 2, "f32")],
+    "c3g": [(128, 1152, 7, 3, 1, 1, "f32")],
     "c4a": [(64, 96, 56, 7, 1, 3, "f16")],
     "c4b": [(64, 192, 28, 7, 1, 3, "f16")],
     "c5k3": [(32, 256, 32, 3, 1, 1, "f32")],

@@ -179,6 +179,15 @@ int dwconv_b200_set_path(int path) {
 
 int dwconv_b200_last_path(void) { return t_last_path; }
 
+int dwconv_b200_debug_plan(int op, int dtype, const dwconv_b200_shape *shape, int aligned16,
+                           int *out24) {
+  if (shape == nullptr || out24 == nullptr || check_shape(shape) != DWCONV_B200_OK) return 0;
+  const int es = (int)elem_size(dtype);
+  if (es != 4 && es != 2) return 0;
+  if (op == 2) return rows_debug_filter_plan(es, *shape, aligned16, out24);
+  return rows_debug_conv_plan(op, es, *shape, aligned16, out24);
+}
+
 int dwconv_b200_device_status(void) {
   if (cudaDeviceSynchronize() != cudaSuccess) {
     t_last_cuda_error = (int)cudaGetLastError();

@@ -21,6 +21,10 @@ int rows_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *parti
 // Reads and clears the flags kernels raise when a bounded wait expires (synchronises the
 // device).  Bit 0: forward/backward-input kernels, bit 1: backward-filter kernels.
 int rows_take_device_error();
+// Variant and tiling a call would use, as 24 ints (0 returned: the family declines):
+// VI, VO, U, mask, LW, G, NRT, TH, NRB, RBH, PS, ZT, ZBF, TAPB, DPL, DYOFF, ntiles|TPC, SL, mode.
+int rows_debug_conv_plan(int op, int esize, const Shape &s, int a16, int *out);
+int rows_debug_filter_plan(int esize, const Shape &s, int a16, int *out);
 int rows_conv_take_error();
 int rows_filter_take_error();
 

@@ -7,42 +7,90 @@ namespace {
 
 __device__ int g_conv_error_flag;
 
+// When set (rows_debug_conv_plan), the selected variant and tiling are written here and
+// nothing is launched.
+thread_local int *t_plan_out = nullptr;
+
 template <typename T> struct RowsDtype { static constexpr bool ok = false; };
 template <> struct RowsDtype<float> { static constexpr bool ok = true; };
 template <> struct RowsDtype<__half> { static constexpr bool ok = true; };
 
-constexpr int conv_u(int K, int S, int mode) {
-  return mode == MODE_FWD ? (S == 1 ? (K <= 5 ? 4 : 2) : 2) : (K <= 5 ? 4 : 2);
-}
 constexpr int conv_minb(int K) { return K <= 5 ? 2 : 1; }
+
+// Rows-per-chunk choices compiled for each (K, S, MODE); the planner picks per shape.
+template <int K, int S, int MODE> struct ConvU;
+template <> struct ConvU<3, 1, MODE_FWD> { static constexpr int n = 2; static constexpr int v[2] = {4, 7}; };
+template <> struct ConvU<5, 1, MODE_FWD> { static constexpr int n = 2; static constexpr int v[2] = {4, 7}; };
+template <> struct ConvU<7, 1, MODE_FWD> { static constexpr int n = 1; static constexpr int v[2] = {2, 2}; };
+template <> struct ConvU<3, 2, MODE_FWD> { static constexpr int n = 2; static constexpr int v[2] = {2, 7}; };
+template <> struct ConvU<5, 2, MODE_FWD> { static constexpr int n = 2; static constexpr int v[2] = {2, 4}; };
+template <> struct ConvU<7, 2, MODE_FWD> { static constexpr int n = 1; static constexpr int v[2] = {2, 2}; };
+template <> struct ConvU<3, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[2] = {4, 14}; };
+template <> struct ConvU<5, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[2] = {4, 14}; };
+template <> struct ConvU<7, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[2] = {2, 4}; };
+
+int *conv_flag_address() {
+  static std::atomic<int *> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  int *p = cached[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    if (cudaGetSymbolAddress((void **)&p, g_conv_error_flag) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    cached[dev].store(p, std::memory_order_release);
+  }
+  return p;
+}
+
+template <typename T, int K, int S, int MODE, int VI, int VO, int U, bool MASK>
+int launch_variant(const RowsParams &p, cudaStream_t st) {
+  constexpr int MINB = conv_minb(K);
+  auto kernel = rows_conv_kernel<T, K, S, MODE, VI, VO, U, MASK, MINB>;
+  static std::atomic<unsigned long long> smem_done{0};
+  if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
+  int *flag = conv_flag_address();
+  if (flag == nullptr) return ROWS_DECLINED;
+  const int grid = (int)min((long long)sm_count() * MINB, (long long)p.ntiles);
+  kernel<<<grid, ROWS_THREADS, ROWS_SMEM_BYTES, st>>>(p, flag);
+  return ROWS_SERVED;
+}
 
 template <typename T, int K, int S, int MODE, int VI, int VO>
 int launch_conv(RowsParams p, cudaStream_t st) {
-  constexpr int U = conv_u(K, S, MODE);
-  constexpr int MINB = conv_minb(K);
-  const int lanes = max(ceil_div(p.Win, VI), ceil_div(p.Wout, VO));
+  using Geo = RowsGeo<K, S, MODE, VI, VO, ConvU<K, S, MODE>::v[0]>;  // column geometry: U-independent
+  const int lanes_in = ceil_div(p.Win, VI);
+  const int lanes = max(lanes_in, ceil_div(p.Wout, VO));
   p.LW = pick_lw(lanes);
   if (p.LW == 0) return ROWS_DECLINED;
-  const int NSEG = ROWS_WARPS * (32 / p.LW);
-  TilePlan t;
-  if (!plan_tiles(t, K, S, MODE, U, p.Hin, p.Hout, p.Win * (int)sizeof(T), 0, NSEG,
-                  ROWS_STAGE_BYTES))
-    return ROWS_DECLINED;
+  PlanInput in{K, S, MODE, p.Hin, p.Win, p.Hout, p.Wout, (int)sizeof(T),
+               ROWS_CWARPS * (32 / p.LW), true, false};
+  const TilePlan t = plan_best(in, ConvU<K, S, MODE>::v, ConvU<K, S, MODE>::n);
+  if (!t.ok) return ROWS_DECLINED;
   p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;
+  p.PS = t.PS; p.ZT = t.ZT; p.ZBF = t.ZBF; p.TAPB = t.TAPB;
   const long long ntiles = (long long)ceil_div(p.NC, p.G) * p.NRT;
   if (ntiles > (1ll << 30)) return ROWS_DECLINED;
   p.ntiles = (int)ntiles;
-  auto kernel = rows_conv_kernel<T, K, S, MODE, VI, VO, U, MINB>;
-  static std::atomic<unsigned long long> smem_done{0};
-  if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
-  int *flag = nullptr;
-  if (cudaGetSymbolAddress((void **)&flag, g_conv_error_flag) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return ROWS_DECLINED;
+  // halo columns reach this many lanes to either side; spare (zero) lanes at the end of each
+  // segment make explicit masking unnecessary
+  constexpr int halo_lanes = (-Geo::fdiv(Geo::CMIN, VI) > Geo::fdiv(Geo::CMAX, VI))
+                                 ? -Geo::fdiv(Geo::CMIN, VI)
+                                 : Geo::fdiv(Geo::CMAX, VI);
+  const bool mask = (p.LW - lanes_in) < halo_lanes;
+  if (t_plan_out != nullptr) {
+    const int v[24] = {VI, VO, t.U, mask ? 1 : 0, p.LW, p.G, p.NRT, p.TH, p.NRB, p.RBH, p.PS, p.ZT,
+                       p.ZBF, p.TAPB, 0, 0, p.ntiles, 0, MODE, 0, 0, 0, 0, 0};
+    for (int i = 0; i < 24; ++i) t_plan_out[i] = v[i];
+    return ROWS_SERVED;
   }
-  const int grid = (int)min((long long)sm_count() * MINB, ntiles);
-  kernel<<<grid, ROWS_THREADS, ROWS_SMEM_BYTES, st>>>(p, flag);
-  return ROWS_SERVED;
+  constexpr int U0 = ConvU<K, S, MODE>::v[0], U1 = ConvU<K, S, MODE>::v[1];
+  if (t.U == U0)
+    return mask ? launch_variant<T, K, S, MODE, VI, VO, U0, true>(p, st)
+                : launch_variant<T, K, S, MODE, VI, VO, U0, false>(p, st);
+  return mask ? launch_variant<T, K, S, MODE, VI, VO, U1, true>(p, st)
+              : launch_variant<T, K, S, MODE, VI, VO, U1, false>(p, st);
 }
 
 // Picks the widest per-lane vector the widths and pointers allow.
@@ -126,6 +174,23 @@ int rows_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStre
     // stride 1: the transposed operation is the same correlation with the flipped filter
     return select_k<T, MODE_BWD>(p, s.kh, s.sh, st);
   }
+}
+
+// Variant and tiling forward (op 0) or backward-input (op 1) would use, for inspection: the
+// test-suite models the kernels' index arithmetic on the CPU from these numbers.
+int rows_debug_conv_plan(int op, int esize, const Shape &s, int a16, int *out) {
+  // only alignment matters for selection; the pointers are never dereferenced
+  const void *fake = reinterpret_cast<const void *>(a16 ? (uintptr_t)0x1000 : (uintptr_t)0x1004);
+  t_plan_out = out;
+  int r = ROWS_DECLINED;
+  if (esize == 4)
+    r = op == 0 ? rows_forward<float>((const float *)fake, (const float *)fake, (float *)fake, s, nullptr)
+                : rows_backward_input<float>((const float *)fake, (const float *)fake, (float *)fake, s, nullptr);
+  else if (esize == 2)
+    r = op == 0 ? rows_forward<__half>((const __half *)fake, (const __half *)fake, (__half *)fake, s, nullptr)
+                : rows_backward_input<__half>((const __half *)fake, (const __half *)fake, (__half *)fake, s, nullptr);
+  t_plan_out = nullptr;
+  return r == ROWS_SERVED ? 1 : 0;
 }
 
 int rows_conv_take_error() {

@@ -3,25 +3,34 @@
 //
 // Structure shared by forward, backward-input and backward-filter:
 //
-//  * A persistent CTA walks a list of tiles.  A tile is a run of full-width rows of one plane,
-//    or a group of whole small planes; either way it is ONE contiguous byte range of the NCHW
-//    tensor, so it is brought into shared memory by a single bulk asynchronous copy
-//    (cp.async.bulk, the TMA unit) that signals an mbarrier.  Stages form a ring; the copy of
-//    tile i+2 is in flight while tile i is computed.  Ranges that do not meet the 16-byte rules
-//    of the bulk copy (misaligned base, ragged last group) are staged by plain loads instead.
+//  * Persistent, warp-specialised CTAs: 7 consumer warps compute, 1 producer warp moves data.
+//    A tile is a run of full-width rows of one plane, or a group of whole small planes.  Each
+//    plane's rows are one contiguous byte range of the NCHW tensor, so the producer brings them
+//    into shared memory with bulk asynchronous copies (cp.async.bulk, the TMA unit) that
+//    signal a "full" mbarrier; consumers hand a stage back through an "empty" mbarrier.  The
+//    ring has 3 stages, so two tiles are in flight while one is computed.  A slot keeps its
+//    source's phase within 16 bytes, so the aligned interior of ANY range is a bulk copy; only
+//    ragged heads and tails (< 16 bytes) are moved by the producer's lanes with plain loads.
+//  * Every plane slot in a stage is preceded and followed by zeroed elements, so the rows
+//    above and below the map read as zero without any test in the inner loop: the margins of
+//    whole-plane slots are zeroed once per CTA and never overwritten; for row tiles the top
+//    margin is permanent and the producer clears the rows after a plane's last tile.
 //  * A tile is split into tasks (plane, block of output rows).  A task is executed by a
-//    SEGMENT of a warp: LW = 8, 16 or 32 adjacent lanes.  Lane j of the segment owns VI
-//    adjacent input columns and VO adjacent output columns.  It reads its own columns of an
-//    input row from shared memory with one vector load and gets the k-1 halo columns from
-//    neighbouring lanes by warp shuffle; rows stream through a register window, so each
-//    input element is read from shared memory once per task.
-//  * The filter taps of the task's channel sit in registers.  Every output has one
-//    accumulator, taps are applied row-major with one FMA each: the summation order of the
-//    reference kernels (torch_dwconv/dwconv_kernel.cu:164-172), hence bit-identical fp32.
+//    SEGMENT of a warp: LW = 8, 16 or 32 adjacent lanes.  Lane j owns VI adjacent input
+//    columns and VO adjacent output columns.  It reads its own columns of an input row from
+//    shared memory with one vector load and gets the k-1 halo columns from neighbouring lanes
+//    by warp shuffle; lanes beyond the map width read the zero margin, which also supplies the
+//    left/right padding when a segment has spare lanes (otherwise halo values are masked).
+//    Rows stream through a register window: each input element is read from shared memory
+//    once per task.
+//  * The filter taps of the tile's channels are written to the stage by the producer (fp32,
+//    already flipped for backward-input) and held in registers during a task.  Every output
+//    has one accumulator, taps are applied row-major with one FMA each: the summation order
+//    of the reference kernels (torch_dwconv/dwconv_kernel.cu:164-172), hence bit-identical.
 //  * Outputs leave as VO-wide vector stores, contiguous across the segment.
 //
-// All waits on mbarriers are bounded; on expiry the CTA raises a flag the host can read
-// (rows_take_device_error) and leaves after a bounded wait for its copies in flight.
+// All waits on mbarriers are bounded; on expiry the warp raises a flag the host can read
+// (dwconv_b200_device_status), stops waiting and runs to the end of the kernel.
 #pragma once
 
 #include "common.cuh"
@@ -31,11 +40,12 @@ namespace dwb {
 
 enum { MODE_FWD = 0, MODE_BWD = 1 };
 
-constexpr int ROWS_THREADS = 256;
-constexpr int ROWS_WARPS = ROWS_THREADS / 32;
+constexpr int ROWS_CWARPS = 7;                        // consumer warps
+constexpr int ROWS_THREADS = (ROWS_CWARPS + 1) * 32;  // + 1 producer warp
 constexpr int ROWS_STAGES = 3;
 constexpr int ROWS_STAGE_BYTES = 32 * 1024;
-constexpr int ROWS_SMEM_BYTES = ROWS_STAGES * ROWS_STAGE_BYTES + 128;
+constexpr int ROWS_TAIL_BYTES = 4096;  // barriers, flags, cross-warp reduction scratch
+constexpr int ROWS_SMEM_BYTES = ROWS_STAGES * ROWS_STAGE_BYTES + ROWS_TAIL_BYTES;
 constexpr unsigned ROWS_WAIT_LIMIT = 1u << 22;  // mbarrier polls before giving up
 
 // ---------------------------------------------------------------------------------------
@@ -50,12 +60,15 @@ __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
-// Generic-proxy accesses to shared memory (earlier reads of a stage) ordered before the
-// async-proxy write of the next bulk copy into it.
+// Orders this thread's earlier generic-proxy shared-memory accesses before later
+// async-proxy (bulk copy) accesses to the same locations.
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                "r"(bytes)
                : "memory");
@@ -86,6 +99,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
+// Barrier among the consumer warps only (the producer warp never joins it).
+__device__ __forceinline__ void consumer_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(ROWS_CWARPS * 32) : "memory");
+}
 
 // ---------------------------------------------------------------------------------------
 // Compile-time geometry of one kernel variant.
@@ -95,34 +112,40 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
 // "rel" values are relative to the chunk's base input row (r*S resp. r/S) and to the lane's
 // first own input column (j*VI).
 // ---------------------------------------------------------------------------------------
+__host__ __device__ constexpr int geo_fdiv(int a, int b) {
+  return a >= 0 ? a / b : -((-a + b - 1) / b);
+}
+__host__ __device__ constexpr bool geo_used(int K, int S, int mode, int u, int t) {
+  return mode == MODE_FWD ? true : (((u - K / 2 + t) % S) + S) % S == 0;
+}
+__host__ __device__ constexpr int geo_rel(int K, int S, int mode, int u, int t) {
+  return mode == MODE_FWD ? u * S - K / 2 + t : geo_fdiv(u - K / 2 + t, S);
+}
+__host__ __device__ constexpr int geo_min_rel(int K, int S, int mode, int n) {
+  int m = 1 << 20;
+  for (int u = 0; u < n; ++u)
+    for (int t = 0; t < K; ++t)
+      if (geo_used(K, S, mode, u, t) && geo_rel(K, S, mode, u, t) < m) m = geo_rel(K, S, mode, u, t);
+  return m;
+}
+__host__ __device__ constexpr int geo_max_rel(int K, int S, int mode, int n) {
+  int m = -(1 << 20);
+  for (int u = 0; u < n; ++u)
+    for (int t = 0; t < K; ++t)
+      if (geo_used(K, S, mode, u, t) && geo_rel(K, S, mode, u, t) > m) m = geo_rel(K, S, mode, u, t);
+  return m;
+}
+
 template <int K, int S, int MODE, int VI, int VO, int U>
 struct RowsGeo {
   static constexpr int P = K / 2;
-  static constexpr int fdiv(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
-  static constexpr bool used(int u, int t) {
-    return MODE == MODE_FWD ? true : (((u - P + t) % S) + S) % S == 0;
-  }
-  static constexpr int rel(int u, int t) {
-    return MODE == MODE_FWD ? u * S - P + t : fdiv(u - P + t, S);
-  }
-  static constexpr int min_rel(int n) {
-    int m = 1 << 20;
-    for (int u = 0; u < n; ++u)
-      for (int t = 0; t < K; ++t)
-        if (used(u, t) && rel(u, t) < m) m = rel(u, t);
-    return m;
-  }
-  static constexpr int max_rel(int n) {
-    int m = -(1 << 20);
-    for (int u = 0; u < n; ++u)
-      for (int t = 0; t < K; ++t)
-        if (used(u, t) && rel(u, t) > m) m = rel(u, t);
-    return m;
-  }
-  static constexpr int RMIN = min_rel(U), RMAX = max_rel(U);
+  static constexpr int fdiv(int a, int b) { return geo_fdiv(a, b); }
+  static constexpr bool used(int u, int t) { return geo_used(K, S, MODE, u, t); }
+  static constexpr int rel(int u, int t) { return geo_rel(K, S, MODE, u, t); }
+  static constexpr int RMIN = geo_min_rel(K, S, MODE, U), RMAX = geo_max_rel(K, S, MODE, U);
   static constexpr int KR = RMAX - RMIN + 1;                    // window rows per chunk
   static constexpr int ADV = MODE == MODE_FWD ? U * S : U / S;  // input rows per chunk
-  static constexpr int CMIN = min_rel(VO), CMAX = max_rel(VO);
+  static constexpr int CMIN = geo_min_rel(K, S, MODE, VO), CMAX = geo_max_rel(K, S, MODE, VO);
   static constexpr int NIN = CMAX - CMIN + 1;  // window columns
   static_assert(MODE == MODE_FWD || (U % S == 0 && VO % S == 0), "BWD: U, VO multiples of S");
   static_assert(MODE == MODE_FWD ? VI == VO * S : VO == VI * S, "VI/VO inconsistent with stride");
@@ -130,21 +153,27 @@ struct RowsGeo {
 };
 
 // First / one-past-last input row a tile of output rows [R0, R0+th) reads, clipped to the map.
-template <int K, int S, int MODE>
-__host__ __device__ __forceinline__ void tile_in_rows(int R0, int th, int Hin, int &lo, int &hi) {
-  constexpr int P = K / 2;
+__host__ __device__ __forceinline__ void tile_in_rows(int K, int S, int mode, int R0, int th,
+                                                      int Hin, int &lo, int &hi) {
+  const int P = K / 2;
   int a, b;
-  if (MODE == MODE_FWD) {
+  if (mode == MODE_FWD) {
     a = R0 * S - P;
     b = (R0 + th - 1) * S - P + K;
   } else {
-    const int n0 = R0 - P, n1 = R0 + th - 1 - P + K - 1;
-    a = n0 >= 0 ? n0 / S : -((-n0 + S - 1) / S);
-    b = (n1 >= 0 ? n1 / S : -((-n1 + S - 1) / S)) + 1;
+    a = geo_fdiv(R0 - P, S);
+    b = geo_fdiv(R0 + th - 1 - P + K - 1, S) + 1;
   }
   lo = a < 0 ? 0 : a;
   hi = b > Hin ? Hin : b;
   if (hi < lo) hi = lo;
+}
+
+// Split of a tile's th output rows over NRB row blocks; starts on multiples of RS.
+__host__ __device__ __forceinline__ void task_rows(int rb, int NRB, int R0, int th, int RS,
+                                                   int &r_begin, int &r_end) {
+  r_begin = R0 + ((rb * th) / NRB) / RS * RS;
+  r_end = (rb == NRB - 1) ? (R0 + th) : R0 + (((rb + 1) * th) / NRB) / RS * RS;
 }
 
 struct RowsParams {
@@ -153,60 +182,88 @@ struct RowsParams {
   void *out;
   int NC, C;
   int Hin, Win, Hout, Wout;
-  int G;    // planes per tile (whole planes when > 1)
-  int NRT;  // row tiles per plane group (1 when G > 1)
-  int TH;   // output rows per row tile
-  int NRB;  // row blocks (tasks) per plane inside a tile
-  int RBH;  // row-loop trip count of a task, a multiple of U
-  int LW;   // lanes per segment: 8, 16 or 32
+  int G;     // planes per tile (whole planes when NRT == 1)
+  int NRT;   // row tiles per plane (G == 1 when > 1)
+  int TH;    // output rows per row tile
+  int NRB;   // row blocks (tasks) per plane inside a tile
+  int RBH;   // row-loop trip count of a task, a multiple of U
+  int LW;    // lanes per segment: 8, 16 or 32
+  int PS;    // elements per plane slot in a stage, zero margins included
+  int ZT;    // zero elements ahead of a slot's data
+  int ZBF;   // elements the producer clears behind the data of a plane's last row tile
+  int TAPB;  // bytes at the head of a stage that hold the tile's taps (fp32)
   int ntiles;
   int flip;  // apply the filter flipped in both axes (backward-input)
 };
 
-template <typename T, int V> struct VecIO;
-// VI/VO elements between shared or global memory and fp32 registers.
-template <> struct VecIO<float, 1> {
-  static __device__ __forceinline__ void ld(const float *p, float (&v)[1]) { v[0] = *p; }
-  static __device__ __forceinline__ void st(float *p, const float (&v)[1]) { *p = v[0]; }
+// V elements from shared memory (32-bit shared address) into fp32 registers.
+template <typename T, int V> struct SmemLd;
+template <> struct SmemLd<float, 1> {
+  static __device__ __forceinline__ void ld(uint32_t a, float (&v)[1]) {
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[0]) : "r"(a));
+  }
 };
-template <> struct VecIO<float, 2> {
-  static __device__ __forceinline__ void ld(const float *p, float (&v)[2]) {
-    const float2 t = *reinterpret_cast<const float2 *>(p);
+template <> struct SmemLd<float, 2> {
+  static __device__ __forceinline__ void ld(uint32_t a, float (&v)[2]) {
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v[0]), "=f"(v[1]) : "r"(a));
+  }
+};
+template <> struct SmemLd<float, 4> {
+  static __device__ __forceinline__ void ld(uint32_t a, float (&v)[4]) {
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3])
+                 : "r"(a));
+  }
+};
+template <> struct SmemLd<__half, 1> {
+  static __device__ __forceinline__ void ld(uint32_t a, float (&v)[1]) {
+    unsigned short h;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(a));
+    v[0] = __half2float(__ushort_as_half(h));
+  }
+};
+template <> struct SmemLd<__half, 2> {
+  static __device__ __forceinline__ void ld(uint32_t a, float (&v)[2]) {
+    uint32_t r;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(r) : "r"(a));
+    const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(&r));
     v[0] = t.x; v[1] = t.y;
   }
+};
+template <> struct SmemLd<__half, 4> {
+  static __device__ __forceinline__ void ld(uint32_t a, float (&v)[4]) {
+    uint32_t r0, r1;
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(a));
+    const float2 x = __half22float2(*reinterpret_cast<const __half2 *>(&r0));
+    const float2 y = __half22float2(*reinterpret_cast<const __half2 *>(&r1));
+    v[0] = x.x; v[1] = x.y; v[2] = y.x; v[3] = y.y;
+  }
+};
+
+// V fp32 registers to global memory as one vector store of T.
+template <typename T, int V> struct GmemSt;
+template <> struct GmemSt<float, 1> {
+  static __device__ __forceinline__ void st(float *p, const float (&v)[1]) { *p = v[0]; }
+};
+template <> struct GmemSt<float, 2> {
   static __device__ __forceinline__ void st(float *p, const float (&v)[2]) {
     *reinterpret_cast<float2 *>(p) = make_float2(v[0], v[1]);
   }
 };
-template <> struct VecIO<float, 4> {
-  static __device__ __forceinline__ void ld(const float *p, float (&v)[4]) {
-    const float4 t = *reinterpret_cast<const float4 *>(p);
-    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-  }
+template <> struct GmemSt<float, 4> {
   static __device__ __forceinline__ void st(float *p, const float (&v)[4]) {
     *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
   }
 };
-template <> struct VecIO<__half, 1> {
-  static __device__ __forceinline__ void ld(const __half *p, float (&v)[1]) { v[0] = __half2float(*p); }
+template <> struct GmemSt<__half, 1> {
   static __device__ __forceinline__ void st(__half *p, const float (&v)[1]) { *p = __float2half_rn(v[0]); }
 };
-template <> struct VecIO<__half, 2> {
-  static __device__ __forceinline__ void ld(const __half *p, float (&v)[2]) {
-    const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(p));
-    v[0] = t.x; v[1] = t.y;
-  }
+template <> struct GmemSt<__half, 2> {
   static __device__ __forceinline__ void st(__half *p, const float (&v)[2]) {
     *reinterpret_cast<__half2 *>(p) = __halves2half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
   }
 };
-template <> struct VecIO<__half, 4> {
-  static __device__ __forceinline__ void ld(const __half *p, float (&v)[4]) {
-    const uint2 raw = *reinterpret_cast<const uint2 *>(p);
-    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-  }
+template <> struct GmemSt<__half, 4> {
   static __device__ __forceinline__ void st(__half *p, const float (&v)[4]) {
     __half2 a = __halves2half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
     __half2 b = __halves2half2(__float2half_rn(v[2]), __float2half_rn(v[3]));
@@ -217,24 +274,35 @@ template <> struct VecIO<__half, 4> {
   }
 };
 
-// Shared-memory bookkeeping of the stage ring.
+// Shared-memory bookkeeping: stages, then full[], empty[] barriers, the abort flag and a
+// scratch area for cross-warp sums.
 struct RowsRing {
   unsigned char *base;
-  uint64_t *bar;   // ROWS_STAGES barriers
-  int *abort_flag;
-  uint32_t phase;  // bit s = parity the next wait on stage s expects
+  uint64_t *full;
+  uint64_t *empty;
+  volatile int *abort_flag;
+  float *scratch;  // (ROWS_TAIL_BYTES - 128) bytes
   __device__ __forceinline__ unsigned char *stage(int s) const { return base + s * ROWS_STAGE_BYTES; }
 };
 
+// Zero all stages (the margins must read as zero from the first tile on), set up barriers.
 __device__ __forceinline__ RowsRing rows_ring_init(unsigned char *smem) {
   RowsRing r;
   r.base = smem;
-  r.bar = reinterpret_cast<uint64_t *>(smem + ROWS_STAGES * ROWS_STAGE_BYTES);
-  r.abort_flag = reinterpret_cast<int *>(r.bar + ROWS_STAGES);
-  r.phase = 0;
+  unsigned char *tail = smem + ROWS_STAGES * ROWS_STAGE_BYTES;
+  r.full = reinterpret_cast<uint64_t *>(tail);
+  r.empty = r.full + ROWS_STAGES;
+  r.abort_flag = reinterpret_cast<volatile int *>(r.empty + ROWS_STAGES);
+  r.scratch = reinterpret_cast<float *>(tail + 128);
+  uint4 *z = reinterpret_cast<uint4 *>(smem);
+  for (int i = threadIdx.x; i < ROWS_STAGES * ROWS_STAGE_BYTES / 16; i += ROWS_THREADS)
+    z[i] = make_uint4(0u, 0u, 0u, 0u);
   if (threadIdx.x == 0) {
 #pragma unroll
-    for (int s = 0; s < ROWS_STAGES; ++s) mbar_init(&r.bar[s], 1);
+    for (int s = 0; s < ROWS_STAGES; ++s) {
+      mbar_init(&r.full[s], 1);             // the producer's arrive (+ the copies' bytes)
+      mbar_init(&r.empty[s], ROWS_CWARPS);  // one arrive per consumer warp
+    }
     *r.abort_flag = 0;
     fence_barrier_init();
   }
@@ -247,23 +315,58 @@ __device__ __forceinline__ bool bulk_ok(const void *src, size_t bytes) {
   return bytes > 0 && ((reinterpret_cast<uintptr_t>(src) | bytes) & 15) == 0;
 }
 
-// Plain-load staging of a range the bulk copy cannot take.  All threads; caller syncs.
+// Element offset at which a range starting at global address `src` is placed behind the
+// 16-byte aligned start of its slot: the slot keeps the source's phase within 16 bytes, so that
+// the interior of the range is a legal bulk copy whatever the source alignment.
+template <typename T> __device__ __forceinline__ int slot_phase(const T *src) {
+  return (int)((reinterpret_cast<uintptr_t>(src) & 15) / sizeof(T));
+}
+
+// One lane stages `n` elements from global `src` into a slot whose data area starts at the
+// 16-byte aligned shared address `dst16`; they land at dst16 + slot_phase(src).  The 16-byte
+// aligned interior goes through the bulk-copy unit (completion on `bar`); the ragged head and
+// tail (< 16 bytes each) are moved with plain loads; the slack before the first element and
+// 16 bytes behind the last are cleared, because a tile with another phase may have left data
+// there and the consumers rely on zeros around the data.  Returns the bulk-copied bytes.
 template <typename T>
-__device__ __forceinline__ void stage_by_loads(T *dst, const T *src, int n) {
-  for (int i = threadIdx.x; i < n; i += ROWS_THREADS) dst[i] = src[i];
+__device__ __forceinline__ uint32_t stage_range(T *dst16, const T *src, int n, uint64_t *bar) {
+  constexpr int EPB = 16 / (int)sizeof(T);  // elements per 16 bytes
+  const int phase = slot_phase(src);
+  T *dst = dst16 + phase;
+  int head = (EPB - phase) & (EPB - 1);
+  if (head > n) head = n;
+  const int interior = (n - head) & ~(EPB - 1);
+  const int tail = n - head - interior;
+  if (interior > 0)
+    bulk_copy_g2s(dst + head, src + head, (uint32_t)interior * (uint32_t)sizeof(T), bar);
+  T hv[EPB], tv[EPB];
+#pragma unroll
+  for (int i = 0; i < EPB - 1; ++i) {
+    hv[i] = (i < head) ? src[i] : Elem<T>::from_acc(0);
+    tv[i] = (i < tail) ? src[head + interior + i] : Elem<T>::from_acc(0);
+  }
+#pragma unroll
+  for (int i = 0; i < EPB - 1; ++i) {
+    if (i < head) dst[i] = hv[i];
+    if (i < tail) dst[head + interior + i] = tv[i];
+    if (i < phase) dst16[i] = Elem<T>::from_acc(0);
+  }
+#pragma unroll
+  for (int i = 0; i < EPB; ++i) dst[n + i] = Elem<T>::from_acc(0);
+  return (uint32_t)interior * (uint32_t)sizeof(T);
 }
 
 // ---------------------------------------------------------------------------------------
 // One chunk-row of the register window: own columns from shared memory, halo by shuffle.
+// MASK: the segment has no spare zero lanes on its sides, halo values crossing the map edge
+// must be masked explicitly.
 // ---------------------------------------------------------------------------------------
-template <typename T, typename Geo, int VI>
-__device__ __forceinline__ void load_window_row(float (&win)[Geo::NIN], const T *row_ptr,
-                                                const bool row_ok, const int lane,
+template <typename T, typename Geo, int VI, bool MASK>
+__device__ __forceinline__ void load_window_row(float (&win)[Geo::NIN], const uint32_t addr,
+                                                const int (&src_lane)[Geo::NIN],
                                                 const uint32_t (&halo_mask)[Geo::NIN]) {
   float own[VI];
-#pragma unroll
-  for (int i = 0; i < VI; ++i) own[i] = 0.f;
-  if (row_ok) VecIO<T, VI>::ld(row_ptr, own);
+  SmemLd<T, VI>::ld(addr, own);
 #pragma unroll
   for (int ci = 0; ci < Geo::NIN; ++ci) {
     const int c = ci + Geo::CMIN;
@@ -272,165 +375,202 @@ __device__ __forceinline__ void load_window_row(float (&win)[Geo::NIN], const T 
     if (dl == 0) {
       win[ci] = own[el];
     } else {
-      const uint32_t bits =
-          __shfl_sync(0xffffffffu, __float_as_uint(own[el]), (lane + dl) & 31) & halo_mask[ci];
+      uint32_t bits = __shfl_sync(0xffffffffu, __float_as_uint(own[el]), src_lane[ci]);
+      if (MASK) bits &= halo_mask[ci];
       win[ci] = __uint_as_float(bits);
     }
   }
 }
 
-// Per-lane masks: window column c is real data iff 0 <= j*VI + c < Win.
 template <typename Geo, int VI>
-__device__ __forceinline__ void make_halo_masks(uint32_t (&halo_mask)[Geo::NIN], int j, int Win) {
+__device__ __forceinline__ void make_lane_tables(int (&src_lane)[Geo::NIN],
+                                                 uint32_t (&halo_mask)[Geo::NIN], int lane, int j,
+                                                 int Win) {
 #pragma unroll
   for (int ci = 0; ci < Geo::NIN; ++ci) {
-    const int col = j * VI + ci + Geo::CMIN;
+    const int c = ci + Geo::CMIN;
+    src_lane[ci] = (lane + Geo::fdiv(c, VI)) & 31;
+    const int col = j * VI + c;
     halo_mask[ci] = (col >= 0 && col < Win) ? 0xffffffffu : 0u;
   }
+}
+
+// Geometry of one conv tile, identical on every thread.
+struct ConvTile {
+  int pg, R0, th, gcount, in_lo, in_hi;
+};
+template <int K, int S, int MODE>
+__device__ __forceinline__ ConvTile conv_tile(const RowsParams &p, int tile) {
+  ConvTile t;
+  t.pg = tile / p.NRT;
+  const int rt = tile - t.pg * p.NRT;
+  t.R0 = rt * p.TH;
+  t.th = min(p.TH, p.Hout - t.R0);
+  t.gcount = min(p.G, p.NC - t.pg * p.G);
+  if (p.NRT == 1) {
+    t.in_lo = 0;
+    t.in_hi = p.Hin;
+  } else {
+    tile_in_rows(K, S, MODE, t.R0, t.th, p.Hin, t.in_lo, t.in_hi);
+  }
+  return t;
 }
 
 // ---------------------------------------------------------------------------------------
 // forward / backward-input
 // ---------------------------------------------------------------------------------------
-template <typename T, int K, int S, int MODE, int VI, int VO, int U, int MINB>
+template <typename T, int K, int S, int MODE, int VI, int VO, int U, bool MASK, int MINB>
 __global__ void __launch_bounds__(ROWS_THREADS, MINB)
 rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
   using Geo = RowsGeo<K, S, MODE, VI, VO, U>;
+  constexpr int KK = K * K;
   extern __shared__ __align__(128) unsigned char rows_smem[];
   RowsRing ring = rows_ring_init(rows_smem);
 
   const T *__restrict__ gin = static_cast<const T *>(p.in);
   const T *__restrict__ gw = static_cast<const T *>(p.w);
   T *__restrict__ gout = static_cast<T *>(p.out);
-
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  const size_t plane_in = (size_t)p.Hin * p.Win;
+  const size_t plane_out = (size_t)p.Hout * p.Wout;
+
+  if (warp == ROWS_CWARPS) {
+    // ------------------------------- producer warp -------------------------------
+    bool aborted = false;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
+      const int stage = it % ROWS_STAGES;
+      const int use = it / ROWS_STAGES;
+      if (use > 0 && !aborted && !mbar_wait_bounded(&ring.empty[stage], (use - 1) & 1)) {
+        aborted = true;
+        *ring.abort_flag = 1;
+        atomicExch(error_flag, 1);
+      }
+      if (aborted || *ring.abort_flag) break;
+      const ConvTile t = conv_tile<K, S, MODE>(p, tile);
+      unsigned char *sb = ring.stage(stage);
+      fence_proxy_async_smem();
+      // the planes' rows: bulk copies go out first, everything below overlaps with them
+      T *data = reinterpret_cast<T *>(sb + p.TAPB);
+      const int elems = (t.in_hi - t.in_lo) * p.Win;
+      const T *src0 = gin + (size_t)t.pg * p.G * plane_in + (size_t)t.in_lo * p.Win;
+      uint32_t tx = 0;
+      for (int g = lane; g < t.gcount; g += 32)
+        tx += stage_range(data + (size_t)g * p.PS + p.ZT, src0 + (size_t)g * plane_in, elems,
+                          &ring.full[stage]);
+      if (p.NRT > 1 && t.in_hi == p.Hin) {  // last row tile of a plane: rows below the map are zero
+        T *below = data + p.ZT + slot_phase(src0) + elems;
+        for (int i = lane; i < p.ZBF; i += 32) below[i] = Elem<T>::from_acc(0);
+      }
+      // taps of the tile's planes, fp32, flipped for backward-input; loads batched so that
+      // their latencies overlap
+      float *staps = reinterpret_cast<float *>(sb);
+      const int ntap = t.gcount * KK;
+      const int c_base = (int)(((long long)t.pg * p.G) % p.C);
+      constexpr int TB = 8;
+      for (int base = 0; base < ntap; base += 32 * TB) {
+        float v[TB];
+#pragma unroll
+        for (int k = 0; k < TB; ++k) {
+          const int idx = base + k * 32 + lane;
+          v[k] = 0.f;
+          if (idx < ntap) {
+            const int g = idx / KK;
+            const int tp = idx - g * KK;
+            const int c = (c_base + g) % p.C;
+            v[k] = Elem<T>::ld(gw + (size_t)c * KK + (p.flip ? (KK - 1 - tp) : tp));
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < TB; ++k) {
+          const int idx = base + k * 32 + lane;
+          if (idx < ntap) staps[idx] = v[k];
+        }
+      }
+      tx = warp_sum(tx);
+      __syncwarp();
+      if (lane == 0) {
+        if (tx)
+          mbar_arrive_expect_tx(&ring.full[stage], tx);
+        else
+          mbar_arrive(&ring.full[stage]);
+      }
+    }
+    return;
+  }
+
+  // ------------------------------- consumer warps -------------------------------
   const int LW = p.LW;
   const int segs_per_warp = 32 / LW;
   const int j = lane & (LW - 1);
   const int seg = warp * segs_per_warp + lane / LW;
-  const int NSEG = ROWS_WARPS * segs_per_warp;
+  const int NSEG = ROWS_CWARPS * segs_per_warp;
   const bool in_alive = j * VI < p.Win;    // Win % VI == 0: a lane's block is all in or all out
   const bool out_alive = j * VO < p.Wout;  // Wout % VO == 0
+  constexpr int RS = (MODE == MODE_BWD) ? S : 1;
 
+  int src_lane[Geo::NIN];
   uint32_t halo_mask[Geo::NIN];
-  make_halo_masks<Geo, VI>(halo_mask, j, p.Win);
+  make_lane_tables<Geo, VI>(src_lane, halo_mask, lane, j, p.Win);
 
-  const size_t plane_in = (size_t)p.Hin * p.Win;
-  const size_t plane_out = (size_t)p.Hout * p.Wout;
   const int ntasks = p.G * p.NRB;
-
-  // tile -> source range; identical on every thread
-  auto tile_geom = [&](int tile, int &pg, int &R0, int &th, int &gcount, int &in_lo, int &in_hi) {
-    pg = tile / p.NRT;
-    const int rt = tile - pg * p.NRT;
-    R0 = rt * p.TH;
-    th = min(p.TH, p.Hout - R0);
-    gcount = min(p.G, p.NC - pg * p.G);
-    if (p.G > 1) {
-      in_lo = 0;
-      in_hi = p.Hin;
-    } else {
-      tile_in_rows<K, S, MODE>(R0, th, p.Hin, in_lo, in_hi);
-    }
-  };
-  auto tile_src = [&](int pg, int gcount, int in_lo, int in_hi, const T *&src, size_t &elems) {
-    src = gin + (size_t)pg * p.G * plane_in + (size_t)in_lo * p.Win;
-    elems = (p.G > 1) ? (size_t)gcount * plane_in : (size_t)(in_hi - in_lo) * p.Win;
-  };
-  auto issue = [&](int tile, int stage) {  // thread 0 only
-    int pg, R0, th, gcount, in_lo, in_hi;
-    tile_geom(tile, pg, R0, th, gcount, in_lo, in_hi);
-    const T *src;
-    size_t elems;
-    tile_src(pg, gcount, in_lo, in_hi, src, elems);
-    const size_t bytes = elems * sizeof(T);
-    if (bulk_ok(src, bytes)) {
-      mbar_expect_tx(&ring.bar[stage], (uint32_t)bytes);
-      bulk_copy_g2s(ring.stage(stage), src, (uint32_t)bytes, &ring.bar[stage]);
-    }
-  };
-
-  if (threadIdx.x == 0) {
-#pragma unroll
-    for (int s = 0; s < ROWS_STAGES - 1; ++s) {
-      const int t = blockIdx.x + s * gridDim.x;
-      if (t < p.ntiles) issue(t, s);
-    }
-  }
-
+  const uint32_t row_bytes = (uint32_t)p.Win * (uint32_t)sizeof(T);
+  bool aborted = false;
   int it = 0;
   for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
     const int stage = it % ROWS_STAGES;
-    if (threadIdx.x == 0) {
-      const int nt = tile + (ROWS_STAGES - 1) * gridDim.x;
-      if (nt < p.ntiles) {
-        fence_proxy_async_smem();
-        issue(nt, (it + ROWS_STAGES - 1) % ROWS_STAGES);
-      }
+    const int use = it / ROWS_STAGES;
+    if (!aborted && !mbar_wait_bounded(&ring.full[stage], use & 1)) {
+      aborted = true;
+      *ring.abort_flag = 1;
+      atomicExch(error_flag, 1);
     }
-    int pg, R0, th, gcount, in_lo, in_hi;
-    tile_geom(tile, pg, R0, th, gcount, in_lo, in_hi);
-    const T *src;
-    size_t elems;
-    tile_src(pg, gcount, in_lo, in_hi, src, elems);
-    T *sdata = reinterpret_cast<T *>(ring.stage(stage));
-    if (bulk_ok(src, elems * sizeof(T))) {
-      const uint32_t parity = (ring.phase >> stage) & 1u;
-      ring.phase ^= 1u << stage;
-      if (!mbar_wait_bounded(&ring.bar[stage], parity)) {
-        *ring.abort_flag = 1;
-        atomicExch(error_flag, 1);
-      }
-    } else {
-      stage_by_loads(sdata, src, (int)elems);
-      __syncthreads();
-    }
-    const int tile_rows = in_hi - in_lo;
+    if (aborted || *ring.abort_flag) break;
+    const ConvTile t = conv_tile<K, S, MODE>(p, tile);
+    unsigned char *sb = ring.stage(stage);
+    const float *staps = reinterpret_cast<const float *>(sb);
+    const uint32_t sdata = smem_u32(sb + p.TAPB);  // slot 0 starts with >= 16 zero bytes
 
     for (int t0 = 0; t0 < ntasks; t0 += NSEG) {
       const int task = t0 + seg;
       const int g = task / p.NRB;
       const int rb = task - g * p.NRB;
-      const bool active = (task < ntasks) && (g < gcount);
-      const int plane = pg * p.G + (active ? g : 0);
-      // balanced split of the tile's rows over the NRB row blocks, starts on multiples of S
-      constexpr int RS = (MODE == MODE_BWD) ? S : 1;
-      const int r_begin = R0 + ((rb * th) / p.NRB) / RS * RS;
-      const int r_end = (rb == p.NRB - 1) ? (R0 + th) : R0 + (((rb + 1) * th) / p.NRB) / RS * RS;
+      const bool active = (task < ntasks) && (g < t.gcount);
+      const int plane = t.pg * p.G + (active ? g : 0);
+      int r_begin, r_end;
+      task_rows(rb, p.NRB, t.R0, t.th, RS, r_begin, r_end);
 
       float taps[K][K];
-      {
-        const T *wp = gw + (size_t)(plane % p.C) * (K * K);
 #pragma unroll
-        for (int ty = 0; ty < K; ++ty)
+      for (int ty = 0; ty < K; ++ty)
 #pragma unroll
-          for (int tx = 0; tx < K; ++tx) {
-            const int idx = ty * K + tx;
-            taps[ty][tx] = active ? Elem<T>::ld(wp + (p.flip ? (K * K - 1 - idx) : idx)) : 0.f;
-          }
+        for (int tx = 0; tx < K; ++tx) taps[ty][tx] = active ? staps[g * KK + ty * K + tx] : 0.f;
+
+      // shared address of this lane's block in window row 0, and the row pitch; lanes with
+      // nothing to read sit on the zero margin with pitch 0
+      const int q0 = (MODE == MODE_FWD ? r_begin * S : r_begin / S) + Geo::RMIN - t.in_lo;
+      uint32_t a = sdata;
+      uint32_t pitch = 0;
+      if (active && in_alive) {
+        const int phase = slot_phase(gin + (size_t)plane * plane_in + (size_t)t.in_lo * p.Win);
+        a = sdata + (uint32_t)((g * p.PS + p.ZT + phase + q0 * p.Win + j * VI) * (int)sizeof(T));
+        pitch = row_bytes;
       }
-      const T *splane = sdata + (size_t)(active ? g : 0) * tile_rows * p.Win + j * VI;
-      T *oplane = gout + (size_t)plane * plane_out + j * VO;
+      T *orow = gout + (size_t)plane * plane_out + (size_t)r_begin * p.Wout + j * VO;
+      int rows_left = (active && out_alive) ? (r_end - r_begin) : 0;
 
       float rows[Geo::KR][Geo::NIN];
-      // chunk base input row: r*S (FWD) or r/S (BWD), plus RMIN
-      int ibase = (MODE == MODE_FWD ? r_begin * S : r_begin / S) + Geo::RMIN;
 #pragma unroll
       for (int i = 0; i < Geo::KR - Geo::ADV; ++i) {
-        const int ir = ibase + i;
-        const bool ok = active && in_alive && ir >= in_lo && ir < in_hi;
-        load_window_row<T, Geo, VI>(rows[i], splane + (size_t)(ir - in_lo) * p.Win, ok, lane,
-                                    halo_mask);
+        load_window_row<T, Geo, VI, MASK>(rows[i], a, src_lane, halo_mask);
+        a += pitch;
       }
       for (int rr = 0; rr < p.RBH; rr += U) {
-        const int r = r_begin + rr;
 #pragma unroll
         for (int i = Geo::KR - Geo::ADV; i < Geo::KR; ++i) {
-          const int ir = ibase + i;
-          const bool ok = active && in_alive && ir >= in_lo && ir < in_hi;
-          load_window_row<T, Geo, VI>(rows[i], splane + (size_t)(ir - in_lo) * p.Win, ok, lane,
-                                      halo_mask);
+          load_window_row<T, Geo, VI, MASK>(rows[i], a, src_lane, halo_mask);
+          a += pitch;
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -450,26 +590,20 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
               }
             }
           }
-          if (active && out_alive && (r + u) < r_end)
-            VecIO<T, VO>::st(oplane + (size_t)(r + u) * p.Wout, acc);
+          if (u < rows_left) GmemSt<T, VO>::st(orow, acc);
+          orow += p.Wout;
         }
 #pragma unroll
         for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
 #pragma unroll
           for (int ci = 0; ci < Geo::NIN; ++ci) rows[i][ci] = rows[i + Geo::ADV][ci];
-        ibase += Geo::ADV;
+        rows_left -= U;
       }
     }
-    __syncthreads();  // every warp is done with this stage before it is refilled
-    if (*ring.abort_flag) break;
-  }
-  // Leaving early with copies in flight would let them land in shared memory that no longer
-  // belongs to this CTA: give each pending stage a bounded wait.
-  if (*ring.abort_flag && threadIdx.x == 0) {
-    for (int s = 0; s < ROWS_STAGES; ++s) (void)mbar_wait_bounded(&ring.bar[s], (ring.phase >> s) & 1u);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ring.empty[stage]);  // this warp is done with the stage
   }
 }
-
 
 // ---------------------------------------------------------------------------------------
 // backward-filter, first pass
@@ -479,222 +613,242 @@ struct RowsFilterParams {
   const void *dy;
   float *partial;  // [C][SL][K*K]
   int N, C, H, W, Ho, Wo;
-  int G;    // images (planes of one channel) per tile; whole planes when > 1
+  int G;    // images (planes of one channel) per tile; whole planes when NRT == 1
   int NRT;  // row tiles per plane
   int TH;   // dy rows per row tile
   int NRB, RBH, LW;
-  int TPC;  // tiles per channel = ceil(N / G) * NRT
-  int SL;   // CTAs (slices of the tile list) per channel
-  int XPL;  // elements reserved per x plane in a stage
-  int DPL;  // elements reserved per dy plane in a stage
-  int DYOFF;  // byte offset of the dy region inside a stage (multiple of 128)
-  int x_bulk, dy_bulk;  // plane byte sizes are multiples of 16 (all planes equally aligned)
+  int TPC;    // tiles per channel = ceil(N / G) * NRT
+  int SL;     // work items (slices of the tile list) per channel
+  int PS;     // elements per x plane slot, zero margins included
+  int ZT;     // zero elements ahead of an x slot's data
+  int ZBF;    // elements cleared behind the x data of a plane's last row tile
+  int DPL;    // elements per dy plane slot
+  int DYOFF;  // byte offset of the dy slots inside a stage (multiple of 128)
 };
 
-// CTA (channel c, slice): accumulates dW[c] over its share of the (image, row tile) list.
+struct FilterTile {
+  int n0, gcount, R0, th, in_lo, in_hi;
+};
+template <int K, int S>
+__device__ __forceinline__ FilterTile filter_tile(const RowsFilterParams &p, int tt) {
+  FilterTile t;
+  const int ng = tt / p.NRT;
+  const int rt = tt - ng * p.NRT;
+  t.n0 = ng * p.G;
+  t.gcount = min(p.G, p.N - t.n0);
+  t.R0 = rt * p.TH;
+  t.th = min(p.TH, p.Ho - t.R0);
+  if (p.NRT == 1) {
+    t.in_lo = 0;
+    t.in_hi = p.H;
+  } else {
+    tile_in_rows(K, S, MODE_FWD, t.R0, t.th, p.H, t.in_lo, t.in_hi);
+  }
+  return t;
+}
+
+// Persistent CTAs walk work items (channel c, slice of that channel's (image, row tile) list).
 // Lane layout as in the forward kernel: the x window is the forward window, dy is the lane's VO
-// own output columns.  Each lane keeps K*K accumulators across all its tasks; one warp-shuffle
-// sum and one cross-warp sum in shared memory at the end give the slice's partial, written
-// to its own slot (no atomics); a second kernel adds the slices in order.
-template <typename T, int K, int S, int VI, int VO, int U, int MINB>
+// own output columns.  Each lane keeps K*K accumulators over an item; one warp-shuffle sum and
+// one cross-warp sum in shared memory give the item's partial, written to its own slot (no
+// atomics); a second kernel adds a channel's slices in order.  The copy pipeline runs across
+// item boundaries.
+template <typename T, int K, int S, int VI, int VO, int U, bool MASK, int MINB>
 __global__ void __launch_bounds__(ROWS_THREADS, MINB)
 rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
   using Geo = RowsGeo<K, S, MODE_FWD, VI, VO, U>;
+  constexpr int KK = K * K;
   extern __shared__ __align__(128) unsigned char rows_smem[];
   RowsRing ring = rows_ring_init(rows_smem);
 
   const T *__restrict__ gx = static_cast<const T *>(p.x);
   const T *__restrict__ gdy = static_cast<const T *>(p.dy);
-
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  const size_t plane_x = (size_t)p.H * p.W;
+  const size_t plane_dy = (size_t)p.Ho * p.Wo;
+  const int nitems = p.C * p.SL;
+
+  if (warp == ROWS_CWARPS) {
+    // ------------------------------- producer warp -------------------------------
+    bool aborted = false;
+    int it = 0;
+    for (int item = blockIdx.x; item < nitems && !aborted; item += gridDim.x) {
+      const int c = item / p.SL;
+      const int slice = item - c * p.SL;
+      const int t_begin = (int)(((long long)slice * p.TPC) / p.SL);
+      const int t_end = (int)(((long long)(slice + 1) * p.TPC) / p.SL);
+      for (int tt = t_begin; tt < t_end; ++tt, ++it) {
+        const int stage = it % ROWS_STAGES;
+        const int use = it / ROWS_STAGES;
+        if (use > 0 && !mbar_wait_bounded(&ring.empty[stage], (use - 1) & 1)) {
+          aborted = true;
+          *ring.abort_flag = 1;
+          atomicExch(error_flag, 2);
+        }
+        if (aborted || *ring.abort_flag) {
+          aborted = true;
+          break;
+        }
+        const FilterTile t = filter_tile<K, S>(p, tt);
+        unsigned char *sb = ring.stage(stage);
+        fence_proxy_async_smem();
+        T *xs = reinterpret_cast<T *>(sb);
+        T *ds = reinterpret_cast<T *>(sb + p.DYOFF);
+        const int xe = (t.in_hi - t.in_lo) * p.W;
+        const int de = t.th * p.Wo;
+        const size_t pl0 = (size_t)t.n0 * p.C + c;
+        const T *xsrc0 = gx + pl0 * plane_x + (size_t)t.in_lo * p.W;
+        const T *dsrc0 = gdy + pl0 * plane_dy + (size_t)t.R0 * p.Wo;
+        uint32_t tx = 0;
+        for (int g = lane; g < t.gcount; g += 32) {
+          tx += stage_range(xs + (size_t)g * p.PS + p.ZT, xsrc0 + (size_t)g * p.C * plane_x, xe,
+                            &ring.full[stage]);
+          tx += stage_range(ds + (size_t)g * p.DPL, dsrc0 + (size_t)g * p.C * plane_dy, de,
+                            &ring.full[stage]);
+        }
+        if (p.NRT > 1 && t.in_hi == p.H) {
+          T *below = xs + p.ZT + slot_phase(xsrc0) + xe;
+          for (int i = lane; i < p.ZBF; i += 32) below[i] = Elem<T>::from_acc(0);
+        }
+        tx = warp_sum(tx);
+        __syncwarp();
+        if (lane == 0) {
+          if (tx)
+            mbar_arrive_expect_tx(&ring.full[stage], tx);
+          else
+            mbar_arrive(&ring.full[stage]);
+        }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------- consumer warps -------------------------------
   const int LW = p.LW;
   const int segs_per_warp = 32 / LW;
   const int j = lane & (LW - 1);
   const int seg = warp * segs_per_warp + lane / LW;
-  const int NSEG = ROWS_WARPS * segs_per_warp;
+  const int NSEG = ROWS_CWARPS * segs_per_warp;
   const bool in_alive = j * VI < p.W;
   const bool out_alive = j * VO < p.Wo;
 
+  int src_lane[Geo::NIN];
   uint32_t halo_mask[Geo::NIN];
-  make_halo_masks<Geo, VI>(halo_mask, j, p.W);
+  make_lane_tables<Geo, VI>(src_lane, halo_mask, lane, j, p.W);
 
-  const int c = blockIdx.x / p.SL;
-  const int slice = blockIdx.x - c * p.SL;
-  const int t_begin = (int)(((long long)slice * p.TPC) / p.SL);
-  const int t_end = (int)(((long long)(slice + 1) * p.TPC) / p.SL);
-  const size_t plane_x = (size_t)p.H * p.W;
-  const size_t plane_dy = (size_t)p.Ho * p.Wo;
   const int ntasks = p.G * p.NRB;
-
-  struct TileGeom {
-    int n0, gcount, R0, th, in_lo, in_hi;
-    bool bx, bd;
-    uint32_t xbytes, dbytes;
-  };
-  auto tile_geom = [&](int tt) {
-    TileGeom g;
-    const int ng = tt / p.NRT;
-    const int rt = tt - ng * p.NRT;
-    g.n0 = ng * p.G;
-    g.gcount = min(p.G, p.N - g.n0);
-    g.R0 = rt * p.TH;
-    g.th = min(p.TH, p.Ho - g.R0);
-    if (p.G > 1) {
-      g.in_lo = 0;
-      g.in_hi = p.H;
-    } else {
-      tile_in_rows<K, S, MODE_FWD>(g.R0, g.th, p.H, g.in_lo, g.in_hi);
-    }
-    g.xbytes = (uint32_t)((g.in_hi - g.in_lo) * p.W * (int)sizeof(T));
-    g.dbytes = (uint32_t)(g.th * p.Wo * (int)sizeof(T));
-    const T *xs = gx + ((size_t)g.n0 * p.C + c) * plane_x + (size_t)g.in_lo * p.W;
-    const T *ds = gdy + ((size_t)g.n0 * p.C + c) * plane_dy + (size_t)g.R0 * p.Wo;
-    g.bx = p.x_bulk && bulk_ok(xs, g.xbytes);
-    g.bd = p.dy_bulk && bulk_ok(ds, g.dbytes);
-    return g;
-  };
-  auto issue = [&](int tt, int stage) {  // all lanes of warp 0
-    const TileGeom g = tile_geom(tt);
-    const uint32_t total = (uint32_t)g.gcount * ((g.bx ? g.xbytes : 0u) + (g.bd ? g.dbytes : 0u));
-    if (total == 0) return;
-    if (lane == 0) mbar_expect_tx(&ring.bar[stage], total);
-    __syncwarp();
-    T *xs_s = reinterpret_cast<T *>(ring.stage(stage));
-    T *ds_s = reinterpret_cast<T *>(ring.stage(stage) + p.DYOFF);
-    for (int gi = lane; gi < g.gcount; gi += 32) {
-      const size_t pl = (size_t)(g.n0 + gi) * p.C + c;
-      if (g.bx)
-        bulk_copy_g2s(xs_s + (size_t)gi * p.XPL, gx + pl * plane_x + (size_t)g.in_lo * p.W, g.xbytes,
-                      &ring.bar[stage]);
-      if (g.bd)
-        bulk_copy_g2s(ds_s + (size_t)gi * p.DPL, gdy + pl * plane_dy + (size_t)g.R0 * p.Wo, g.dbytes,
-                      &ring.bar[stage]);
-    }
-  };
-
-  if (warp == 0) {
-#pragma unroll
-    for (int s = 0; s < ROWS_STAGES - 1; ++s)
-      if (t_begin + s < t_end) issue(t_begin + s, s);
-  }
-
-  float acc[K][K];
-#pragma unroll
-  for (int ty = 0; ty < K; ++ty)
-#pragma unroll
-    for (int tx = 0; tx < K; ++tx) acc[ty][tx] = 0.f;
-
+  const uint32_t row_bytes = (uint32_t)p.W * (uint32_t)sizeof(T);
+  const uint32_t drow_bytes = (uint32_t)p.Wo * (uint32_t)sizeof(T);
+  // A warp whose wait expired keeps walking the loops without waiting or computing, so that
+  // it still meets the other consumer warps at every consumer_sync().
+  bool aborted = false;
   int it = 0;
-  for (int tt = t_begin; tt < t_end; ++tt, ++it) {
-    const int stage = it % ROWS_STAGES;
-    if (warp == 0) {
-      const int nt = tt + ROWS_STAGES - 1;
-      if (nt < t_end) {
-        fence_proxy_async_smem();
-        issue(nt, (it + ROWS_STAGES - 1) % ROWS_STAGES);
-      }
-    }
-    const TileGeom g = tile_geom(tt);
-    T *xs_s = reinterpret_cast<T *>(ring.stage(stage));
-    T *ds_s = reinterpret_cast<T *>(ring.stage(stage) + p.DYOFF);
-    if (g.bx || g.bd) {
-      const uint32_t parity = (ring.phase >> stage) & 1u;
-      ring.phase ^= 1u << stage;
-      if (!mbar_wait_bounded(&ring.bar[stage], parity)) {
+  for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+    const int c = item / p.SL;
+    const int slice = item - c * p.SL;
+    const int t_begin = (int)(((long long)slice * p.TPC) / p.SL);
+    const int t_end = (int)(((long long)(slice + 1) * p.TPC) / p.SL);
+
+    float acc[K][K];
+#pragma unroll
+    for (int ty = 0; ty < K; ++ty)
+#pragma unroll
+      for (int tx = 0; tx < K; ++tx) acc[ty][tx] = 0.f;
+
+    for (int tt = t_begin; tt < t_end; ++tt, ++it) {
+      const int stage = it % ROWS_STAGES;
+      const int use = it / ROWS_STAGES;
+      if (!aborted && (*ring.abort_flag || !mbar_wait_bounded(&ring.full[stage], use & 1))) {
+        aborted = true;
         *ring.abort_flag = 1;
         atomicExch(error_flag, 2);
       }
-    }
-    if (!g.bx || !g.bd) {
-      const int xe = (g.in_hi - g.in_lo) * p.W, de = g.th * p.Wo;
-      for (int gi = 0; gi < g.gcount; ++gi) {
-        const size_t pl = (size_t)(g.n0 + gi) * p.C + c;
-        if (!g.bx)
-          stage_by_loads(xs_s + (size_t)gi * p.XPL, gx + pl * plane_x + (size_t)g.in_lo * p.W, xe);
-        if (!g.bd)
-          stage_by_loads(ds_s + (size_t)gi * p.DPL, gdy + pl * plane_dy + (size_t)g.R0 * p.Wo, de);
-      }
-      __syncthreads();
-    }
+      if (aborted) continue;
+      const FilterTile t = filter_tile<K, S>(p, tt);
+      unsigned char *sb = ring.stage(stage);
+      const uint32_t sx = smem_u32(sb);  // x slot 0 starts with >= 16 zero bytes
+      const uint32_t sd = smem_u32(sb + p.DYOFF);
 
-    for (int t0 = 0; t0 < ntasks; t0 += NSEG) {
-      const int task = t0 + seg;
-      const int gi = task / p.NRB;
-      const int rb = task - gi * p.NRB;
-      const bool active = (task < ntasks) && (gi < g.gcount);
-      const int r_begin = g.R0 + (rb * g.th) / p.NRB;
-      const int r_end = (rb == p.NRB - 1) ? (g.R0 + g.th) : g.R0 + ((rb + 1) * g.th) / p.NRB;
-      const T *splane = xs_s + (size_t)(active ? gi : 0) * p.XPL + j * VI;
-      const T *dplane = ds_s + (size_t)(active ? gi : 0) * p.DPL + j * VO;
+      for (int t0 = 0; t0 < ntasks; t0 += NSEG) {
+        const int task = t0 + seg;
+        const int g = task / p.NRB;
+        const int rb = task - g * p.NRB;
+        const bool active = (task < ntasks) && (g < t.gcount);
+        int r_begin, r_end;
+        task_rows(rb, p.NRB, t.R0, t.th, 1, r_begin, r_end);
 
-      float rows[Geo::KR][Geo::NIN];
-      int ibase = r_begin * S + Geo::RMIN;
-#pragma unroll
-      for (int i = 0; i < Geo::KR - Geo::ADV; ++i) {
-        const int ir = ibase + i;
-        const bool ok = active && in_alive && ir >= g.in_lo && ir < g.in_hi;
-        load_window_row<T, Geo, VI>(rows[i], splane + (size_t)(ir - g.in_lo) * p.W, ok, lane,
-                                    halo_mask);
-      }
-      for (int rr = 0; rr < p.RBH; rr += U) {
-        const int r = r_begin + rr;
-#pragma unroll
-        for (int i = Geo::KR - Geo::ADV; i < Geo::KR; ++i) {
-          const int ir = ibase + i;
-          const bool ok = active && in_alive && ir >= g.in_lo && ir < g.in_hi;
-          load_window_row<T, Geo, VI>(rows[i], splane + (size_t)(ir - g.in_lo) * p.W, ok, lane,
-                                      halo_mask);
+        const int q0 = r_begin * S + Geo::RMIN - t.in_lo;
+        uint32_t a = sx;
+        uint32_t pitch = 0;
+        const size_t pl = (size_t)(t.n0 + (active ? g : 0)) * p.C + c;
+        if (active && in_alive) {
+          const int phase = slot_phase(gx + pl * plane_x + (size_t)t.in_lo * p.W);
+          a = sx + (uint32_t)((g * p.PS + p.ZT + phase + q0 * p.W + j * VI) * (int)sizeof(T));
+          pitch = row_bytes;
         }
+        const int dphase = slot_phase(gdy + pl * plane_dy + (size_t)t.R0 * p.Wo);
+        uint32_t da = sd + (uint32_t)(((active ? g : 0) * p.DPL + dphase + (r_begin - t.R0) * p.Wo +
+                                       j * VO) * (int)sizeof(T));
+        int rows_left = (active && out_alive) ? (r_end - r_begin) : 0;
+
+        float rows[Geo::KR][Geo::NIN];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          float dyv[VO];
+        for (int i = 0; i < Geo::KR - Geo::ADV; ++i) {
+          load_window_row<T, Geo, VI, MASK>(rows[i], a, src_lane, halo_mask);
+          a += pitch;
+        }
+        for (int rr = 0; rr < p.RBH; rr += U) {
 #pragma unroll
-          for (int e = 0; e < VO; ++e) dyv[e] = 0.f;
-          if (active && out_alive && (r + u) < r_end)
-            VecIO<T, VO>::ld(dplane + (size_t)(r + u - g.R0) * p.Wo, dyv);
-#pragma unroll
-          for (int ty = 0; ty < K; ++ty) {
-            const int ri = Geo::rel(u, ty) - Geo::RMIN;
-#pragma unroll
-            for (int tx = 0; tx < K; ++tx)
-#pragma unroll
-              for (int e = 0; e < VO; ++e)
-                acc[ty][tx] = fmaf(dyv[e], rows[ri][Geo::rel(e, tx) - Geo::CMIN], acc[ty][tx]);
+          for (int i = Geo::KR - Geo::ADV; i < Geo::KR; ++i) {
+            load_window_row<T, Geo, VI, MASK>(rows[i], a, src_lane, halo_mask);
+            a += pitch;
           }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (u < rows_left) {  // rows past the task's end must not contribute
+              float dyv[VO];
+              SmemLd<T, VO>::ld(da, dyv);
+#pragma unroll
+              for (int ty = 0; ty < K; ++ty) {
+                const int ri = Geo::rel(u, ty) - Geo::RMIN;
+#pragma unroll
+                for (int tx = 0; tx < K; ++tx)
+#pragma unroll
+                  for (int e = 0; e < VO; ++e)
+                    acc[ty][tx] = fmaf(dyv[e], rows[ri][Geo::rel(e, tx) - Geo::CMIN], acc[ty][tx]);
+              }
+            }
+            da += drow_bytes;
+          }
+#pragma unroll
+          for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
+#pragma unroll
+            for (int ci = 0; ci < Geo::NIN; ++ci) rows[i][ci] = rows[i + Geo::ADV][ci];
+          rows_left -= U;
         }
-#pragma unroll
-        for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
-#pragma unroll
-          for (int ci = 0; ci < Geo::NIN; ++ci) rows[i][ci] = rows[i + Geo::ADV][ci];
-        ibase += Geo::ADV;
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ring.empty[stage]);
     }
-    __syncthreads();
-    if (*ring.abort_flag) break;
-  }
 
-  if (*ring.abort_flag) {
-    if (threadIdx.x == 0)
-      for (int s = 0; s < ROWS_STAGES; ++s)
-        (void)mbar_wait_bounded(&ring.bar[s], (ring.phase >> s) & 1u);
-    __syncthreads();
-  }
-  // every copy this CTA issued has landed: stage 0 is free to hold the cross-warp sums
-  float *red = reinterpret_cast<float *>(ring.stage(0));
+    // item done: sum over lanes, then over warps, and publish the slice's partial
+    float *red = ring.scratch;  // [ROWS_CWARPS][KK]
 #pragma unroll
-  for (int ty = 0; ty < K; ++ty)
+    for (int ty = 0; ty < K; ++ty)
 #pragma unroll
-    for (int tx = 0; tx < K; ++tx) {
-      const float v = warp_sum(acc[ty][tx]);
-      if (lane == 0) red[warp * (K * K) + ty * K + tx] = v;
+      for (int tx = 0; tx < K; ++tx) {
+        const float v = warp_sum(acc[ty][tx]);
+        if (lane == 0) red[warp * KK + ty * K + tx] = v;
+      }
+    consumer_sync();
+    if (threadIdx.x < KK) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < ROWS_CWARPS; ++w) s += red[w * KK + threadIdx.x];
+      p.partial[((size_t)c * p.SL + slice) * KK + threadIdx.x] = s;
     }
-  __syncthreads();
-  if (threadIdx.x < K * K) {
-    float s = 0.f;
-#pragma unroll
-    for (int w = 0; w < ROWS_WARPS; ++w) s += red[w * (K * K) + threadIdx.x];
-    p.partial[((size_t)c * p.SL + slice) * (K * K) + threadIdx.x] = s;
+    consumer_sync();  // red is rewritten by the next item
   }
 }
 

@@ -7,8 +7,16 @@ namespace {
 
 __device__ int g_filter_error_flag;
 
-constexpr int filter_u(int K, int S) { return S == 1 ? (K == 3 ? 4 : 2) : (K <= 5 ? 2 : 1); }
 constexpr int filter_minb(int K) { return K <= 5 ? 2 : 1; }
+
+// Rows-per-chunk choices compiled for each (K, S); the planner picks per shape.
+template <int K, int S> struct FilterU;
+template <> struct FilterU<3, 1> { static constexpr int n = 2; static constexpr int v[2] = {4, 7}; };
+template <> struct FilterU<5, 1> { static constexpr int n = 2; static constexpr int v[2] = {2, 4}; };
+template <> struct FilterU<7, 1> { static constexpr int n = 1; static constexpr int v[2] = {2, 2}; };
+template <> struct FilterU<3, 2> { static constexpr int n = 2; static constexpr int v[2] = {2, 7}; };
+template <> struct FilterU<5, 2> { static constexpr int n = 1; static constexpr int v[2] = {2, 2}; };
+template <> struct FilterU<7, 2> { static constexpr int n = 1; static constexpr int v[2] = {1, 1}; };
 
 inline bool filter_shape_ok(const Shape &s) {
   if (s.kh != s.kw || (s.kh != 3 && s.kh != 5 && s.kh != 7)) return false;
@@ -19,76 +27,119 @@ inline bool filter_shape_ok(const Shape &s) {
   return true;
 }
 
-// (VI, VO) for the map widths; 0 if none applies.  a16: both tensors 16-byte aligned.
-inline int pick_v(int S, int W, int Wo, bool a16, int &VI, int &VO) {
+// (VI, VO) for the map widths; false if none applies.  a16: both tensors 16-byte aligned.
+inline bool pick_v(int S, int W, int Wo, bool a16, int &VI, int &VO) {
   if (S == 1) {
-    if (a16 && W % 4 == 0 && W <= 128 && W > 16) { VI = VO = 4; return 1; }
-    if (a16 && W % 2 == 0 && W <= 64 && W > 8) { VI = VO = 2; return 1; }
-    if (W <= 32) { VI = VO = 1; return 1; }
-    return 0;
+    if (a16 && W % 4 == 0 && W <= 128 && W > 16) { VI = VO = 4; return true; }
+    if (a16 && W % 2 == 0 && W <= 64 && W > 8) { VI = VO = 2; return true; }
+    if (W <= 32) { VI = VO = 1; return true; }
+    return false;
   }
-  if (a16 && W % 4 == 0 && Wo % 2 == 0 && W <= 128 && W > 16) { VI = 4; VO = 2; return 1; }
-  if (a16 && W % 2 == 0 && W <= 64) { VI = 2; VO = 1; return 1; }
-  return 0;
+  if (a16 && W % 4 == 0 && Wo % 2 == 0 && W <= 128 && W > 16) { VI = 4; VO = 2; return true; }
+  if (a16 && W % 2 == 0 && W <= 64) { VI = 2; VO = 1; return true; }
+  return false;
 }
 
-template <typename T>
-bool plan_filter(const Shape &s, bool a16, RowsFilterParams &p, int &VI, int &VO) {
-  if (!filter_shape_ok(s)) return false;
-  const int K = s.kh, S = s.sh;
-  if (!pick_v(S, s.W, s.Wo, a16, VI, VO)) return false;
-  const int lanes = max(ceil_div(s.W, VI), ceil_div(s.Wo, VO));
+struct FilterPlan {
+  RowsFilterParams p;
+  int VI, VO, U;
+  bool mask;
+};
+
+template <typename T, int K, int S>
+bool plan_filter_ks(const Shape &s, bool a16, FilterPlan &f) {
+  if (!pick_v(S, s.W, s.Wo, a16, f.VI, f.VO)) return false;
+  const int lanes_in = ceil_div(s.W, f.VI);
+  const int lanes = max(lanes_in, ceil_div(s.Wo, f.VO));
+  RowsFilterParams &p = f.p;
   p.LW = pick_lw(lanes);
   if (p.LW == 0) return false;
-  const int NSEG = ROWS_WARPS * (32 / p.LW);
-  const int U = filter_u(K, S);
-  TilePlan t;
-  // the dy region starts on a 128-byte boundary: keep that slack out of the budget
-  if (!plan_tiles(t, K, S, MODE_FWD, U, s.H, s.Ho, s.W * (int)sizeof(T), s.Wo * (int)sizeof(T),
-                  NSEG, ROWS_STAGE_BYTES - 128))
-    return false;
+  PlanInput in{K, S, MODE_FWD, s.H, s.W, s.Ho, s.Wo, (int)sizeof(T),
+               ROWS_CWARPS * (32 / p.LW), false, true};
+  const TilePlan t = plan_best(in, FilterU<K, S>::v, FilterU<K, S>::n);
+  if (!t.ok) return false;
   p.N = s.N; p.C = s.C; p.H = s.H; p.W = s.W; p.Ho = s.Ho; p.Wo = s.Wo;
   p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;
-  const int xrows = (p.G > 1) ? s.H : min(s.H, (p.TH - 1) * S + K);
-  p.XPL = xrows * s.W;
-  p.DPL = p.TH * s.Wo;
-  p.DYOFF = round_up(p.G * p.XPL * (int)sizeof(T), 128);
-  if (p.DYOFF + p.G * p.DPL * (int)sizeof(T) > ROWS_STAGE_BYTES) return false;
-  p.TPC = ceil_div(s.N, p.G) * p.NRT;
-  int SL = ceil_div(4 * sm_count(), s.C);
+  p.PS = t.PS; p.ZT = t.ZT; p.ZBF = t.ZBF; p.DPL = t.DPL; p.DYOFF = t.DYOFF;
+  f.U = t.U;
+  const long long tpc = (long long)ceil_div(s.N, p.G) * p.NRT;
+  if (tpc > (1ll << 30)) return false;
+  p.TPC = (int)tpc;
+  // enough work items for ~2 per resident CTA, at least one tile each
+  const int slots = sm_count() * filter_minb(K);
+  int SL = ceil_div(2 * slots, s.C);
   if (SL > p.TPC) SL = p.TPC;
   if (SL < 1) SL = 1;
   p.SL = SL;
-  p.x_bulk = ((size_t)s.H * s.W * sizeof(T)) % 16 == 0;
-  p.dy_bulk = ((size_t)s.Ho * s.Wo * sizeof(T)) % 16 == 0;
+  // halo reach in lanes (column geometry does not depend on U)
+  const int cmin = geo_min_rel(K, S, MODE_FWD, f.VO), cmax = geo_max_rel(K, S, MODE_FWD, f.VO);
+  const int hl = -geo_fdiv(cmin, f.VI), hr = geo_fdiv(cmax, f.VI);
+  f.mask = (p.LW - lanes_in) < (hl > hr ? hl : hr);
   return true;
 }
 
-template <typename T, int K, int S, int VI, int VO>
-int launch_filter(const RowsFilterParams &p, cudaStream_t st) {
-  constexpr int U = filter_u(K, S);
+template <typename T>
+bool plan_filter(const Shape &s, bool a16, FilterPlan &f) {
+  if (!filter_shape_ok(s)) return false;
+  switch (s.kh * 10 + s.sh) {
+    case 31: return plan_filter_ks<T, 3, 1>(s, a16, f);
+    case 51: return plan_filter_ks<T, 5, 1>(s, a16, f);
+    case 71: return plan_filter_ks<T, 7, 1>(s, a16, f);
+    case 32: return plan_filter_ks<T, 3, 2>(s, a16, f);
+    case 52: return plan_filter_ks<T, 5, 2>(s, a16, f);
+    case 72: return plan_filter_ks<T, 7, 2>(s, a16, f);
+    default: return false;
+  }
+}
+
+int *filter_flag_address() {
+  static std::atomic<int *> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  int *p = cached[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    if (cudaGetSymbolAddress((void **)&p, g_filter_error_flag) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    cached[dev].store(p, std::memory_order_release);
+  }
+  return p;
+}
+
+template <typename T, int K, int S, int VI, int VO, int U, bool MASK>
+int launch_variant(const RowsFilterParams &p, cudaStream_t st) {
   constexpr int MINB = filter_minb(K);
-  auto kernel = rows_filter_kernel<T, K, S, VI, VO, U, MINB>;
+  auto kernel = rows_filter_kernel<T, K, S, VI, VO, U, MASK, MINB>;
   static std::atomic<unsigned long long> smem_done{0};
   if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
-  int *flag = nullptr;
-  if (cudaGetSymbolAddress((void **)&flag, g_filter_error_flag) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return ROWS_DECLINED;
-  }
-  kernel<<<p.C * p.SL, ROWS_THREADS, ROWS_SMEM_BYTES, st>>>(p, flag);
+  int *flag = filter_flag_address();
+  if (flag == nullptr) return ROWS_DECLINED;
+  const long long items = (long long)p.C * p.SL;
+  const int grid = (int)min((long long)sm_count() * MINB, items);
+  kernel<<<grid, ROWS_THREADS, ROWS_SMEM_BYTES, st>>>(p, flag);
   return ROWS_SERVED;
 }
 
+template <typename T, int K, int S, int VI, int VO>
+int launch_filter_v(const FilterPlan &f, cudaStream_t st) {
+  constexpr int U0 = FilterU<K, S>::v[0], U1 = FilterU<K, S>::v[1];
+  if (f.U == U0)
+    return f.mask ? launch_variant<T, K, S, VI, VO, U0, true>(f.p, st)
+                  : launch_variant<T, K, S, VI, VO, U0, false>(f.p, st);
+  return f.mask ? launch_variant<T, K, S, VI, VO, U1, true>(f.p, st)
+                : launch_variant<T, K, S, VI, VO, U1, false>(f.p, st);
+}
+
 template <typename T, int K, int S>
-int select_filter_v(const RowsFilterParams &p, int VI, cudaStream_t st) {
+int launch_filter(const FilterPlan &f, cudaStream_t st) {
   if (S == 1) {
-    if (VI == 4) return launch_filter<T, K, 1, 4, 4>(p, st);
-    if (VI == 2) return launch_filter<T, K, 1, 2, 2>(p, st);
-    return launch_filter<T, K, 1, 1, 1>(p, st);
+    if (f.VI == 4) return launch_filter_v<T, K, 1, 4, 4>(f, st);
+    if (f.VI == 2) return launch_filter_v<T, K, 1, 2, 2>(f, st);
+    return launch_filter_v<T, K, 1, 1, 1>(f, st);
   }
-  if (VI == 4) return launch_filter<T, K, 2, 4, 2>(p, st);
-  return launch_filter<T, K, 2, 2, 1>(p, st);
+  if (f.VI == 4) return launch_filter_v<T, K, 2, 4, 2>(f, st);
+  return launch_filter_v<T, K, 2, 2, 1>(f, st);
 }
 
 template <typename T> struct RowsDtype { static constexpr bool ok = false; };
@@ -102,10 +153,10 @@ template <typename T> int rows_backward_filter_slices(const Shape &s) {
     return 0;
   } else {
     // alignment is not known here: report the largest slice count either choice would use
-    RowsFilterParams p{};
-    int VI, VO, best = 0;
+    FilterPlan f{};
+    int best = 0;
     for (int a16 = 0; a16 < 2; ++a16)
-      if (plan_filter<T>(s, a16 != 0, p, VI, VO) && p.SL > best) best = p.SL;
+      if (plan_filter<T>(s, a16 != 0, f) && f.p.SL > best) best = f.p.SL;
     return best;
   }
 }
@@ -117,18 +168,17 @@ int rows_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *parti
     return ROWS_DECLINED;
   } else {
     const bool a16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy)) & 15) == 0;
-    RowsFilterParams p{};
-    int VI, VO;
-    if (!plan_filter<T>(s, a16, p, VI, VO)) return ROWS_DECLINED;
-    p.x = x; p.dy = dy; p.partial = partial;
-    *slices_out = p.SL;
+    FilterPlan f{};
+    if (!plan_filter<T>(s, a16, f)) return ROWS_DECLINED;
+    f.p.x = x; f.p.dy = dy; f.p.partial = partial;
+    *slices_out = f.p.SL;
     switch (s.kh * 10 + s.sh) {
-      case 31: return select_filter_v<T, 3, 1>(p, VI, st);
-      case 51: return select_filter_v<T, 5, 1>(p, VI, st);
-      case 71: return select_filter_v<T, 7, 1>(p, VI, st);
-      case 32: return select_filter_v<T, 3, 2>(p, VI, st);
-      case 52: return select_filter_v<T, 5, 2>(p, VI, st);
-      case 72: return select_filter_v<T, 7, 2>(p, VI, st);
+      case 31: return launch_filter<T, 3, 1>(f, st);
+      case 51: return launch_filter<T, 5, 1>(f, st);
+      case 71: return launch_filter<T, 7, 1>(f, st);
+      case 32: return launch_filter<T, 3, 2>(f, st);
+      case 52: return launch_filter<T, 5, 2>(f, st);
+      case 72: return launch_filter<T, 7, 2>(f, st);
       default: return ROWS_DECLINED;
     }
   }
@@ -155,5 +205,18 @@ template int rows_backward_filter_slices<double>(const Shape &);
 template int rows_backward_filter<float>(const float *, const float *, float *, const Shape &, cudaStream_t, int *);
 template int rows_backward_filter<__half>(const __half *, const __half *, float *, const Shape &, cudaStream_t, int *);
 template int rows_backward_filter<double>(const double *, const double *, double *, const Shape &, cudaStream_t, int *);
+
+// Tiling the backward-filter first pass would use, for inspection: the test-suite models the
+// kernel's index arithmetic on the CPU from these numbers.
+int rows_debug_filter_plan(int esize, const Shape &s, int a16, int *out) {
+  FilterPlan f{};
+  bool ok = esize == 4 ? plan_filter<float>(s, a16 != 0, f) : plan_filter<__half>(s, a16 != 0, f);
+  if (!ok) return 0;
+  const RowsFilterParams &p = f.p;
+  const int v[24] = {f.VI, f.VO, f.U, f.mask ? 1 : 0, p.LW, p.G, p.NRT, p.TH, p.NRB, p.RBH, p.PS, p.ZT,
+                     p.ZBF, 0, p.DPL, p.DYOFF, p.TPC, p.SL, 0, 0, 0, 0, 0, 0};
+  for (int i = 0; i < 24; ++i) out[i] = v[i];
+  return 1;
+}
 
 }  // namespace dwb

@@ -36,6 +36,7 @@ def _load():
         "dwconv_b200_set_path": (ci, [ci]),
         "dwconv_b200_last_path": (ci, []),
         "dwconv_b200_device_status": (ci, []),
+        "dwconv_b200_debug_plan": (ci, [ci, ci, sp, ci, ctypes.POINTER(ci)]),
         "dwconv_b200_out_size": (ci, [ci] * 6),
         "dwconv_b200_forward": (ci, [vp, vp, vp, ci, sp, vp]),
         "dwconv_b200_backward_input": (ci, [vp, vp, vp, ci, sp, vp]),
@@ -63,7 +64,7 @@ lib = _load()
 EXPORTS = (
     "dwconv_b200_version", "dwconv_b200_status_string", "dwconv_b200_last_cuda_error",
     "dwconv_b200_set_path", "dwconv_b200_last_path", "dwconv_b200_device_status",
-    "dwconv_b200_out_size",
+    "dwconv_b200_debug_plan", "dwconv_b200_out_size",
     "dwconv_b200_forward", "dwconv_b200_backward_input",
     "dwconv_b200_backward_filter_workspace_bytes", "dwconv_b200_backward_filter",
     "dwconv_b200_use_dwconv2d_small", "dwconv_b200_dwconv2d", "dwconv_b200_dwconv2d_small",

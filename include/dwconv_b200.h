@@ -93,6 +93,13 @@ DWCONV_B200_API int dwconv_b200_last_cuda_error(void);
  * Diagnostic: not needed on the hot path.  No counterpart in the reference. */
 DWCONV_B200_API int dwconv_b200_device_status(void);
 
+/* Host-only: the kernel variant and tiling the rows family would use for an operator
+ * (op 0 forward, 1 backward-input, 2 backward-filter), as 24 ints; returns 0 if that family
+ * declines the problem.  For tests that model the kernels' index arithmetic on the CPU.
+ * No counterpart in the reference. */
+DWCONV_B200_API int dwconv_b200_debug_plan(int op, int dtype, const dwconv_b200_shape *shape,
+                                           int aligned16, int *out24);
+
 /* Force a kernel family (testing / profiling).  Process-wide; returns the previous value. */
 DWCONV_B200_API int dwconv_b200_set_path(int path);
 /* Kernel family that served the calling thread's most recent call. */
