@@ -44,7 +44,7 @@ constexpr int ROWS_CWARPS = 7;                        // consumer warps
 constexpr int ROWS_THREADS = (ROWS_CWARPS + 1) * 32;  // + 1 producer warp
 constexpr int ROWS_STAGES = 3;
 constexpr int ROWS_STAGE_BYTES = 32 * 1024;
-constexpr int ROWS_TAIL_BYTES = 4096;  // barriers, flags, cross-warp reduction scratch
+constexpr int ROWS_TAIL_BYTES = 8192;  // barriers, flags, cross-segment reduction scratch
 constexpr int ROWS_SMEM_BYTES = ROWS_STAGES * ROWS_STAGE_BYTES + ROWS_TAIL_BYTES;
 constexpr unsigned ROWS_WAIT_LIMIT = 1u << 22;  // mbarrier polls before giving up
 
@@ -188,10 +188,8 @@ struct RowsParams {
   int NRB;   // row blocks (tasks) per plane inside a tile
   int RBH;   // row-loop trip count of a task, a multiple of U
   int LW;    // lanes per segment: 8, 16 or 32
-  int PS;    // elements per plane slot in a stage, zero margins included
-  int ZT;    // zero elements ahead of a slot's data
-  int ZBF;   // elements the producer clears behind the data of a plane's last row tile
-  int TAPB;  // bytes at the head of a stage that hold the tile's taps (fp32)
+  int TAPB;  // bytes at the head of a stage that hold the tile's taps (fp32); 16 zero bytes
+             // follow, then the tile's rows
   int ntiles;
   int flip;  // apply the filter flipped in both axes (backward-input)
 };
@@ -322,12 +320,10 @@ template <typename T> __device__ __forceinline__ int slot_phase(const T *src) {
   return (int)((reinterpret_cast<uintptr_t>(src) & 15) / sizeof(T));
 }
 
-// One lane stages `n` elements from global `src` into a slot whose data area starts at the
-// 16-byte aligned shared address `dst16`; they land at dst16 + slot_phase(src).  The 16-byte
-// aligned interior goes through the bulk-copy unit (completion on `bar`); the ragged head and
-// tail (< 16 bytes each) are moved with plain loads; the slack before the first element and
-// 16 bytes behind the last are cleared, because a tile with another phase may have left data
-// there and the consumers rely on zeros around the data.  Returns the bulk-copied bytes.
+// One lane stages `n` elements from global `src` into a data area that starts at the 16-byte
+// aligned shared address `dst16`; they land at dst16 + slot_phase(src).  The 16-byte aligned
+// interior goes through the bulk-copy unit (completion on `bar`); the ragged head and tail
+// (< 16 bytes each) are moved with plain loads.  Returns the bulk-copied bytes.
 template <typename T>
 __device__ __forceinline__ uint32_t stage_range(T *dst16, const T *src, int n, uint64_t *bar) {
   constexpr int EPB = 16 / (int)sizeof(T);  // elements per 16 bytes
@@ -349,10 +345,7 @@ __device__ __forceinline__ uint32_t stage_range(T *dst16, const T *src, int n, u
   for (int i = 0; i < EPB - 1; ++i) {
     if (i < head) dst[i] = hv[i];
     if (i < tail) dst[head + interior + i] = tv[i];
-    if (i < phase) dst16[i] = Elem<T>::from_acc(0);
   }
-#pragma unroll
-  for (int i = 0; i < EPB; ++i) dst[n + i] = Elem<T>::from_acc(0);
   return (uint32_t)interior * (uint32_t)sizeof(T);
 }
 
@@ -361,12 +354,18 @@ __device__ __forceinline__ uint32_t stage_range(T *dst16, const T *src, int n, u
 // MASK: the segment has no spare zero lanes on its sides, halo values crossing the map edge
 // must be masked explicitly.
 // ---------------------------------------------------------------------------------------
+// `q` is the row's index inside the staged rows of the lane's plane; rows outside [0, lim) are
+// the zero padding above / below the map and are read from the stage's zero bytes instead.
 template <typename T, typename Geo, int VI, bool MASK>
-__device__ __forceinline__ void load_window_row(float (&win)[Geo::NIN], const uint32_t addr,
+__device__ __forceinline__ void load_window_row(float (&win)[Geo::NIN], uint32_t &addr,
+                                                const uint32_t pitch, int &q, const int lim,
+                                                const uint32_t zaddr,
                                                 const int (&src_lane)[Geo::NIN],
                                                 const uint32_t (&halo_mask)[Geo::NIN]) {
   float own[VI];
-  SmemLd<T, VI>::ld(addr, own);
+  SmemLd<T, VI>::ld(((unsigned)q < (unsigned)lim) ? addr : zaddr, own);
+  addr += pitch;
+  q += 1;
 #pragma unroll
   for (int ci = 0; ci < Geo::NIN; ++ci) {
     const int c = ci + Geo::CMIN;
@@ -437,31 +436,26 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
 
   if (warp == ROWS_CWARPS) {
     // ------------------------------- producer warp -------------------------------
-    bool aborted = false;
     int it = 0;
     for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
       const int stage = it % ROWS_STAGES;
       const int use = it / ROWS_STAGES;
-      if (use > 0 && !aborted && !mbar_wait_bounded(&ring.empty[stage], (use - 1) & 1)) {
-        aborted = true;
+      if (use > 0 && !mbar_wait_bounded(&ring.empty[stage], (use - 1) & 1)) {
         *ring.abort_flag = 1;
         atomicExch(error_flag, 1);
       }
-      if (aborted || *ring.abort_flag) break;
+      if (*ring.abort_flag) break;
       const ConvTile t = conv_tile<K, S, MODE>(p, tile);
       unsigned char *sb = ring.stage(stage);
-      fence_proxy_async_smem();
-      // the planes' rows: bulk copies go out first, everything below overlaps with them
-      T *data = reinterpret_cast<T *>(sb + p.TAPB);
-      const int elems = (t.in_hi - t.in_lo) * p.Win;
-      const T *src0 = gin + (size_t)t.pg * p.G * plane_in + (size_t)t.in_lo * p.Win;
+      // the tile's rows are one contiguous range of the tensor: one bulk copy, issued first
+      // so that the tap loads below overlap with it
       uint32_t tx = 0;
-      for (int g = lane; g < t.gcount; g += 32)
-        tx += stage_range(data + (size_t)g * p.PS + p.ZT, src0 + (size_t)g * plane_in, elems,
-                          &ring.full[stage]);
-      if (p.NRT > 1 && t.in_hi == p.Hin) {  // last row tile of a plane: rows below the map are zero
-        T *below = data + p.ZT + slot_phase(src0) + elems;
-        for (int i = lane; i < p.ZBF; i += 32) below[i] = Elem<T>::from_acc(0);
+      if (lane == 0) {
+        fence_proxy_async_smem();
+        const int nrows = t.in_hi - t.in_lo;
+        const int elems = (p.NRT == 1) ? t.gcount * (int)plane_in : nrows * p.Win;
+        const T *src0 = gin + (size_t)t.pg * p.G * plane_in + (size_t)t.in_lo * p.Win;
+        tx = stage_range(reinterpret_cast<T *>(sb + p.TAPB + 16), src0, elems, &ring.full[stage]);
       }
       // taps of the tile's planes, fp32, flipped for backward-input; loads batched so that
       // their latencies overlap
@@ -488,7 +482,6 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
           if (idx < ntap) staps[idx] = v[k];
         }
       }
-      tx = warp_sum(tx);
       __syncwarp();
       if (lane == 0) {
         if (tx)
@@ -516,21 +509,23 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
 
   const int ntasks = p.G * p.NRB;
   const uint32_t row_bytes = (uint32_t)p.Win * (uint32_t)sizeof(T);
-  bool aborted = false;
   int it = 0;
   for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
     const int stage = it % ROWS_STAGES;
     const int use = it / ROWS_STAGES;
-    if (!aborted && !mbar_wait_bounded(&ring.full[stage], use & 1)) {
-      aborted = true;
+    if (!mbar_wait_bounded(&ring.full[stage], use & 1)) {
       *ring.abort_flag = 1;
       atomicExch(error_flag, 1);
     }
-    if (aborted || *ring.abort_flag) break;
+    if (*ring.abort_flag) break;
     const ConvTile t = conv_tile<K, S, MODE>(p, tile);
     unsigned char *sb = ring.stage(stage);
     const float *staps = reinterpret_cast<const float *>(sb);
-    const uint32_t sdata = smem_u32(sb + p.TAPB);  // slot 0 starts with >= 16 zero bytes
+    const uint32_t zaddr = smem_u32(sb + p.TAPB);  // 16 bytes that are always zero
+    const int nrows = t.in_hi - t.in_lo;           // staged rows per plane
+    const int phase =
+        slot_phase(gin + (size_t)t.pg * p.G * plane_in + (size_t)t.in_lo * p.Win);
+    const uint32_t sdata = zaddr + 16u + (uint32_t)(phase * (int)sizeof(T));
 
     for (int t0 = 0; t0 < ntasks; t0 += NSEG) {
       const int task = t0 + seg;
@@ -547,31 +542,26 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
 #pragma unroll
         for (int tx = 0; tx < K; ++tx) taps[ty][tx] = active ? staps[g * KK + ty * K + tx] : 0.f;
 
-      // shared address of this lane's block in window row 0, and the row pitch; lanes with
-      // nothing to read sit on the zero margin with pitch 0
-      const int q0 = (MODE == MODE_FWD ? r_begin * S : r_begin / S) + Geo::RMIN - t.in_lo;
-      uint32_t a = sdata;
-      uint32_t pitch = 0;
+      // row index (inside the plane's staged rows) of window row 0, its shared address, and the
+      // row pitch; lanes with nothing to read have lim = 0 and only ever read the zero bytes
+      int q = (MODE == MODE_FWD ? r_begin * S : r_begin / S) + Geo::RMIN - t.in_lo;
+      int lim = 0;
+      uint32_t a = zaddr;
       if (active && in_alive) {
-        const int phase = slot_phase(gin + (size_t)plane * plane_in + (size_t)t.in_lo * p.Win);
-        a = sdata + (uint32_t)((g * p.PS + p.ZT + phase + q0 * p.Win + j * VI) * (int)sizeof(T));
-        pitch = row_bytes;
+        lim = nrows;
+        a = sdata + (uint32_t)(((g * nrows + q) * p.Win + j * VI) * (int)sizeof(T));
       }
       T *orow = gout + (size_t)plane * plane_out + (size_t)r_begin * p.Wout + j * VO;
       int rows_left = (active && out_alive) ? (r_end - r_begin) : 0;
 
       float rows[Geo::KR][Geo::NIN];
 #pragma unroll
-      for (int i = 0; i < Geo::KR - Geo::ADV; ++i) {
-        load_window_row<T, Geo, VI, MASK>(rows[i], a, src_lane, halo_mask);
-        a += pitch;
-      }
+      for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
+        load_window_row<T, Geo, VI, MASK>(rows[i], a, row_bytes, q, lim, zaddr, src_lane, halo_mask);
       for (int rr = 0; rr < p.RBH; rr += U) {
 #pragma unroll
-        for (int i = Geo::KR - Geo::ADV; i < Geo::KR; ++i) {
-          load_window_row<T, Geo, VI, MASK>(rows[i], a, src_lane, halo_mask);
-          a += pitch;
-        }
+        for (int i = Geo::KR - Geo::ADV; i < Geo::KR; ++i)
+          load_window_row<T, Geo, VI, MASK>(rows[i], a, row_bytes, q, lim, zaddr, src_lane, halo_mask);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           float acc[VO];
@@ -613,29 +603,25 @@ struct RowsFilterParams {
   const void *dy;
   float *partial;  // [C][SL][K*K]
   int N, C, H, W, Ho, Wo;
-  int G;    // images (planes of one channel) per tile; whole planes when NRT == 1
-  int NRT;  // row tiles per plane
-  int TH;   // dy rows per row tile
-  int NRB, RBH, LW;
-  int TPC;    // tiles per channel = ceil(N / G) * NRT
-  int SL;     // work items (slices of the tile list) per channel
-  int PS;     // elements per x plane slot, zero margins included
-  int ZT;     // zero elements ahead of an x slot's data
-  int ZBF;    // elements cleared behind the x data of a plane's last row tile
-  int DPL;    // elements per dy plane slot
-  int DYOFF;  // byte offset of the dy slots inside a stage (multiple of 128)
+  int G;      // consecutive channels (planes of one image) per tile; whole planes when NRT == 1
+  int NRT;    // row tiles per plane (G == 1 when > 1)
+  int TH;     // dy rows per row tile
+  int NRB, RBH, LW;  // G * NRB <= segments per CTA: a segment keeps its (channel, row block)
+  int NCG;    // channel groups = ceil(C / G)
+  int TPC;    // tiles per channel group = N * NRT
+  int SL;     // work items (slices of that tile list) per channel group
+  int DYOFF;  // byte offset of the dy rows inside a stage (16-byte aligned); the stage starts
+              // with 16 zero bytes, the x rows follow
 };
 
 struct FilterTile {
-  int n0, gcount, R0, th, in_lo, in_hi;
+  int n, R0, th, in_lo, in_hi;
 };
 template <int K, int S>
 __device__ __forceinline__ FilterTile filter_tile(const RowsFilterParams &p, int tt) {
   FilterTile t;
-  const int ng = tt / p.NRT;
-  const int rt = tt - ng * p.NRT;
-  t.n0 = ng * p.G;
-  t.gcount = min(p.G, p.N - t.n0);
+  t.n = tt / p.NRT;
+  const int rt = tt - t.n * p.NRT;
   t.R0 = rt * p.TH;
   t.th = min(p.TH, p.Ho - t.R0);
   if (p.NRT == 1) {
@@ -647,12 +633,14 @@ __device__ __forceinline__ FilterTile filter_tile(const RowsFilterParams &p, int
   return t;
 }
 
-// Persistent CTAs walk work items (channel c, slice of that channel's (image, row tile) list).
-// Lane layout as in the forward kernel: the x window is the forward window, dy is the lane's VO
-// own output columns.  Each lane keeps K*K accumulators over an item; one warp-shuffle sum and
-// one cross-warp sum in shared memory give the item's partial, written to its own slot (no
-// atomics); a second kernel adds a channel's slices in order.  The copy pipeline runs across
-// item boundaries.
+// Persistent CTAs walk work items (group of G consecutive channels, slice of the (image, row
+// tile) list).  A tile holds the x rows and dy rows of the group's planes in one image: two
+// contiguous ranges, two bulk copies.  Segment s of the CTA owns (channel g, row block rb) =
+// (s / NRB, s % NRB) for the whole item; lane layout as in the forward kernel (the x window is
+// the forward window, dy the lane's VO own output columns).  Each lane keeps K*K accumulators
+// over the item; at its end they are summed over the segment's lanes by shuffle, then over the
+// channel's row blocks through shared memory in a fixed order, and written to the (channel,
+// slice) slot of the partials (no atomics).  A second kernel adds a channel's slices in order.
 template <typename T, int K, int S, int VI, int VO, int U, bool MASK, int MINB>
 __global__ void __launch_bounds__(ROWS_THREADS, MINB)
 rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
@@ -667,49 +655,44 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
   const int warp = threadIdx.x >> 5;
   const size_t plane_x = (size_t)p.H * p.W;
   const size_t plane_dy = (size_t)p.Ho * p.Wo;
-  const int nitems = p.C * p.SL;
+  const int nitems = p.NCG * p.SL;
 
   if (warp == ROWS_CWARPS) {
     // ------------------------------- producer warp -------------------------------
-    bool aborted = false;
+    bool stop = false;
     int it = 0;
-    for (int item = blockIdx.x; item < nitems && !aborted; item += gridDim.x) {
-      const int c = item / p.SL;
-      const int slice = item - c * p.SL;
+    for (int item = blockIdx.x; item < nitems && !stop; item += gridDim.x) {
+      const int cg = item / p.SL;
+      const int slice = item - cg * p.SL;
+      const int c0 = cg * p.G;
+      const int gcount = min(p.G, p.C - c0);
       const int t_begin = (int)(((long long)slice * p.TPC) / p.SL);
       const int t_end = (int)(((long long)(slice + 1) * p.TPC) / p.SL);
       for (int tt = t_begin; tt < t_end; ++tt, ++it) {
         const int stage = it % ROWS_STAGES;
         const int use = it / ROWS_STAGES;
         if (use > 0 && !mbar_wait_bounded(&ring.empty[stage], (use - 1) & 1)) {
-          aborted = true;
           *ring.abort_flag = 1;
           atomicExch(error_flag, 2);
         }
-        if (aborted || *ring.abort_flag) {
-          aborted = true;
+        if (*ring.abort_flag) {
+          stop = true;
           break;
         }
         const FilterTile t = filter_tile<K, S>(p, tt);
         unsigned char *sb = ring.stage(stage);
-        fence_proxy_async_smem();
-        T *xs = reinterpret_cast<T *>(sb);
-        T *ds = reinterpret_cast<T *>(sb + p.DYOFF);
-        const int xe = (t.in_hi - t.in_lo) * p.W;
-        const int de = t.th * p.Wo;
-        const size_t pl0 = (size_t)t.n0 * p.C + c;
-        const T *xsrc0 = gx + pl0 * plane_x + (size_t)t.in_lo * p.W;
-        const T *dsrc0 = gdy + pl0 * plane_dy + (size_t)t.R0 * p.Wo;
+        const size_t pl0 = (size_t)t.n * p.C + c0;
         uint32_t tx = 0;
-        for (int g = lane; g < t.gcount; g += 32) {
-          tx += stage_range(xs + (size_t)g * p.PS + p.ZT, xsrc0 + (size_t)g * p.C * plane_x, xe,
-                            &ring.full[stage]);
-          tx += stage_range(ds + (size_t)g * p.DPL, dsrc0 + (size_t)g * p.C * plane_dy, de,
-                            &ring.full[stage]);
-        }
-        if (p.NRT > 1 && t.in_hi == p.H) {
-          T *below = xs + p.ZT + slot_phase(xsrc0) + xe;
-          for (int i = lane; i < p.ZBF; i += 32) below[i] = Elem<T>::from_acc(0);
+        if (lane == 0) {
+          fence_proxy_async_smem();
+          const int xe = (p.NRT == 1) ? gcount * (int)plane_x : (t.in_hi - t.in_lo) * p.W;
+          tx = stage_range(reinterpret_cast<T *>(sb + 16), gx + pl0 * plane_x + (size_t)t.in_lo * p.W,
+                           xe, &ring.full[stage]);
+        } else if (lane == 1) {
+          fence_proxy_async_smem();
+          const int de = (p.NRT == 1) ? gcount * (int)plane_dy : t.th * p.Wo;
+          tx = stage_range(reinterpret_cast<T *>(sb + p.DYOFF),
+                           gdy + pl0 * plane_dy + (size_t)t.R0 * p.Wo, de, &ring.full[stage]);
         }
         tx = warp_sum(tx);
         __syncwarp();
@@ -729,7 +712,6 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
   const int segs_per_warp = 32 / LW;
   const int j = lane & (LW - 1);
   const int seg = warp * segs_per_warp + lane / LW;
-  const int NSEG = ROWS_CWARPS * segs_per_warp;
   const bool in_alive = j * VI < p.W;
   const bool out_alive = j * VO < p.Wo;
 
@@ -737,18 +719,24 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
   uint32_t halo_mask[Geo::NIN];
   make_lane_tables<Geo, VI>(src_lane, halo_mask, lane, j, p.W);
 
-  const int ntasks = p.G * p.NRB;
+  const int ntasks = p.G * p.NRB;  // <= segments per CTA
+  const int g = seg / p.NRB;       // this segment's channel within the group, and row block
+  const int rb = seg - g * p.NRB;
   const uint32_t row_bytes = (uint32_t)p.W * (uint32_t)sizeof(T);
   const uint32_t drow_bytes = (uint32_t)p.Wo * (uint32_t)sizeof(T);
+  float *red = ring.scratch;  // [ntasks][KK]
   // A warp whose wait expired keeps walking the loops without waiting or computing, so that
   // it still meets the other consumer warps at every consumer_sync().
   bool aborted = false;
   int it = 0;
   for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-    const int c = item / p.SL;
-    const int slice = item - c * p.SL;
+    const int cg = item / p.SL;
+    const int slice = item - cg * p.SL;
+    const int c0 = cg * p.G;
+    const int gcount = min(p.G, p.C - c0);
     const int t_begin = (int)(((long long)slice * p.TPC) / p.SL);
     const int t_end = (int)(((long long)(slice + 1) * p.TPC) / p.SL);
+    const bool active = (seg < ntasks) && (g < gcount);
 
     float acc[K][K];
 #pragma unroll
@@ -767,86 +755,78 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
       if (aborted) continue;
       const FilterTile t = filter_tile<K, S>(p, tt);
       unsigned char *sb = ring.stage(stage);
-      const uint32_t sx = smem_u32(sb);  // x slot 0 starts with >= 16 zero bytes
-      const uint32_t sd = smem_u32(sb + p.DYOFF);
+      const size_t pl0 = (size_t)t.n * p.C + c0;
+      const uint32_t zaddr = smem_u32(sb);  // 16 bytes that are always zero
+      const int nrows = t.in_hi - t.in_lo;
+      const int xphase = slot_phase(gx + pl0 * plane_x + (size_t)t.in_lo * p.W);
+      const int dphase = slot_phase(gdy + pl0 * plane_dy + (size_t)t.R0 * p.Wo);
+      const int drows = (p.NRT == 1) ? p.Ho : t.th;  // staged dy rows per plane
 
-      for (int t0 = 0; t0 < ntasks; t0 += NSEG) {
-        const int task = t0 + seg;
-        const int g = task / p.NRB;
-        const int rb = task - g * p.NRB;
-        const bool active = (task < ntasks) && (g < t.gcount);
-        int r_begin, r_end;
-        task_rows(rb, p.NRB, t.R0, t.th, 1, r_begin, r_end);
+      int r_begin, r_end;
+      task_rows(rb, p.NRB, t.R0, t.th, 1, r_begin, r_end);
+      int q = r_begin * S + Geo::RMIN - t.in_lo;
+      int lim = 0;
+      uint32_t a = zaddr;
+      if (active && in_alive) {
+        lim = nrows;
+        a = zaddr + 16u + (uint32_t)((xphase + (g * nrows + q) * p.W + j * VI) * (int)sizeof(T));
+      }
+      uint32_t da = smem_u32(sb + p.DYOFF) +
+                    (uint32_t)((dphase + ((active ? g : 0) * drows + (r_begin - t.R0)) * p.Wo + j * VO) *
+                               (int)sizeof(T));
+      int rows_left = (active && out_alive) ? (r_end - r_begin) : 0;
 
-        const int q0 = r_begin * S + Geo::RMIN - t.in_lo;
-        uint32_t a = sx;
-        uint32_t pitch = 0;
-        const size_t pl = (size_t)(t.n0 + (active ? g : 0)) * p.C + c;
-        if (active && in_alive) {
-          const int phase = slot_phase(gx + pl * plane_x + (size_t)t.in_lo * p.W);
-          a = sx + (uint32_t)((g * p.PS + p.ZT + phase + q0 * p.W + j * VI) * (int)sizeof(T));
-          pitch = row_bytes;
-        }
-        const int dphase = slot_phase(gdy + pl * plane_dy + (size_t)t.R0 * p.Wo);
-        uint32_t da = sd + (uint32_t)(((active ? g : 0) * p.DPL + dphase + (r_begin - t.R0) * p.Wo +
-                                       j * VO) * (int)sizeof(T));
-        int rows_left = (active && out_alive) ? (r_end - r_begin) : 0;
-
-        float rows[Geo::KR][Geo::NIN];
+      float rows[Geo::KR][Geo::NIN];
 #pragma unroll
-        for (int i = 0; i < Geo::KR - Geo::ADV; ++i) {
-          load_window_row<T, Geo, VI, MASK>(rows[i], a, src_lane, halo_mask);
-          a += pitch;
-        }
-        for (int rr = 0; rr < p.RBH; rr += U) {
+      for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
+        load_window_row<T, Geo, VI, MASK>(rows[i], a, row_bytes, q, lim, zaddr, src_lane, halo_mask);
+      for (int rr = 0; rr < p.RBH; rr += U) {
 #pragma unroll
-          for (int i = Geo::KR - Geo::ADV; i < Geo::KR; ++i) {
-            load_window_row<T, Geo, VI, MASK>(rows[i], a, src_lane, halo_mask);
-            a += pitch;
-          }
+        for (int i = Geo::KR - Geo::ADV; i < Geo::KR; ++i)
+          load_window_row<T, Geo, VI, MASK>(rows[i], a, row_bytes, q, lim, zaddr, src_lane, halo_mask);
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            if (u < rows_left) {  // rows past the task's end must not contribute
-              float dyv[VO];
-              SmemLd<T, VO>::ld(da, dyv);
+        for (int u = 0; u < U; ++u) {
+          if (u < rows_left) {  // rows past the task's end must not contribute
+            float dyv[VO];
+            SmemLd<T, VO>::ld(da, dyv);
 #pragma unroll
-              for (int ty = 0; ty < K; ++ty) {
-                const int ri = Geo::rel(u, ty) - Geo::RMIN;
+            for (int ty = 0; ty < K; ++ty) {
+              const int ri = Geo::rel(u, ty) - Geo::RMIN;
 #pragma unroll
-                for (int tx = 0; tx < K; ++tx)
+              for (int tx = 0; tx < K; ++tx)
 #pragma unroll
-                  for (int e = 0; e < VO; ++e)
-                    acc[ty][tx] = fmaf(dyv[e], rows[ri][Geo::rel(e, tx) - Geo::CMIN], acc[ty][tx]);
-              }
+                for (int e = 0; e < VO; ++e)
+                  acc[ty][tx] = fmaf(dyv[e], rows[ri][Geo::rel(e, tx) - Geo::CMIN], acc[ty][tx]);
             }
-            da += drow_bytes;
           }
-#pragma unroll
-          for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
-#pragma unroll
-            for (int ci = 0; ci < Geo::NIN; ++ci) rows[i][ci] = rows[i + Geo::ADV][ci];
-          rows_left -= U;
+          da += drow_bytes;
         }
+#pragma unroll
+        for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
+#pragma unroll
+          for (int ci = 0; ci < Geo::NIN; ++ci) rows[i][ci] = rows[i + Geo::ADV][ci];
+        rows_left -= U;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&ring.empty[stage]);
     }
 
-    // item done: sum over lanes, then over warps, and publish the slice's partial
-    float *red = ring.scratch;  // [ROWS_CWARPS][KK]
+    // item done: sum over the segment's lanes, then over the channel's row blocks
 #pragma unroll
     for (int ty = 0; ty < K; ++ty)
 #pragma unroll
       for (int tx = 0; tx < K; ++tx) {
-        const float v = warp_sum(acc[ty][tx]);
-        if (lane == 0) red[warp * KK + ty * K + tx] = v;
+        float v = acc[ty][tx];
+        for (int off = LW >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (j == 0 && seg < ntasks) red[seg * KK + ty * K + tx] = v;
       }
     consumer_sync();
-    if (threadIdx.x < KK) {
+    for (int idx = threadIdx.x; idx < gcount * KK; idx += ROWS_CWARPS * 32) {
+      const int gg = idx / KK;
+      const int tap = idx - gg * KK;
       float s = 0.f;
-#pragma unroll
-      for (int w = 0; w < ROWS_CWARPS; ++w) s += red[w * KK + threadIdx.x];
-      p.partial[((size_t)c * p.SL + slice) * KK + threadIdx.x] = s;
+      for (int b = 0; b < p.NRB; ++b) s += red[(gg * p.NRB + b) * KK + tap];
+      p.partial[((size_t)(c0 + gg) * p.SL + slice) * KK + tap] = s;
     }
     consumer_sync();  // red is rewritten by the next item
   }

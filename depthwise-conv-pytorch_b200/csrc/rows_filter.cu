@@ -55,19 +55,20 @@ bool plan_filter_ks(const Shape &s, bool a16, FilterPlan &f) {
   p.LW = pick_lw(lanes);
   if (p.LW == 0) return false;
   PlanInput in{K, S, MODE_FWD, s.H, s.W, s.Ho, s.Wo, (int)sizeof(T),
-               ROWS_CWARPS * (32 / p.LW), false, true};
+               ROWS_CWARPS * (32 / p.LW), s.C, true};
   const TilePlan t = plan_best(in, FilterU<K, S>::v, FilterU<K, S>::n);
   if (!t.ok) return false;
   p.N = s.N; p.C = s.C; p.H = s.H; p.W = s.W; p.Ho = s.Ho; p.Wo = s.Wo;
   p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;
-  p.PS = t.PS; p.ZT = t.ZT; p.ZBF = t.ZBF; p.DPL = t.DPL; p.DYOFF = t.DYOFF;
+  p.DYOFF = t.DYOFF;
   f.U = t.U;
-  const long long tpc = (long long)ceil_div(s.N, p.G) * p.NRT;
+  const long long tpc = (long long)s.N * p.NRT;
   if (tpc > (1ll << 30)) return false;
   p.TPC = (int)tpc;
+  p.NCG = ceil_div(s.C, p.G);
   // enough work items for ~2 per resident CTA, at least one tile each
   const int slots = sm_count() * filter_minb(K);
-  int SL = ceil_div(2 * slots, s.C);
+  int SL = ceil_div(2 * slots, p.NCG);
   if (SL > p.TPC) SL = p.TPC;
   if (SL < 1) SL = 1;
   p.SL = SL;
@@ -115,7 +116,7 @@ int launch_variant(const RowsFilterParams &p, cudaStream_t st) {
   if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
   int *flag = filter_flag_address();
   if (flag == nullptr) return ROWS_DECLINED;
-  const long long items = (long long)p.C * p.SL;
+  const long long items = (long long)p.NCG * p.SL;
   const int grid = (int)min((long long)sm_count() * MINB, items);
   kernel<<<grid, ROWS_THREADS, ROWS_SMEM_BYTES, st>>>(p, flag);
   return ROWS_SERVED;
@@ -213,8 +214,8 @@ int rows_debug_filter_plan(int esize, const Shape &s, int a16, int *out) {
   bool ok = esize == 4 ? plan_filter<float>(s, a16 != 0, f) : plan_filter<__half>(s, a16 != 0, f);
   if (!ok) return 0;
   const RowsFilterParams &p = f.p;
-  const int v[24] = {f.VI, f.VO, f.U, f.mask ? 1 : 0, p.LW, p.G, p.NRT, p.TH, p.NRB, p.RBH, p.PS, p.ZT,
-                     p.ZBF, 0, p.DPL, p.DYOFF, p.TPC, p.SL, 0, 0, 0, 0, 0, 0};
+  const int v[24] = {f.VI, f.VO, f.U, f.mask ? 1 : 0, p.LW, p.G, p.NRT, p.TH, p.NRB, p.RBH, 0, 0,
+                     0, 0, 0, p.DYOFF, p.TPC, p.SL, 0, p.NCG, 0, 0, 0, 0};
   for (int i = 0; i < 24; ++i) out[i] = v[i];
   return 1;
 }

@@ -48,8 +48,9 @@ struct PlanInput {
   int Hout, Wout;    // rows the tasks iterate over / their width
   int esize;         // bytes per element
   int NSEG;          // segments per CTA
-  bool taps;         // the stage holds the tile's taps (forward / backward-input)
-  bool stage_out;    // the stage also holds the Hout x Wout map (backward-filter: dy)
+  int maxG;          // planes that can share a tile (forward: N*C; backward-filter: C)
+  bool filter;       // backward-filter: the stage also holds the Hout x Wout rows (dy), no taps,
+                     // and a segment keeps one task for a whole item (G * NRB <= NSEG)
 };
 
 // One tiling of the problem for a given rows-per-chunk U.
@@ -57,21 +58,21 @@ struct TilePlan {
   bool ok;
   int U;
   int G, NRT, TH, NRB, RBH;
-  int PS, ZT, ZBF, TAPB, DPL, DYOFF;
+  int TAPB, DYOFF;
   int bytes;   // stage bytes in use
   double eff;  // useful output rows / segment-row slots spent
 };
 
-inline int plan_base_row(int mode, int S, int r) { return mode == MODE_FWD ? r * S : r / S; }
-
-// Fills margins / slot sizes for a candidate (G, NRT, TH, NRB) and scores it.
+// Fills RBH and the stage layout for a candidate (G, NRT, TH, NRB) and scores it.
 inline bool plan_finish(const PlanInput &in, int U, TilePlan &t) {
   const int RS = (in.mode == MODE_BWD) ? in.S : 1;
-  const int RMIN = geo_min_rel(in.K, in.S, in.mode, U), RMAX = geo_max_rel(in.K, in.S, in.mode, U);
   const int b = in.esize;
-  int lenmax = 0;
+  int lenmax = 0, rows_in = 0;
   for (int rt = 0; rt < t.NRT; ++rt) {
     const int R0 = rt * t.TH, th = (in.Hout - R0 < t.TH) ? in.Hout - R0 : t.TH;
+    int lo = 0, hi = in.Hin;
+    if (t.NRT > 1) tile_in_rows(in.K, in.S, in.mode, R0, th, in.Hin, lo, hi);
+    if (hi - lo > rows_in) rows_in = hi - lo;
     for (int rb = 0; rb < t.NRB; ++rb) {
       int r0, r1;
       task_rows(rb, t.NRB, R0, th, RS, r0, r1);
@@ -79,38 +80,15 @@ inline bool plan_finish(const PlanInput &in, int U, TilePlan &t) {
     }
   }
   if (lenmax <= 0) return false;
+  if (in.filter && t.G * t.NRB > in.NSEG) return false;
   t.RBH = round_up(lenmax, U);
-  int qmin = 0, rows_need = 0;
-  for (int rt = 0; rt < t.NRT; ++rt) {
-    const int R0 = rt * t.TH, th = (in.Hout - R0 < t.TH) ? in.Hout - R0 : t.TH;
-    int lo = 0, hi = in.Hin;
-    if (t.NRT > 1) tile_in_rows(in.K, in.S, in.mode, R0, th, in.Hin, lo, hi);
-    int need = hi - lo;
-    if (t.NRT > 1 && hi == in.Hin) need += in.K;  // cleared rows below the map
-    for (int rb = 0; rb < t.NRB; ++rb) {
-      int r0, r1;
-      task_rows(rb, t.NRB, R0, th, RS, r0, r1);
-      const int q0 = plan_base_row(in.mode, in.S, r0) + RMIN - lo;
-      const int q1 = plan_base_row(in.mode, in.S, r0 + t.RBH - U) + RMAX - lo;  // last row read
-      if (q0 < qmin) qmin = q0;
-      if (q1 + 1 > need) need = q1 + 1;
-    }
-    if (need > rows_need) rows_need = need;
-  }
-  const int above_bytes = (-qmin) * in.Win * b;
-  t.ZT = round_up(above_bytes < 16 ? 16 : above_bytes, 16) / b;
-  // + 32 bytes: the data may sit up to 15 bytes behind the slot's aligned start (it keeps its
-  // source's phase) and 16 bytes behind it are cleared
-  t.PS = round_up((t.ZT + rows_need * in.Win) * b + 32, 16) / b;
-  t.ZBF = (t.NRT > 1) ? in.K * in.Win : 0;
-  t.TAPB = in.taps ? round_up(t.G * in.K * in.K * 4, 128) : 0;
-  int total = t.TAPB + t.G * t.PS * b;
-  t.DPL = 0;
+  // stage: [taps][16 zero bytes][rows, up to 15 bytes behind their aligned start]
+  t.TAPB = in.filter ? 0 : round_up(t.G * in.K * in.K * 4, 128);
+  int total = t.TAPB + 16 + 16 + t.G * rows_in * in.Win * b;
   t.DYOFF = 0;
-  if (in.stage_out) {
-    t.DYOFF = round_up(total, 128);
-    t.DPL = round_up(t.TH * in.Wout * b + 32, 16) / b;
-    total = t.DYOFF + t.G * t.DPL * b;
+  if (in.filter) {
+    t.DYOFF = round_up(total, 16);
+    total = t.DYOFF + 16 + t.G * t.TH * in.Wout * b;
   }
   t.bytes = total;
   if (total > ROWS_STAGE_BYTES) return false;
@@ -135,7 +113,10 @@ inline TilePlan plan_for_u(const PlanInput &in, int U) {
     return true;
   };
   // whole planes: every group size up to four rounds of segments
-  for (int G = 4 * in.NSEG; G >= 1; --G) {
+  int gmax = 4 * in.NSEG;
+  if (in.filter) gmax = in.NSEG;
+  if (gmax > in.maxG) gmax = in.maxG;
+  for (int G = gmax; G >= 1; --G) {
     const int nrb_max = (G >= in.NSEG) ? 1 : in.NSEG / G;
     for (int NRB = 1; NRB <= nrb_max; ++NRB) {
       if (NRB > 1 && NRB * RS > in.Hout) break;
@@ -184,7 +165,7 @@ inline TilePlan plan_best(const PlanInput &in, const int *u_options, int n_optio
   static std::mutex mu;
   static std::vector<Entry> table;
   int key[16] = {in.K, in.S, in.mode, in.Hin, in.Win, in.Hout, in.Wout, in.esize, in.NSEG,
-                 in.taps ? 1 : 0, in.stage_out ? 1 : 0, n_options, 0, 0, 0, 0};
+                 in.maxG, in.filter ? 1 : 0, n_options, 0, 0, 0, 0};
   for (int i = 0; i < n_options && i < 4; ++i) key[12 + i] = u_options[i];
   {
     std::lock_guard<std::mutex> lock(mu);
