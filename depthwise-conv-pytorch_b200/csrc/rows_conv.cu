@@ -19,15 +19,15 @@ constexpr int conv_minb(int K) { return K <= 5 ? 2 : 1; }
 
 // Rows-per-chunk choices compiled for each (K, S, MODE); the planner picks per shape.
 template <int K, int S, int MODE> struct ConvU;
-template <> struct ConvU<3, 1, MODE_FWD> { static constexpr int n = 2; static constexpr int v[2] = {4, 7}; };
-template <> struct ConvU<5, 1, MODE_FWD> { static constexpr int n = 2; static constexpr int v[2] = {4, 7}; };
-template <> struct ConvU<7, 1, MODE_FWD> { static constexpr int n = 1; static constexpr int v[2] = {2, 2}; };
-template <> struct ConvU<3, 2, MODE_FWD> { static constexpr int n = 2; static constexpr int v[2] = {2, 7}; };
-template <> struct ConvU<5, 2, MODE_FWD> { static constexpr int n = 2; static constexpr int v[2] = {2, 4}; };
-template <> struct ConvU<7, 2, MODE_FWD> { static constexpr int n = 1; static constexpr int v[2] = {2, 2}; };
-template <> struct ConvU<3, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[2] = {4, 14}; };
-template <> struct ConvU<5, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[2] = {4, 14}; };
-template <> struct ConvU<7, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[2] = {2, 4}; };
+template <> struct ConvU<3, 1, MODE_FWD> { static constexpr int n = 3; static constexpr int v[3] = {4, 7, 14}; };
+template <> struct ConvU<5, 1, MODE_FWD> { static constexpr int n = 2; static constexpr int v[3] = {4, 7, 7}; };
+template <> struct ConvU<7, 1, MODE_FWD> { static constexpr int n = 1; static constexpr int v[3] = {2, 2, 2}; };
+template <> struct ConvU<3, 2, MODE_FWD> { static constexpr int n = 2; static constexpr int v[3] = {2, 7, 7}; };
+template <> struct ConvU<5, 2, MODE_FWD> { static constexpr int n = 2; static constexpr int v[3] = {2, 4, 4}; };
+template <> struct ConvU<7, 2, MODE_FWD> { static constexpr int n = 1; static constexpr int v[3] = {2, 2, 2}; };
+template <> struct ConvU<3, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[3] = {4, 14, 14}; };
+template <> struct ConvU<5, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[3] = {4, 14, 14}; };
+template <> struct ConvU<7, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[3] = {2, 4, 4}; };
 
 int *conv_flag_address() {
   static std::atomic<int *> cached[64];
@@ -85,12 +85,15 @@ int launch_conv(RowsParams p, cudaStream_t st) {
     for (int i = 0; i < 24; ++i) t_plan_out[i] = v[i];
     return ROWS_SERVED;
   }
-  constexpr int U0 = ConvU<K, S, MODE>::v[0], U1 = ConvU<K, S, MODE>::v[1];
+  constexpr int U0 = ConvU<K, S, MODE>::v[0], U1 = ConvU<K, S, MODE>::v[1], U2 = ConvU<K, S, MODE>::v[2];
   if (t.U == U0)
     return mask ? launch_variant<T, K, S, MODE, VI, VO, U0, true>(p, st)
                 : launch_variant<T, K, S, MODE, VI, VO, U0, false>(p, st);
-  return mask ? launch_variant<T, K, S, MODE, VI, VO, U1, true>(p, st)
-              : launch_variant<T, K, S, MODE, VI, VO, U1, false>(p, st);
+  if (t.U == U1)
+    return mask ? launch_variant<T, K, S, MODE, VI, VO, U1, true>(p, st)
+                : launch_variant<T, K, S, MODE, VI, VO, U1, false>(p, st);
+  return mask ? launch_variant<T, K, S, MODE, VI, VO, U2, true>(p, st)
+              : launch_variant<T, K, S, MODE, VI, VO, U2, false>(p, st);
 }
 
 // Picks the widest per-lane vector the widths and pointers allow.

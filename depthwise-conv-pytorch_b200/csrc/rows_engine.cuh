@@ -42,8 +42,14 @@ enum { MODE_FWD = 0, MODE_BWD = 1 };
 
 constexpr int ROWS_CWARPS = 7;                        // consumer warps
 constexpr int ROWS_THREADS = (ROWS_CWARPS + 1) * 32;  // + 1 producer warp
-constexpr int ROWS_STAGES = 3;
-constexpr int ROWS_STAGE_BYTES = 32 * 1024;
+#ifndef ROWS_STAGES_CFG
+#define ROWS_STAGES_CFG 3
+#endif
+#ifndef ROWS_STAGE_KB_CFG
+#define ROWS_STAGE_KB_CFG 32
+#endif
+constexpr int ROWS_STAGES = ROWS_STAGES_CFG;
+constexpr int ROWS_STAGE_BYTES = ROWS_STAGE_KB_CFG * 1024;
 constexpr int ROWS_TAIL_BYTES = 8192;  // barriers, flags, cross-segment reduction scratch
 constexpr int ROWS_SMEM_BYTES = ROWS_STAGES * ROWS_STAGE_BYTES + ROWS_TAIL_BYTES;
 constexpr unsigned ROWS_WAIT_LIMIT = 1u << 22;  // mbarrier polls before giving up
@@ -188,8 +194,8 @@ struct RowsParams {
   int NRB;   // row blocks (tasks) per plane inside a tile
   int RBH;   // row-loop trip count of a task, a multiple of U
   int LW;    // lanes per segment: 8, 16 or 32
-  int TAPB;  // bytes at the head of a stage that hold the tile's taps (fp32); 16 zero bytes
-             // follow, then the tile's rows
+  int TAPB;  // bytes at the head of a stage that hold the taps of the tile's channels; 16 zero
+             // bytes follow, then the tile's rows
   int ntiles;
   int flip;  // apply the filter flipped in both axes (backward-input)
 };
@@ -354,18 +360,23 @@ __device__ __forceinline__ uint32_t stage_range(T *dst16, const T *src, int n, u
 // MASK: the segment has no spare zero lanes on its sides, halo values crossing the map edge
 // must be masked explicitly.
 // ---------------------------------------------------------------------------------------
-// `q` is the row's index inside the staged rows of the lane's plane; rows outside [0, lim) are
-// the zero padding above / below the map and are read from the stage's zero bytes instead.
-template <typename T, typename Geo, int VI, bool MASK>
-__device__ __forceinline__ void load_window_row(float (&win)[Geo::NIN], uint32_t &addr,
-                                                const uint32_t pitch, int &q, const int lim,
-                                                const uint32_t zaddr,
-                                                const int (&src_lane)[Geo::NIN],
-                                                const uint32_t (&halo_mask)[Geo::NIN]) {
-  float own[VI];
+// A window row is fetched in two steps so that a chunk can issue all its shared-memory loads
+// back to back before the first dependent shuffle.
+// Step 1: the lane's own VI columns.  `q` is the row's index inside the staged rows of the
+// lane's plane; rows outside [0, lim) are the zero padding above / below the map and are read
+// from the stage's zero bytes instead.
+template <typename T, int VI>
+__device__ __forceinline__ void load_own_row(float (&own)[VI], uint32_t &addr, const uint32_t pitch,
+                                             int &q, const int lim, const uint32_t zaddr) {
   SmemLd<T, VI>::ld(((unsigned)q < (unsigned)lim) ? addr : zaddr, own);
   addr += pitch;
   q += 1;
+}
+// Step 2: the halo columns from the neighbouring lanes.
+template <typename Geo, int VI, bool MASK>
+__device__ __forceinline__ void build_window_row(float (&win)[Geo::NIN], const float (&own)[VI],
+                                                 const int (&src_lane)[Geo::NIN],
+                                                 const uint32_t (&halo_mask)[Geo::NIN]) {
 #pragma unroll
   for (int ci = 0; ci < Geo::NIN; ++ci) {
     const int c = ci + Geo::CMIN;
@@ -415,6 +426,29 @@ __device__ __forceinline__ ConvTile conv_tile(const RowsParams &p, int tile) {
   return t;
 }
 
+// Where the taps of a tile's channels sit in the stage.  Channels c_base .. c_base+count-1
+// (mod C): range A = [c_base, min(C, c_base+count)), range B = the wrapped remainder [0, nB).
+// Each range keeps its source's 16-byte phase; B starts on the next 16-byte boundary behind A.
+struct TapLayout {
+  int c_base, nA, nB;
+  int phaseA, phaseB;  // elements
+  int offB16;          // element offset of B's aligned start
+  bool direct;         // false: count > C, the producer gathers taps[g*KK + t] with plain loads
+};
+template <typename T, int KK>
+__device__ __forceinline__ TapLayout tap_layout(const T *gw, int first_plane, int count, int C) {
+  constexpr int EPB = 16 / (int)sizeof(T);
+  TapLayout l;
+  l.c_base = first_plane % C;
+  l.direct = count <= C;
+  l.nA = min(count, C - l.c_base);
+  l.nB = l.direct ? count - l.nA : 0;
+  l.phaseA = slot_phase(gw + (size_t)l.c_base * KK);
+  l.phaseB = slot_phase(gw);
+  l.offB16 = (l.phaseA + l.nA * KK + EPB - 1) / EPB * EPB;
+  return l;
+}
+
 // ---------------------------------------------------------------------------------------
 // forward / backward-input
 // ---------------------------------------------------------------------------------------
@@ -457,31 +491,27 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
         const T *src0 = gin + (size_t)t.pg * p.G * plane_in + (size_t)t.in_lo * p.Win;
         tx = stage_range(reinterpret_cast<T *>(sb + p.TAPB + 16), src0, elems, &ring.full[stage]);
       }
-      // taps of the tile's planes, fp32, flipped for backward-input; loads batched so that
-      // their latencies overlap
-      float *staps = reinterpret_cast<float *>(sb);
-      const int ntap = t.gcount * KK;
-      const int c_base = (int)(((long long)t.pg * p.G) % p.C);
-      constexpr int TB = 8;
-      for (int base = 0; base < ntap; base += 32 * TB) {
-        float v[TB];
-#pragma unroll
-        for (int k = 0; k < TB; ++k) {
-          const int idx = base + k * 32 + lane;
-          v[k] = 0.f;
-          if (idx < ntap) {
-            const int g = idx / KK;
-            const int tp = idx - g * KK;
-            const int c = (c_base + g) % p.C;
-            v[k] = Elem<T>::ld(gw + (size_t)c * KK + (p.flip ? (KK - 1 - tp) : tp));
-          }
+      // taps of the tile's channels: consecutive channels are one contiguous range of the
+      // filter tensor (two when the group wraps past the last channel), so they are bulk
+      // copies too, issued by lanes 1 and 2
+      const TapLayout tl = tap_layout<T, KK>(gw, t.pg * p.G, t.gcount, p.C);
+      T *staps = reinterpret_cast<T *>(sb);
+      if (tl.direct) {
+        if (lane == 1) {
+          fence_proxy_async_smem();
+          tx = stage_range(staps, gw + (size_t)tl.c_base * KK, tl.nA * KK, &ring.full[stage]);
+        } else if (lane == 2 && tl.nB > 0) {
+          fence_proxy_async_smem();
+          tx = stage_range(staps + tl.offB16, gw, tl.nB * KK, &ring.full[stage]);
         }
-#pragma unroll
-        for (int k = 0; k < TB; ++k) {
-          const int idx = base + k * 32 + lane;
-          if (idx < ntap) staps[idx] = v[k];
+      } else {
+        // more planes in the tile than channels in the tensor: gather with plain loads
+        for (int idx = lane; idx < t.gcount * KK; idx += 32) {
+          const int g = idx / KK;
+          staps[idx] = gw[(size_t)((tl.c_base + g) % p.C) * KK + (idx - g * KK)];
         }
       }
+      tx = warp_sum(tx);
       __syncwarp();
       if (lane == 0) {
         if (tx)
@@ -520,7 +550,8 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
     if (*ring.abort_flag) break;
     const ConvTile t = conv_tile<K, S, MODE>(p, tile);
     unsigned char *sb = ring.stage(stage);
-    const float *staps = reinterpret_cast<const float *>(sb);
+    const T *staps = reinterpret_cast<const T *>(sb);
+    const TapLayout tl = tap_layout<T, KK>(gw, t.pg * p.G, t.gcount, p.C);
     const uint32_t zaddr = smem_u32(sb + p.TAPB);  // 16 bytes that are always zero
     const int nrows = t.in_hi - t.in_lo;           // staged rows per plane
     const int phase =
@@ -537,10 +568,22 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
       task_rows(rb, p.NRB, t.R0, t.th, RS, r_begin, r_end);
 
       float taps[K][K];
+      {
+        // this plane's taps in the stage; backward-input reads them back to front
+        const int cw = tl.c_base + g;
+        const T *tp = staps;
+        if (active) {
+          tp = !tl.direct ? staps + g * KK
+               : (cw < p.C) ? staps + tl.phaseA + g * KK
+                            : staps + tl.offB16 + tl.phaseB + (cw - p.C) * KK;
+        }
+        const int t_first = p.flip ? KK - 1 : 0, t_step = p.flip ? -1 : 1;
 #pragma unroll
-      for (int ty = 0; ty < K; ++ty)
+        for (int ty = 0; ty < K; ++ty)
 #pragma unroll
-        for (int tx = 0; tx < K; ++tx) taps[ty][tx] = active ? staps[g * KK + ty * K + tx] : 0.f;
+          for (int tx = 0; tx < K; ++tx)
+            taps[ty][tx] = active ? Elem<T>::to_acc(tp[t_first + t_step * (ty * K + tx)]) : 0.f;
+      }
 
       // row index (inside the plane's staged rows) of window row 0, its shared address, and the
       // row pitch; lanes with nothing to read have lim = 0 and only ever read the zero bytes
@@ -555,13 +598,24 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
       int rows_left = (active && out_alive) ? (r_end - r_begin) : 0;
 
       float rows[Geo::KR][Geo::NIN];
+      {
+        float own[Geo::KR - Geo::ADV][VI];
 #pragma unroll
-      for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
-        load_window_row<T, Geo, VI, MASK>(rows[i], a, row_bytes, q, lim, zaddr, src_lane, halo_mask);
+        for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
+          load_own_row<T, VI>(own[i], a, row_bytes, q, lim, zaddr);
+#pragma unroll
+        for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
+          build_window_row<Geo, VI, MASK>(rows[i], own[i], src_lane, halo_mask);
+      }
       for (int rr = 0; rr < p.RBH; rr += U) {
+        {
+          float own[Geo::ADV][VI];
 #pragma unroll
-        for (int i = Geo::KR - Geo::ADV; i < Geo::KR; ++i)
-          load_window_row<T, Geo, VI, MASK>(rows[i], a, row_bytes, q, lim, zaddr, src_lane, halo_mask);
+          for (int i = 0; i < Geo::ADV; ++i) load_own_row<T, VI>(own[i], a, row_bytes, q, lim, zaddr);
+#pragma unroll
+          for (int i = 0; i < Geo::ADV; ++i)
+            build_window_row<Geo, VI, MASK>(rows[Geo::KR - Geo::ADV + i], own[i], src_lane, halo_mask);
+        }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           float acc[VO];
@@ -777,18 +831,34 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
       int rows_left = (active && out_alive) ? (r_end - r_begin) : 0;
 
       float rows[Geo::KR][Geo::NIN];
+      {
+        float own[Geo::KR - Geo::ADV][VI];
 #pragma unroll
-      for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
-        load_window_row<T, Geo, VI, MASK>(rows[i], a, row_bytes, q, lim, zaddr, src_lane, halo_mask);
+        for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
+          load_own_row<T, VI>(own[i], a, row_bytes, q, lim, zaddr);
+#pragma unroll
+        for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
+          build_window_row<Geo, VI, MASK>(rows[i], own[i], src_lane, halo_mask);
+      }
       for (int rr = 0; rr < p.RBH; rr += U) {
+        {
+          float own[Geo::ADV][VI];
 #pragma unroll
-        for (int i = Geo::KR - Geo::ADV; i < Geo::KR; ++i)
-          load_window_row<T, Geo, VI, MASK>(rows[i], a, row_bytes, q, lim, zaddr, src_lane, halo_mask);
+          for (int i = 0; i < Geo::ADV; ++i) load_own_row<T, VI>(own[i], a, row_bytes, q, lim, zaddr);
+#pragma unroll
+          for (int i = 0; i < Geo::ADV; ++i)
+            build_window_row<Geo, VI, MASK>(rows[Geo::KR - Geo::ADV + i], own[i], src_lane, halo_mask);
+        }
+        float dys[U][VO];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          SmemLd<T, VO>::ld((u < rows_left) ? da : zaddr, dys[u]);
+          da += drow_bytes;
+        }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           if (u < rows_left) {  // rows past the task's end must not contribute
-            float dyv[VO];
-            SmemLd<T, VO>::ld(da, dyv);
+            const float (&dyv)[VO] = dys[u];
 #pragma unroll
             for (int ty = 0; ty < K; ++ty) {
               const int ri = Geo::rel(u, ty) - Geo::RMIN;
@@ -799,7 +869,6 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
                   acc[ty][tx] = fmaf(dyv[e], rows[ri][Geo::rel(e, tx) - Geo::CMIN], acc[ty][tx]);
             }
           }
-          da += drow_bytes;
         }
 #pragma unroll
         for (int i = 0; i < Geo::KR - Geo::ADV; ++i)

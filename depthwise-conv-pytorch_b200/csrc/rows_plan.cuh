@@ -83,7 +83,8 @@ inline bool plan_finish(const PlanInput &in, int U, TilePlan &t) {
   if (in.filter && t.G * t.NRB > in.NSEG) return false;
   t.RBH = round_up(lenmax, U);
   // stage: [taps][16 zero bytes][rows, up to 15 bytes behind their aligned start]
-  t.TAPB = in.filter ? 0 : round_up(t.G * in.K * in.K * 4, 128);
+  // taps: up to two ranges, each up to 15 bytes behind a 16-byte boundary
+  t.TAPB = in.filter ? 0 : round_up(t.G * in.K * in.K * b + 48, 128);
   int total = t.TAPB + 16 + 16 + t.G * rows_in * in.Win * b;
   t.DYOFF = 0;
   if (in.filter) {
