@@ -19,15 +19,15 @@ constexpr int conv_minb(int K) { return K <= 5 ? 2 : 1; }
 
 // Rows-per-chunk choices compiled for each (K, S, MODE); the planner picks per shape.
 template <int K, int S, int MODE> struct ConvU;
-template <> struct ConvU<3, 1, MODE_FWD> { static constexpr int n = 3; static constexpr int v[3] = {4, 7, 14}; };
-template <> struct ConvU<5, 1, MODE_FWD> { static constexpr int n = 2; static constexpr int v[3] = {4, 7, 7}; };
-template <> struct ConvU<7, 1, MODE_FWD> { static constexpr int n = 1; static constexpr int v[3] = {2, 2, 2}; };
-template <> struct ConvU<3, 2, MODE_FWD> { static constexpr int n = 2; static constexpr int v[3] = {2, 7, 7}; };
-template <> struct ConvU<5, 2, MODE_FWD> { static constexpr int n = 2; static constexpr int v[3] = {2, 4, 4}; };
-template <> struct ConvU<7, 2, MODE_FWD> { static constexpr int n = 1; static constexpr int v[3] = {2, 2, 2}; };
-template <> struct ConvU<3, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[3] = {4, 14, 14}; };
-template <> struct ConvU<5, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[3] = {4, 14, 14}; };
-template <> struct ConvU<7, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[3] = {2, 4, 4}; };
+template <> struct ConvU<3, 1, MODE_FWD> { static constexpr int n = 4; static constexpr int v[4] = {4, 7, 8, 14}; };
+template <> struct ConvU<5, 1, MODE_FWD> { static constexpr int n = 2; static constexpr int v[4] = {4, 7, 7, 7}; };
+template <> struct ConvU<7, 1, MODE_FWD> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };
+template <> struct ConvU<3, 2, MODE_FWD> { static constexpr int n = 3; static constexpr int v[4] = {2, 4, 7, 7}; };
+template <> struct ConvU<5, 2, MODE_FWD> { static constexpr int n = 2; static constexpr int v[4] = {2, 4, 4, 4}; };
+template <> struct ConvU<7, 2, MODE_FWD> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };
+template <> struct ConvU<3, 2, MODE_BWD> { static constexpr int n = 3; static constexpr int v[4] = {4, 8, 14, 14}; };
+template <> struct ConvU<5, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[4] = {4, 14, 14, 14}; };
+template <> struct ConvU<7, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[4] = {2, 4, 4, 4}; };
 
 int *conv_flag_address() {
   static std::atomic<int *> cached[64];
@@ -44,10 +44,10 @@ int *conv_flag_address() {
   return p;
 }
 
-template <typename T, int K, int S, int MODE, int VI, int VO, int U, bool MASK>
+template <typename T, int K, int S, int MODE, int VI, int VO, int U, bool MASK, bool EXACT>
 int launch_variant(const RowsParams &p, cudaStream_t st) {
   constexpr int MINB = conv_minb(K);
-  auto kernel = rows_conv_kernel<T, K, S, MODE, VI, VO, U, MASK, MINB>;
+  auto kernel = rows_conv_kernel<T, K, S, MODE, VI, VO, U, MASK, EXACT, MINB>;
   static std::atomic<unsigned long long> smem_done{0};
   if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
   int *flag = conv_flag_address();
@@ -55,6 +55,23 @@ int launch_variant(const RowsParams &p, cudaStream_t st) {
   const int grid = (int)min((long long)sm_count() * MINB, (long long)p.ntiles);
   kernel<<<grid, ROWS_THREADS, ROWS_SMEM_BYTES, st>>>(p, flag);
   return ROWS_SERVED;
+}
+
+// Dispatch on the planner's runtime choices (U among the compiled options, mask, exact).
+template <typename T, int K, int S, int MODE, int VI, int VO, int I>
+int launch_u(const RowsParams &p, int U, bool mask, bool exact, cudaStream_t st) {
+  constexpr int UI = ConvU<K, S, MODE>::v[I];
+  if (U == UI || I + 1 >= ConvU<K, S, MODE>::n) {
+    if (mask)
+      return exact ? launch_variant<T, K, S, MODE, VI, VO, UI, true, true>(p, st)
+                   : launch_variant<T, K, S, MODE, VI, VO, UI, true, false>(p, st);
+    return exact ? launch_variant<T, K, S, MODE, VI, VO, UI, false, true>(p, st)
+                 : launch_variant<T, K, S, MODE, VI, VO, UI, false, false>(p, st);
+  }
+  if constexpr (I + 1 < ConvU<K, S, MODE>::n)
+    return launch_u<T, K, S, MODE, VI, VO, I + 1>(p, U, mask, exact, st);
+  else
+    return ROWS_DECLINED;
 }
 
 template <typename T, int K, int S, int MODE, int VI, int VO>
@@ -69,6 +86,7 @@ int launch_conv(RowsParams p, cudaStream_t st) {
   const TilePlan t = plan_best(in, ConvU<K, S, MODE>::v, ConvU<K, S, MODE>::n);
   if (!t.ok) return ROWS_DECLINED;
   p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;
+  p.inv_NRB = magic_of(p.NRB);
   p.TAPB = t.TAPB;
   const long long ntiles = (long long)ceil_div(p.NC, p.G) * p.NRT;
   if (ntiles > (1ll << 30)) return ROWS_DECLINED;
@@ -85,15 +103,7 @@ int launch_conv(RowsParams p, cudaStream_t st) {
     for (int i = 0; i < 24; ++i) t_plan_out[i] = v[i];
     return ROWS_SERVED;
   }
-  constexpr int U0 = ConvU<K, S, MODE>::v[0], U1 = ConvU<K, S, MODE>::v[1], U2 = ConvU<K, S, MODE>::v[2];
-  if (t.U == U0)
-    return mask ? launch_variant<T, K, S, MODE, VI, VO, U0, true>(p, st)
-                : launch_variant<T, K, S, MODE, VI, VO, U0, false>(p, st);
-  if (t.U == U1)
-    return mask ? launch_variant<T, K, S, MODE, VI, VO, U1, true>(p, st)
-                : launch_variant<T, K, S, MODE, VI, VO, U1, false>(p, st);
-  return mask ? launch_variant<T, K, S, MODE, VI, VO, U2, true>(p, st)
-              : launch_variant<T, K, S, MODE, VI, VO, U2, false>(p, st);
+  return launch_u<T, K, S, MODE, VI, VO, 0>(p, t.U, mask, t.exact, st);
 }
 
 // Picks the widest per-lane vector the widths and pointers allow.

@@ -52,7 +52,8 @@ constexpr int ROWS_STAGES = ROWS_STAGES_CFG;
 constexpr int ROWS_STAGE_BYTES = ROWS_STAGE_KB_CFG * 1024;
 constexpr int ROWS_TAIL_BYTES = 8192;  // barriers, flags, cross-segment reduction scratch
 constexpr int ROWS_SMEM_BYTES = ROWS_STAGES * ROWS_STAGE_BYTES + ROWS_TAIL_BYTES;
-constexpr unsigned ROWS_WAIT_LIMIT = 1u << 22;  // mbarrier polls before giving up
+constexpr unsigned ROWS_WAIT_LIMIT = 1u << 15;   // mbarrier polls before giving up
+constexpr unsigned ROWS_WAIT_HINT_NS = 100000;  // a poll may suspend the warp this long
 
 // ---------------------------------------------------------------------------------------
 // PTX wrappers
@@ -92,10 +93,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ROWS_WAIT_HINT_NS)
       : "memory");
   return ok != 0;
 }
@@ -175,11 +176,27 @@ __host__ __device__ __forceinline__ void tile_in_rows(int K, int S, int mode, in
   if (hi < lo) hi = lo;
 }
 
+// n / d for small operands (n * d < 2^32) by multiplication with inv = ceil(2^32 / d).
+__host__ __device__ __forceinline__ uint32_t magic_of(int d) {
+  return (uint32_t)((0x100000000ull + (unsigned)d - 1) / (unsigned)d);
+}
+// (d == 1 has no 32-bit magic: magic_of(1) wraps to 0, which stands for "divide by one".)
+__device__ __forceinline__ int magic_div(int n, uint32_t inv) {
+  return inv ? (int)__umulhi((uint32_t)n, inv) : n;
+}
+
 // Split of a tile's th output rows over NRB row blocks; starts on multiples of RS.
 __host__ __device__ __forceinline__ void task_rows(int rb, int NRB, int R0, int th, int RS,
                                                    int &r_begin, int &r_end) {
   r_begin = R0 + ((rb * th) / NRB) / RS * RS;
   r_end = (rb == NRB - 1) ? (R0 + th) : R0 + (((rb + 1) * th) / NRB) / RS * RS;
+}
+// The same on the device, with the division by NRB done by multiplication.
+template <int RS>
+__device__ __forceinline__ void task_rows_fast(int rb, int NRB, uint32_t inv_nrb, int R0, int th,
+                                               int &r_begin, int &r_end) {
+  r_begin = R0 + magic_div(rb * th, inv_nrb) / RS * RS;
+  r_end = (rb == NRB - 1) ? (R0 + th) : R0 + magic_div((rb + 1) * th, inv_nrb) / RS * RS;
 }
 
 struct RowsParams {
@@ -194,6 +211,7 @@ struct RowsParams {
   int NRB;   // row blocks (tasks) per plane inside a tile
   int RBH;   // row-loop trip count of a task, a multiple of U
   int LW;    // lanes per segment: 8, 16 or 32
+  uint32_t inv_NRB;  // magic_of(NRB)
   int TAPB;  // bytes at the head of a stage that hold the taps of the tile's channels; 16 zero
              // bytes follow, then the tile's rows
   int ntiles;
@@ -412,17 +430,20 @@ struct ConvTile {
 template <int K, int S, int MODE>
 __device__ __forceinline__ ConvTile conv_tile(const RowsParams &p, int tile) {
   ConvTile t;
-  t.pg = tile / p.NRT;
-  const int rt = tile - t.pg * p.NRT;
-  t.R0 = rt * p.TH;
-  t.th = min(p.TH, p.Hout - t.R0);
-  t.gcount = min(p.G, p.NC - t.pg * p.G);
   if (p.NRT == 1) {
+    t.pg = tile;
+    t.R0 = 0;
+    t.th = p.Hout;
     t.in_lo = 0;
     t.in_hi = p.Hin;
   } else {
+    t.pg = tile / p.NRT;
+    const int rt = tile - t.pg * p.NRT;
+    t.R0 = rt * p.TH;
+    t.th = min(p.TH, p.Hout - t.R0);
     tile_in_rows(K, S, MODE, t.R0, t.th, p.Hin, t.in_lo, t.in_hi);
   }
+  t.gcount = min(p.G, p.NC - t.pg * p.G);
   return t;
 }
 
@@ -452,7 +473,8 @@ __device__ __forceinline__ TapLayout tap_layout(const T *gw, int first_plane, in
 // ---------------------------------------------------------------------------------------
 // forward / backward-input
 // ---------------------------------------------------------------------------------------
-template <typename T, int K, int S, int MODE, int VI, int VO, int U, bool MASK, int MINB>
+// EXACT: every task of every tile has exactly RBH rows, so no per-row test guards the stores.
+template <typename T, int K, int S, int MODE, int VI, int VO, int U, bool MASK, bool EXACT, int MINB>
 __global__ void __launch_bounds__(ROWS_THREADS, MINB)
 rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
   using Geo = RowsGeo<K, S, MODE, VI, VO, U>;
@@ -560,12 +582,12 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
 
     for (int t0 = 0; t0 < ntasks; t0 += NSEG) {
       const int task = t0 + seg;
-      const int g = task / p.NRB;
+      const int g = magic_div(task, p.inv_NRB);
       const int rb = task - g * p.NRB;
       const bool active = (task < ntasks) && (g < t.gcount);
       const int plane = t.pg * p.G + (active ? g : 0);
       int r_begin, r_end;
-      task_rows(rb, p.NRB, t.R0, t.th, RS, r_begin, r_end);
+      task_rows_fast<RS>(rb, p.NRB, p.inv_NRB, t.R0, t.th, r_begin, r_end);
 
       float taps[K][K];
       {
@@ -595,7 +617,8 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
         a = sdata + (uint32_t)(((g * nrows + q) * p.Win + j * VI) * (int)sizeof(T));
       }
       T *orow = gout + (size_t)plane * plane_out + (size_t)r_begin * p.Wout + j * VO;
-      int rows_left = (active && out_alive) ? (r_end - r_begin) : 0;
+      const bool st_ok = active && out_alive;
+      int rows_left = st_ok ? (r_end - r_begin) : 0;
 
       float rows[Geo::KR][Geo::NIN];
       {
@@ -634,14 +657,14 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
               }
             }
           }
-          if (u < rows_left) GmemSt<T, VO>::st(orow, acc);
+          if (EXACT ? st_ok : (u < rows_left)) GmemSt<T, VO>::st(orow, acc);
           orow += p.Wout;
         }
 #pragma unroll
         for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
 #pragma unroll
           for (int ci = 0; ci < Geo::NIN; ++ci) rows[i][ci] = rows[i + Geo::ADV][ci];
-        rows_left -= U;
+        if (!EXACT) rows_left -= U;
       }
     }
     __syncwarp();
@@ -661,6 +684,7 @@ struct RowsFilterParams {
   int NRT;    // row tiles per plane (G == 1 when > 1)
   int TH;     // dy rows per row tile
   int NRB, RBH, LW;  // G * NRB <= segments per CTA: a segment keeps its (channel, row block)
+  uint32_t inv_NRB;  // magic_of(NRB)
   int NCG;    // channel groups = ceil(C / G)
   int TPC;    // tiles per channel group = N * NRT
   int SL;     // work items (slices of that tile list) per channel group
@@ -695,7 +719,9 @@ __device__ __forceinline__ FilterTile filter_tile(const RowsFilterParams &p, int
 // over the item; at its end they are summed over the segment's lanes by shuffle, then over the
 // channel's row blocks through shared memory in a fixed order, and written to the (channel,
 // slice) slot of the partials (no atomics).  A second kernel adds a channel's slices in order.
-template <typename T, int K, int S, int VI, int VO, int U, bool MASK, int MINB>
+// EXACT: every task of every tile has exactly RBH rows, so every row of the loop contributes
+// and the inner loop has no branch (lanes without work multiply zeros).
+template <typename T, int K, int S, int VI, int VO, int U, bool MASK, bool EXACT, int MINB>
 __global__ void __launch_bounds__(ROWS_THREADS, MINB)
 rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
   using Geo = RowsGeo<K, S, MODE_FWD, VI, VO, U>;
@@ -774,7 +800,7 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
   make_lane_tables<Geo, VI>(src_lane, halo_mask, lane, j, p.W);
 
   const int ntasks = p.G * p.NRB;  // <= segments per CTA
-  const int g = seg / p.NRB;       // this segment's channel within the group, and row block
+  const int g = magic_div(seg, p.inv_NRB);  // this segment's channel within the group, row block
   const int rb = seg - g * p.NRB;
   const uint32_t row_bytes = (uint32_t)p.W * (uint32_t)sizeof(T);
   const uint32_t drow_bytes = (uint32_t)p.Wo * (uint32_t)sizeof(T);
@@ -817,7 +843,7 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
       const int drows = (p.NRT == 1) ? p.Ho : t.th;  // staged dy rows per plane
 
       int r_begin, r_end;
-      task_rows(rb, p.NRB, t.R0, t.th, 1, r_begin, r_end);
+      task_rows_fast<1>(rb, p.NRB, p.inv_NRB, t.R0, t.th, r_begin, r_end);
       int q = r_begin * S + Geo::RMIN - t.in_lo;
       int lim = 0;
       uint32_t a = zaddr;
@@ -825,10 +851,15 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
         lim = nrows;
         a = zaddr + 16u + (uint32_t)((xphase + (g * nrows + q) * p.W + j * VI) * (int)sizeof(T));
       }
-      uint32_t da = smem_u32(sb + p.DYOFF) +
-                    (uint32_t)((dphase + ((active ? g : 0) * drows + (r_begin - t.R0)) * p.Wo + j * VO) *
-                               (int)sizeof(T));
-      int rows_left = (active && out_alive) ? (r_end - r_begin) : 0;
+      const bool dy_ok = active && out_alive;
+      uint32_t da = zaddr;
+      uint32_t dpitch = 0;
+      if (dy_ok) {
+        da = smem_u32(sb + p.DYOFF) +
+             (uint32_t)((dphase + (g * drows + (r_begin - t.R0)) * p.Wo + j * VO) * (int)sizeof(T));
+        dpitch = drow_bytes;
+      }
+      int rows_left = dy_ok ? (r_end - r_begin) : 0;
 
       float rows[Geo::KR][Geo::NIN];
       {
@@ -852,12 +883,12 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
         float dys[U][VO];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          SmemLd<T, VO>::ld((u < rows_left) ? da : zaddr, dys[u]);
-          da += drow_bytes;
+          SmemLd<T, VO>::ld((EXACT || u < rows_left) ? da : zaddr, dys[u]);
+          da += dpitch;
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          if (u < rows_left) {  // rows past the task's end must not contribute
+          if (EXACT || u < rows_left) {  // rows past the task's end must not contribute
             const float (&dyv)[VO] = dys[u];
 #pragma unroll
             for (int ty = 0; ty < K; ++ty) {
@@ -874,7 +905,7 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
         for (int i = 0; i < Geo::KR - Geo::ADV; ++i)
 #pragma unroll
           for (int ci = 0; ci < Geo::NIN; ++ci) rows[i][ci] = rows[i + Geo::ADV][ci];
-        rows_left -= U;
+        if (!EXACT) rows_left -= U;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&ring.empty[stage]);

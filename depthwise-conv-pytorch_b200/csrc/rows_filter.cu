@@ -11,12 +11,12 @@ constexpr int filter_minb(int K) { return K <= 5 ? 2 : 1; }
 
 // Rows-per-chunk choices compiled for each (K, S); the planner picks per shape.
 template <int K, int S> struct FilterU;
-template <> struct FilterU<3, 1> { static constexpr int n = 2; static constexpr int v[2] = {4, 7}; };
-template <> struct FilterU<5, 1> { static constexpr int n = 2; static constexpr int v[2] = {2, 4}; };
-template <> struct FilterU<7, 1> { static constexpr int n = 1; static constexpr int v[2] = {2, 2}; };
-template <> struct FilterU<3, 2> { static constexpr int n = 2; static constexpr int v[2] = {2, 7}; };
-template <> struct FilterU<5, 2> { static constexpr int n = 1; static constexpr int v[2] = {2, 2}; };
-template <> struct FilterU<7, 2> { static constexpr int n = 1; static constexpr int v[2] = {1, 1}; };
+template <> struct FilterU<3, 1> { static constexpr int n = 4; static constexpr int v[4] = {4, 7, 8, 14}; };
+template <> struct FilterU<5, 1> { static constexpr int n = 2; static constexpr int v[4] = {2, 4, 4, 4}; };
+template <> struct FilterU<7, 1> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };
+template <> struct FilterU<3, 2> { static constexpr int n = 3; static constexpr int v[4] = {2, 4, 7, 7}; };
+template <> struct FilterU<5, 2> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };
+template <> struct FilterU<7, 2> { static constexpr int n = 1; static constexpr int v[4] = {1, 1, 1, 1}; };
 
 inline bool filter_shape_ok(const Shape &s) {
   if (s.kh != s.kw || (s.kh != 3 && s.kh != 5 && s.kh != 7)) return false;
@@ -43,7 +43,7 @@ inline bool pick_v(int S, int W, int Wo, bool a16, int &VI, int &VO) {
 struct FilterPlan {
   RowsFilterParams p;
   int VI, VO, U;
-  bool mask;
+  bool mask, exact;
 };
 
 template <typename T, int K, int S>
@@ -60,8 +60,10 @@ bool plan_filter_ks(const Shape &s, bool a16, FilterPlan &f) {
   if (!t.ok) return false;
   p.N = s.N; p.C = s.C; p.H = s.H; p.W = s.W; p.Ho = s.Ho; p.Wo = s.Wo;
   p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;
+  p.inv_NRB = magic_of(p.NRB);
   p.DYOFF = t.DYOFF;
   f.U = t.U;
+  f.exact = t.exact;
   const long long tpc = (long long)s.N * p.NRT;
   if (tpc > (1ll << 30)) return false;
   p.TPC = (int)tpc;
@@ -108,10 +110,10 @@ int *filter_flag_address() {
   return p;
 }
 
-template <typename T, int K, int S, int VI, int VO, int U, bool MASK>
+template <typename T, int K, int S, int VI, int VO, int U, bool MASK, bool EXACT>
 int launch_variant(const RowsFilterParams &p, cudaStream_t st) {
   constexpr int MINB = filter_minb(K);
-  auto kernel = rows_filter_kernel<T, K, S, VI, VO, U, MASK, MINB>;
+  auto kernel = rows_filter_kernel<T, K, S, VI, VO, U, MASK, EXACT, MINB>;
   static std::atomic<unsigned long long> smem_done{0};
   if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
   int *flag = filter_flag_address();
@@ -122,14 +124,24 @@ int launch_variant(const RowsFilterParams &p, cudaStream_t st) {
   return ROWS_SERVED;
 }
 
+template <typename T, int K, int S, int VI, int VO, int I>
+int launch_filter_u(const FilterPlan &f, cudaStream_t st) {
+  constexpr int UI = FilterU<K, S>::v[I];
+  if (f.U == UI || I + 1 >= FilterU<K, S>::n) {
+    if (f.mask)
+      return f.exact ? launch_variant<T, K, S, VI, VO, UI, true, true>(f.p, st)
+                     : launch_variant<T, K, S, VI, VO, UI, true, false>(f.p, st);
+    return f.exact ? launch_variant<T, K, S, VI, VO, UI, false, true>(f.p, st)
+                   : launch_variant<T, K, S, VI, VO, UI, false, false>(f.p, st);
+  }
+  if constexpr (I + 1 < FilterU<K, S>::n)
+    return launch_filter_u<T, K, S, VI, VO, I + 1>(f, st);
+  else
+    return ROWS_DECLINED;
+}
 template <typename T, int K, int S, int VI, int VO>
 int launch_filter_v(const FilterPlan &f, cudaStream_t st) {
-  constexpr int U0 = FilterU<K, S>::v[0], U1 = FilterU<K, S>::v[1];
-  if (f.U == U0)
-    return f.mask ? launch_variant<T, K, S, VI, VO, U0, true>(f.p, st)
-                  : launch_variant<T, K, S, VI, VO, U0, false>(f.p, st);
-  return f.mask ? launch_variant<T, K, S, VI, VO, U1, true>(f.p, st)
-                : launch_variant<T, K, S, VI, VO, U1, false>(f.p, st);
+  return launch_filter_u<T, K, S, VI, VO, 0>(f, st);
 }
 
 template <typename T, int K, int S>

@@ -59,6 +59,7 @@ struct TilePlan {
   int U;
   int G, NRT, TH, NRB, RBH;
   int TAPB, DYOFF;
+  bool exact;  // every task of every tile has exactly RBH rows
   int bytes;   // stage bytes in use
   double eff;  // useful output rows / segment-row slots spent
 };
@@ -67,7 +68,7 @@ struct TilePlan {
 inline bool plan_finish(const PlanInput &in, int U, TilePlan &t) {
   const int RS = (in.mode == MODE_BWD) ? in.S : 1;
   const int b = in.esize;
-  int lenmax = 0, rows_in = 0;
+  int lenmax = 0, lenmin = 1 << 30, rows_in = 0;
   for (int rt = 0; rt < t.NRT; ++rt) {
     const int R0 = rt * t.TH, th = (in.Hout - R0 < t.TH) ? in.Hout - R0 : t.TH;
     int lo = 0, hi = in.Hin;
@@ -77,11 +78,13 @@ inline bool plan_finish(const PlanInput &in, int U, TilePlan &t) {
       int r0, r1;
       task_rows(rb, t.NRB, R0, th, RS, r0, r1);
       if (r1 - r0 > lenmax) lenmax = r1 - r0;
+      if (r1 - r0 < lenmin) lenmin = r1 - r0;
     }
   }
   if (lenmax <= 0) return false;
   if (in.filter && t.G * t.NRB > in.NSEG) return false;
   t.RBH = round_up(lenmax, U);
+  t.exact = (lenmin == t.RBH);
   // stage: [taps][16 zero bytes][rows, up to 15 bytes behind their aligned start]
   // taps: up to two ranges, each up to 15 bytes behind a 16-byte boundary
   t.TAPB = in.filter ? 0 : round_up(t.G * in.K * in.K * b + 48, 128);
@@ -93,8 +96,14 @@ inline bool plan_finish(const PlanInput &in, int U, TilePlan &t) {
   }
   t.bytes = total;
   if (total > ROWS_STAGE_BYTES) return false;
+  // Cost in segment-row slots: every task pays its rows, the window rows it re-reads above its
+  // first row, and a fixed set-up; every tile pays a fixed hand-over.  Score = useful rows / cost.
   const int rounds = ceil_div(t.G * t.NRB, in.NSEG);
-  t.eff = (double)in.Hout * t.G / ((double)t.NRT * rounds * in.NSEG * t.RBH);
+  const double halo = (in.mode == MODE_FWD) ? (double)(in.K - in.S) / in.S : (double)(in.K - 1) / in.S;
+  const double task_rows_cost = t.RBH + halo + 4.0;
+  t.eff = (double)in.Hout * t.G /
+          ((double)t.NRT * in.NSEG * (rounds * task_rows_cost + 4.0));
+  if (t.exact) t.eff *= 1.03;  // no per-row tests in the inner loop
   t.U = U;
   t.ok = true;
   return true;
@@ -168,6 +177,7 @@ inline TilePlan plan_best(const PlanInput &in, const int *u_options, int n_optio
   int key[16] = {in.K, in.S, in.mode, in.Hin, in.Win, in.Hout, in.Wout, in.esize, in.NSEG,
                  in.maxG, in.filter ? 1 : 0, n_options, 0, 0, 0, 0};
   for (int i = 0; i < n_options && i < 4; ++i) key[12 + i] = u_options[i];
+  if (n_options > 4) n_options = 4;
   {
     std::lock_guard<std::mutex> lock(mu);
     for (const Entry &e : table)
