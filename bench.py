@@ -326,6 +326,21 @@ def gpu_arm(args, layers):
             z.record(stream)
             stream.synchronize()
             op_ms[name] = a.elapsed_time(z) / reps
+        # context for the roofline: what a plain device copy of one operator's traffic (read |x|,
+        # write |y| of the first layer) achieves at THIS size, same stream and timing
+        b0 = sets[0][0]
+        cp_a, cp_z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        scratch = [torch.empty_like(sets[i % n_sets][0]["x"]) for i in range(n_sets)]
+        for i in range(3):
+            scratch[i % n_sets].copy_(sets[i % n_sets][0]["x"])
+        cp_a.record(stream)
+        for i in range(reps):
+            scratch[i % n_sets].copy_(sets[i % n_sets][0]["x"])
+        cp_z.record(stream)
+        stream.synchronize()
+        copy_ms = cp_a.elapsed_time(cp_z) / reps
+        copy_gbps = 2 * b0["x"].numel() * b0["x"].element_size() / (copy_ms * 1e-3) / 1e9
+        del scratch
         # keep the GPU loaded until the clock sampler has a few samples
         if sampler is not None:
             t_need = t_load0 + 0.8
@@ -431,7 +446,8 @@ def gpu_arm(args, layers):
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 2),
                          "peak": peak, "unit": UNIT, "frac": round(achieved / peak, 4),
                          "peak_source": peak_src, "traffic": traffic,
-                         "algorithmic_bytes_per_launch": op_bytes},
+                         "algorithmic_bytes_per_launch": op_bytes,
+                         "torch_copy_of_first_layer_x_gbps": round(copy_gbps, 1)},
             "ops_ms": {k: round(v, 5) for k, v in op_ms.items()},
             "ops_gbps": {k: round(op_bytes / (v * 1e-3) / 1e9, 1) for k, v in op_ms.items()},
             "e2e": {"value": round(e2e_val, 3), "unit": UNIT, "h2d_bytes_per_step": h2d,

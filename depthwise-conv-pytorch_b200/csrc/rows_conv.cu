@@ -82,11 +82,12 @@ int launch_conv(RowsParams p, cudaStream_t st) {
   p.LW = pick_lw(lanes);
   if (p.LW == 0) return ROWS_DECLINED;
   PlanInput in{K, S, MODE, p.Hin, p.Win, p.Hout, p.Wout, (int)sizeof(T),
-               ROWS_CWARPS * (32 / p.LW), p.NC, false};
+               ROWS_CWARPS * (32 / p.LW), p.NC, 0, false};
   const TilePlan t = plan_best(in, ConvU<K, S, MODE>::v, ConvU<K, S, MODE>::n);
   if (!t.ok) return ROWS_DECLINED;
   p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;
   p.inv_NRB = magic_of(p.NRB);
+  p.NST = t.NST;
   p.TAPB = t.TAPB;
   const long long ntiles = (long long)ceil_div(p.NC, p.G) * p.NRT;
   if (ntiles > (1ll << 30)) return ROWS_DECLINED;
@@ -98,8 +99,8 @@ int launch_conv(RowsParams p, cudaStream_t st) {
                                  : Geo::fdiv(Geo::CMAX, VI);
   const bool mask = (p.LW - lanes_in) < halo_lanes;
   if (t_plan_out != nullptr) {
-    const int v[24] = {VI, VO, t.U, mask ? 1 : 0, p.LW, p.G, p.NRT, p.TH, p.NRB, p.RBH, 0, 0,
-                       0, p.TAPB, 0, 0, p.ntiles, 0, MODE, 0, 0, 0, 0, 0};
+    const int v[24] = {VI, VO, t.U, mask ? 1 : 0, p.LW, p.G, p.NRT, p.TH, p.NRB, p.RBH, p.NST,
+                       t.exact ? 1 : 0, 0, p.TAPB, 0, 0, p.ntiles, 0, MODE, 0, 0, 0, 0, 0};
     for (int i = 0; i < 24; ++i) t_plan_out[i] = v[i];
     return ROWS_SERVED;
   }

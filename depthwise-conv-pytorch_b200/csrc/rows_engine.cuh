@@ -4,30 +4,32 @@
 // Structure shared by forward, backward-input and backward-filter:
 //
 //  * Persistent, warp-specialised CTAs: 7 consumer warps compute, 1 producer warp moves data.
-//    A tile is a run of full-width rows of one plane, or a group of whole small planes.  Each
-//    plane's rows are one contiguous byte range of the NCHW tensor, so the producer brings them
-//    into shared memory with bulk asynchronous copies (cp.async.bulk, the TMA unit) that
-//    signal a "full" mbarrier; consumers hand a stage back through an "empty" mbarrier.  The
-//    ring has 3 stages, so two tiles are in flight while one is computed.  A slot keeps its
-//    source's phase within 16 bytes, so the aligned interior of ANY range is a bulk copy; only
-//    ragged heads and tails (< 16 bytes) are moved by the producer's lanes with plain loads.
-//  * Every plane slot in a stage is preceded and followed by zeroed elements, so the rows
-//    above and below the map read as zero without any test in the inner loop: the margins of
-//    whole-plane slots are zeroed once per CTA and never overwritten; for row tiles the top
-//    margin is permanent and the producer clears the rows after a plane's last tile.
+//    A tile is a run of full-width rows of one plane, or a group of whole small planes that are
+//    adjacent in memory; either way it is ONE contiguous byte range of the NCHW tensor, so the
+//    producer brings it into shared memory with one bulk asynchronous copy (cp.async.bulk, the
+//    TMA unit) that signals a "full" mbarrier; consumers hand a stage back through an "empty"
+//    mbarrier.  The 96 KB ring has 3 stages of 32 KB or 2 of 48 KB (chosen per problem), so
+//    tiles are in flight while one is computed.  The staged range keeps its source's phase
+//    within 16 bytes, so the aligned interior of ANY range is a legal bulk copy; only ragged
+//    heads and tails (< 16 bytes) are moved by a producer lane with plain loads.
 //  * A tile is split into tasks (plane, block of output rows).  A task is executed by a
 //    SEGMENT of a warp: LW = 8, 16 or 32 adjacent lanes.  Lane j owns VI adjacent input
 //    columns and VO adjacent output columns.  It reads its own columns of an input row from
 //    shared memory with one vector load and gets the k-1 halo columns from neighbouring lanes
-//    by warp shuffle; lanes beyond the map width read the zero margin, which also supplies the
-//    left/right padding when a segment has spare lanes (otherwise halo values are masked).
-//    Rows stream through a register window: each input element is read from shared memory
-//    once per task.
-//  * The filter taps of the tile's channels are written to the stage by the producer (fp32,
-//    already flipped for backward-input) and held in registers during a task.  Every output
-//    has one accumulator, taps are applied row-major with one FMA each: the summation order
-//    of the reference kernels (torch_dwconv/dwconv_kernel.cu:164-172), hence bit-identical.
+//    by warp shuffle.  Rows above / below the map are read from 16 zero bytes kept in every
+//    stage (an address select, no data-dependent branch); lanes beyond the map width read
+//    those zeros too, which supplies the left / right padding when a segment has spare lanes
+//    (otherwise halo values are masked).  Rows stream through a register window: each input
+//    element is read from shared memory once per task.
+//  * The filter taps of the tile's channels are consecutive in the filter tensor, so they are
+//    staged with bulk copies too and held in registers during a task.  Every output has one
+//    accumulator, taps are applied row-major with one FMA each: the summation order of the
+//    reference kernels (torch_dwconv/dwconv_kernel.cu:164-172), hence bit-identical fp32.
 //  * Outputs leave as VO-wide vector stores, contiguous across the segment.
+//  * Backward-filter: a work item is (group of consecutive channels, slice of the image list);
+//    a segment keeps its (channel, row block) and its K*K accumulators for the whole item; the
+//    partial of every (channel, slice) has exactly one writer and a second kernel adds the
+//    slices in order: deterministic, no atomics.
 //
 // All waits on mbarriers are bounded; on expiry the warp raises a flag the host can read
 // (dwconv_b200_device_status), stops waiting and runs to the end of the kernel.
@@ -42,16 +44,11 @@ enum { MODE_FWD = 0, MODE_BWD = 1 };
 
 constexpr int ROWS_CWARPS = 7;                        // consumer warps
 constexpr int ROWS_THREADS = (ROWS_CWARPS + 1) * 32;  // + 1 producer warp
-#ifndef ROWS_STAGES_CFG
-#define ROWS_STAGES_CFG 3
-#endif
-#ifndef ROWS_STAGE_KB_CFG
-#define ROWS_STAGE_KB_CFG 32
-#endif
-constexpr int ROWS_STAGES = ROWS_STAGES_CFG;
-constexpr int ROWS_STAGE_BYTES = ROWS_STAGE_KB_CFG * 1024;
+// The 96 KB ring is cut into 3 stages of 32 KB or 2 stages of 48 KB, chosen per problem.
+constexpr int ROWS_STAGES = 3;  // at most
+constexpr int ROWS_RING_BYTES = 96 * 1024;
 constexpr int ROWS_TAIL_BYTES = 8192;  // barriers, flags, cross-segment reduction scratch
-constexpr int ROWS_SMEM_BYTES = ROWS_STAGES * ROWS_STAGE_BYTES + ROWS_TAIL_BYTES;
+constexpr int ROWS_SMEM_BYTES = ROWS_RING_BYTES + ROWS_TAIL_BYTES;
 constexpr unsigned ROWS_WAIT_LIMIT = 1u << 15;   // mbarrier polls before giving up
 constexpr unsigned ROWS_WAIT_HINT_NS = 100000;  // a poll may suspend the warp this long
 
@@ -212,6 +209,7 @@ struct RowsParams {
   int RBH;   // row-loop trip count of a task, a multiple of U
   int LW;    // lanes per segment: 8, 16 or 32
   uint32_t inv_NRB;  // magic_of(NRB)
+  int NST;   // stages in the ring: 3 (32 KB each) or 2 (48 KB each)
   int TAPB;  // bytes at the head of a stage that hold the taps of the tile's channels; 16 zero
              // bytes follow, then the tile's rows
   int ntiles;
@@ -304,21 +302,24 @@ struct RowsRing {
   uint64_t *empty;
   volatile int *abort_flag;
   float *scratch;  // (ROWS_TAIL_BYTES - 128) bytes
-  __device__ __forceinline__ unsigned char *stage(int s) const { return base + s * ROWS_STAGE_BYTES; }
+  int stage_bytes;
+  __device__ __forceinline__ unsigned char *stage(int s) const { return base + s * stage_bytes; }
 };
 
-// Zero all stages (the margins must read as zero from the first tile on), set up barriers.
-__device__ __forceinline__ RowsRing rows_ring_init(unsigned char *smem) {
+// Sets up the barriers and clears, in every stage, the 16 bytes at `zero_off` that stand in
+// for rows outside the map (nothing else ever writes them).
+__device__ __forceinline__ RowsRing rows_ring_init(unsigned char *smem, int zero_off, int nst) {
   RowsRing r;
   r.base = smem;
-  unsigned char *tail = smem + ROWS_STAGES * ROWS_STAGE_BYTES;
+  r.stage_bytes = ROWS_RING_BYTES / nst;
+  unsigned char *tail = smem + ROWS_RING_BYTES;
   r.full = reinterpret_cast<uint64_t *>(tail);
   r.empty = r.full + ROWS_STAGES;
   r.abort_flag = reinterpret_cast<volatile int *>(r.empty + ROWS_STAGES);
   r.scratch = reinterpret_cast<float *>(tail + 128);
-  uint4 *z = reinterpret_cast<uint4 *>(smem);
-  for (int i = threadIdx.x; i < ROWS_STAGES * ROWS_STAGE_BYTES / 16; i += ROWS_THREADS)
-    z[i] = make_uint4(0u, 0u, 0u, 0u);
+  if (threadIdx.x < nst)
+    *reinterpret_cast<uint4 *>(smem + threadIdx.x * r.stage_bytes + zero_off) =
+        make_uint4(0u, 0u, 0u, 0u);
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int s = 0; s < ROWS_STAGES; ++s) {
@@ -480,7 +481,7 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
   using Geo = RowsGeo<K, S, MODE, VI, VO, U>;
   constexpr int KK = K * K;
   extern __shared__ __align__(128) unsigned char rows_smem[];
-  RowsRing ring = rows_ring_init(rows_smem);
+  RowsRing ring = rows_ring_init(rows_smem, p.TAPB, p.NST);
 
   const T *__restrict__ gin = static_cast<const T *>(p.in);
   const T *__restrict__ gw = static_cast<const T *>(p.w);
@@ -492,10 +493,12 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
 
   if (warp == ROWS_CWARPS) {
     // ------------------------------- producer warp -------------------------------
-    int it = 0;
-    for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
-      const int stage = it % ROWS_STAGES;
-      const int use = it / ROWS_STAGES;
+    int stage = -1, use = 0;
+    for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+      if (++stage == p.NST) {
+        stage = 0;
+        ++use;
+      }
       if (use > 0 && !mbar_wait_bounded(&ring.empty[stage], (use - 1) & 1)) {
         *ring.abort_flag = 1;
         atomicExch(error_flag, 1);
@@ -561,10 +564,12 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
 
   const int ntasks = p.G * p.NRB;
   const uint32_t row_bytes = (uint32_t)p.Win * (uint32_t)sizeof(T);
-  int it = 0;
-  for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
-    const int stage = it % ROWS_STAGES;
-    const int use = it / ROWS_STAGES;
+  int stage = -1, use = 0;
+  for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+    if (++stage == p.NST) {
+      stage = 0;
+      ++use;
+    }
     if (!mbar_wait_bounded(&ring.full[stage], use & 1)) {
       *ring.abort_flag = 1;
       atomicExch(error_flag, 1);
@@ -685,6 +690,7 @@ struct RowsFilterParams {
   int TH;     // dy rows per row tile
   int NRB, RBH, LW;  // G * NRB <= segments per CTA: a segment keeps its (channel, row block)
   uint32_t inv_NRB;  // magic_of(NRB)
+  int NST;    // stages in the ring: 3 (32 KB each) or 2 (48 KB each)
   int NCG;    // channel groups = ceil(C / G)
   int TPC;    // tiles per channel group = N * NRT
   int SL;     // work items (slices of that tile list) per channel group
@@ -727,7 +733,7 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
   using Geo = RowsGeo<K, S, MODE_FWD, VI, VO, U>;
   constexpr int KK = K * K;
   extern __shared__ __align__(128) unsigned char rows_smem[];
-  RowsRing ring = rows_ring_init(rows_smem);
+  RowsRing ring = rows_ring_init(rows_smem, 0, p.NST);
 
   const T *__restrict__ gx = static_cast<const T *>(p.x);
   const T *__restrict__ gdy = static_cast<const T *>(p.dy);
@@ -740,7 +746,7 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
   if (warp == ROWS_CWARPS) {
     // ------------------------------- producer warp -------------------------------
     bool stop = false;
-    int it = 0;
+    int stage = -1, use = 0;
     for (int item = blockIdx.x; item < nitems && !stop; item += gridDim.x) {
       const int cg = item / p.SL;
       const int slice = item - cg * p.SL;
@@ -748,9 +754,11 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
       const int gcount = min(p.G, p.C - c0);
       const int t_begin = (int)(((long long)slice * p.TPC) / p.SL);
       const int t_end = (int)(((long long)(slice + 1) * p.TPC) / p.SL);
-      for (int tt = t_begin; tt < t_end; ++tt, ++it) {
-        const int stage = it % ROWS_STAGES;
-        const int use = it / ROWS_STAGES;
+      for (int tt = t_begin; tt < t_end; ++tt) {
+        if (++stage == p.NST) {
+          stage = 0;
+          ++use;
+        }
         if (use > 0 && !mbar_wait_bounded(&ring.empty[stage], (use - 1) & 1)) {
           *ring.abort_flag = 1;
           atomicExch(error_flag, 2);
@@ -808,7 +816,7 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
   // A warp whose wait expired keeps walking the loops without waiting or computing, so that
   // it still meets the other consumer warps at every consumer_sync().
   bool aborted = false;
-  int it = 0;
+  int stage = -1, use = 0;
   for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
     const int cg = item / p.SL;
     const int slice = item - cg * p.SL;
@@ -824,9 +832,11 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
 #pragma unroll
       for (int tx = 0; tx < K; ++tx) acc[ty][tx] = 0.f;
 
-    for (int tt = t_begin; tt < t_end; ++tt, ++it) {
-      const int stage = it % ROWS_STAGES;
-      const int use = it / ROWS_STAGES;
+    for (int tt = t_begin; tt < t_end; ++tt) {
+      if (++stage == p.NST) {
+        stage = 0;
+        ++use;
+      }
       if (!aborted && (*ring.abort_flag || !mbar_wait_bounded(&ring.full[stage], use & 1))) {
         aborted = true;
         *ring.abort_flag = 1;

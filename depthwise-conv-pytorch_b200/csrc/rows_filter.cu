@@ -55,12 +55,13 @@ bool plan_filter_ks(const Shape &s, bool a16, FilterPlan &f) {
   p.LW = pick_lw(lanes);
   if (p.LW == 0) return false;
   PlanInput in{K, S, MODE_FWD, s.H, s.W, s.Ho, s.Wo, (int)sizeof(T),
-               ROWS_CWARPS * (32 / p.LW), s.C, true};
+               ROWS_CWARPS * (32 / p.LW), s.C, 0, true};
   const TilePlan t = plan_best(in, FilterU<K, S>::v, FilterU<K, S>::n);
   if (!t.ok) return false;
   p.N = s.N; p.C = s.C; p.H = s.H; p.W = s.W; p.Ho = s.Ho; p.Wo = s.Wo;
   p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;
   p.inv_NRB = magic_of(p.NRB);
+  p.NST = t.NST;
   p.DYOFF = t.DYOFF;
   f.U = t.U;
   f.exact = t.exact;
@@ -226,8 +227,8 @@ int rows_debug_filter_plan(int esize, const Shape &s, int a16, int *out) {
   bool ok = esize == 4 ? plan_filter<float>(s, a16 != 0, f) : plan_filter<__half>(s, a16 != 0, f);
   if (!ok) return 0;
   const RowsFilterParams &p = f.p;
-  const int v[24] = {f.VI, f.VO, f.U, f.mask ? 1 : 0, p.LW, p.G, p.NRT, p.TH, p.NRB, p.RBH, 0, 0,
-                     0, 0, 0, p.DYOFF, p.TPC, p.SL, 0, p.NCG, 0, 0, 0, 0};
+  const int v[24] = {f.VI, f.VO, f.U, f.mask ? 1 : 0, p.LW, p.G, p.NRT, p.TH, p.NRB, p.RBH, p.NST,
+                     f.exact ? 1 : 0, 0, 0, 0, p.DYOFF, p.TPC, p.SL, 0, p.NCG, 0, 0, 0, 0};
   for (int i = 0; i < 24; ++i) out[i] = v[i];
   return 1;
 }

@@ -49,6 +49,7 @@ struct PlanInput {
   int esize;         // bytes per element
   int NSEG;          // segments per CTA
   int maxG;          // planes that can share a tile (forward: N*C; backward-filter: C)
+  int stage_bytes;   // capacity of one stage (set by the planner: 32 KB x 3 or 48 KB x 2)
   bool filter;       // backward-filter: the stage also holds the Hout x Wout rows (dy), no taps,
                      // and a segment keeps one task for a whole item (G * NRB <= NSEG)
 };
@@ -59,6 +60,7 @@ struct TilePlan {
   int U;
   int G, NRT, TH, NRB, RBH;
   int TAPB, DYOFF;
+  int NST;     // stages the ring is cut into
   bool exact;  // every task of every tile has exactly RBH rows
   int bytes;   // stage bytes in use
   double eff;  // useful output rows / segment-row slots spent
@@ -95,14 +97,14 @@ inline bool plan_finish(const PlanInput &in, int U, TilePlan &t) {
     total = t.DYOFF + 16 + t.G * t.TH * in.Wout * b;
   }
   t.bytes = total;
-  if (total > ROWS_STAGE_BYTES) return false;
+  if (total > in.stage_bytes) return false;
   // Cost in segment-row slots: every task pays its rows, the window rows it re-reads above its
   // first row, and a fixed set-up; every tile pays a fixed hand-over.  Score = useful rows / cost.
   const int rounds = ceil_div(t.G * t.NRB, in.NSEG);
   const double halo = (in.mode == MODE_FWD) ? (double)(in.K - in.S) / in.S : (double)(in.K - 1) / in.S;
-  const double task_rows_cost = t.RBH + halo + 4.0;
+  const double task_rows_cost = t.RBH + halo + 2.0;
   t.eff = (double)in.Hout * t.G /
-          ((double)t.NRT * in.NSEG * (rounds * task_rows_cost + 4.0));
+          ((double)t.NRT * in.NSEG * (rounds * task_rows_cost + 2.0));
   if (t.exact) t.eff *= 1.03;  // no per-row tests in the inner loop
   t.U = U;
   t.ok = true;
@@ -153,14 +155,24 @@ inline TilePlan plan_for_u(const PlanInput &in, int U) {
   return best;
 }
 
-inline TilePlan plan_search(const PlanInput &in, const int *u_options, int n_options) {
+inline TilePlan plan_search(PlanInput in, const int *u_options, int n_options) {
   TilePlan best{};
   best.ok = false;
-  for (int i = 0; i < n_options; ++i) {
-    TilePlan c = plan_for_u(in, u_options[i]);
-    if (!c.ok) continue;
-    // prefer efficiency; at near-equal efficiency the larger U (less loop overhead)
-    if (!best.ok || c.eff > best.eff * 1.02 || (c.eff >= best.eff * 0.98 && c.U > best.U)) best = c;
+  // three 32 KB stages unless two 48 KB stages are clearly more efficient (small planes whose
+  // groups do not fit 32 KB): a deeper ring hides more latency
+  for (int nst = 3; nst >= 2; --nst) {
+    in.stage_bytes = ROWS_RING_BYTES / nst;
+    TilePlan cfg{};
+    cfg.ok = false;
+    for (int i = 0; i < n_options; ++i) {
+      TilePlan c = plan_for_u(in, u_options[i]);
+      if (!c.ok) continue;
+      // prefer efficiency; at near-equal efficiency the larger U (less loop overhead)
+      if (!cfg.ok || c.eff > cfg.eff * 1.02 || (c.eff >= cfg.eff * 0.98 && c.U > cfg.U)) cfg = c;
+    }
+    if (!cfg.ok) continue;
+    cfg.NST = nst;
+    if (!best.ok || cfg.eff > best.eff * 1.25) best = cfg;
   }
   return best;
 }
@@ -175,7 +187,7 @@ inline TilePlan plan_best(const PlanInput &in, const int *u_options, int n_optio
   static std::mutex mu;
   static std::vector<Entry> table;
   int key[16] = {in.K, in.S, in.mode, in.Hin, in.Win, in.Hout, in.Wout, in.esize, in.NSEG,
-                 in.maxG, in.filter ? 1 : 0, n_options, 0, 0, 0, 0};
+                 in.maxG, in.filter ? 1 : 0, n_options, 0, 0, 0, 0};  // stage_bytes: planner-set
   for (int i = 0; i < n_options && i < 4; ++i) key[12 + i] = u_options[i];
   if (n_options > 4) n_options = 4;
   {
