@@ -82,7 +82,7 @@ int launch_conv(RowsParams p, cudaStream_t st) {
   p.LW = pick_lw(lanes);
   if (p.LW == 0) return ROWS_DECLINED;
   PlanInput in{K, S, MODE, p.Hin, p.Win, p.Hout, p.Wout, (int)sizeof(T),
-               ROWS_CWARPS * (32 / p.LW), p.NC, 0, false};
+               ROWS_CWARPS * (32 / p.LW), p.NC, 0, sm_count() * conv_minb(K), false};
   const TilePlan t = plan_best(in, ConvU<K, S, MODE>::v, ConvU<K, S, MODE>::n);
   if (!t.ok) return ROWS_DECLINED;
   p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;

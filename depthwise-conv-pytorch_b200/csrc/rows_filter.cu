@@ -55,7 +55,7 @@ bool plan_filter_ks(const Shape &s, bool a16, FilterPlan &f) {
   p.LW = pick_lw(lanes);
   if (p.LW == 0) return false;
   PlanInput in{K, S, MODE_FWD, s.H, s.W, s.Ho, s.Wo, (int)sizeof(T),
-               ROWS_CWARPS * (32 / p.LW), s.C, 0, true};
+               ROWS_CWARPS * (32 / p.LW), s.C, 0, 0, true};
   const TilePlan t = plan_best(in, FilterU<K, S>::v, FilterU<K, S>::n);
   if (!t.ok) return false;
   p.N = s.N; p.C = s.C; p.H = s.H; p.W = s.W; p.Ho = s.Ho; p.Wo = s.Wo;

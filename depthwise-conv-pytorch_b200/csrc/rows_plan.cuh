@@ -50,6 +50,8 @@ struct PlanInput {
   int NSEG;          // segments per CTA
   int maxG;          // planes that can share a tile (forward: N*C; backward-filter: C)
   int stage_bytes;   // capacity of one stage (set by the planner: 32 KB x 3 or 48 KB x 2)
+  int slots;         // CTAs resident on the device at once (forward / backward-input: a small
+                     // problem should still be cut into at least this many tiles); 0 = ignore
   bool filter;       // backward-filter: the stage also holds the Hout x Wout rows (dy), no taps,
                      // and a segment keeps one task for a whole item (G * NRB <= NSEG)
 };
@@ -106,6 +108,10 @@ inline bool plan_finish(const PlanInput &in, int U, TilePlan &t) {
   t.eff = (double)in.Hout * t.G /
           ((double)t.NRT * in.NSEG * (rounds * task_rows_cost + 2.0));
   if (t.exact) t.eff *= 1.03;  // no per-row tests in the inner loop
+  if (in.slots > 0) {             // too few tiles leave SMs idle
+    const double ntiles = (double)ceil_div(in.maxG, t.G) * t.NRT;
+    if (ntiles < in.slots) t.eff *= ntiles / in.slots;
+  }
   t.U = U;
   t.ok = true;
   return true;
@@ -137,7 +143,7 @@ inline TilePlan plan_for_u(const PlanInput &in, int U) {
       consider(c);
     }
   }
-  if (best.ok) return best;
+  if (best.ok && !(in.slots > 0 && (double)ceil_div(in.maxG, best.G) < in.slots)) return best;
   // row tiles of a single plane: the few largest tile heights that fit
   int fits = 0;
   for (int NRT = 2; NRT <= in.Hout && fits < 4; ++NRT) {
@@ -188,7 +194,8 @@ inline TilePlan plan_best(const PlanInput &in, const int *u_options, int n_optio
   static std::vector<Entry> table;
   int key[16] = {in.K, in.S, in.mode, in.Hin, in.Win, in.Hout, in.Wout, in.esize, in.NSEG,
                  in.maxG, in.filter ? 1 : 0, n_options, 0, 0, 0, 0};  // stage_bytes: planner-set
-  for (int i = 0; i < n_options && i < 4; ++i) key[12 + i] = u_options[i];
+  key[15] = in.slots;
+  for (int i = 0; i < n_options && i < 3; ++i) key[12 + i] = u_options[i];
   if (n_options > 4) n_options = 4;
   {
     std::lock_guard<std::mutex> lock(mu);
