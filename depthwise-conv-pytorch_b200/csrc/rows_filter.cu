@@ -69,9 +69,11 @@ bool plan_filter_ks(const Shape &s, bool a16, FilterPlan &f) {
   if (tpc > (1ll << 30)) return false;
   p.TPC = (int)tpc;
   p.NCG = ceil_div(s.C, p.G);
-  // enough work items for ~2 per resident CTA, at least one tile each
+  // One equal work item per resident CTA when the channel groups divide the CTA slots well
+  // (no tail, fewest reductions); otherwise about two items per slot.  At least one tile each.
   const int slots = sm_count() * filter_minb(K);
-  int SL = ceil_div(2 * slots, p.NCG);
+  int SL = slots / p.NCG;
+  if (SL < 1 || (long long)SL * p.NCG * 100 < 85ll * slots) SL = ceil_div(2 * slots, p.NCG);
   if (SL > p.TPC) SL = p.TPC;
   if (SL < 1) SL = 1;
   p.SL = SL;
