@@ -216,7 +216,8 @@ def gpu_arm(args, layers):
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        from datetime import timedelta
+        dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=90))
     L = _lib.lib
     tdt = {"f32": torch.float32, "f16": torch.float16, "f64": torch.float64}
     code = {"f32": _lib.F32, "f16": _lib.F16, "f64": _lib.F64}
@@ -264,9 +265,12 @@ def gpu_arm(args, layers):
             op_backward_input(b, st)
             op_backward_filter(b, st)
 
+    # dW all-reduce: packed into one flat fp32 buffer, on a side stream, overlapped with the
+    # next step's kernels; the result is awaited before the next all-reduce starts
     reducer = None
+    pending = [None]
     if world > 1:
-        reducer = FilterGradReducer([b["dw"].shape for b in sets[0]], dev, side_stream=False)
+        reducer = FilterGradReducer([b["dw"].shape for b in sets[0]], dev, side_stream=True)
 
     # ---- one CUDA graph per buffer set (compute only; the collective stays eager) -------
     stream = torch.cuda.Stream(device=dev)
@@ -284,14 +288,25 @@ def gpu_arm(args, layers):
                 compute_step(bufs, torch.cuda.current_stream().cuda_stream)
             graphs.append(g)
 
-    def step(i):
-        bufs = sets[i % n_sets]
+    def compute_only(i):
         if graphs is not None:
             graphs[i % n_sets].replay()
         else:
-            compute_step(bufs, torch.cuda.current_stream().cuda_stream)
+            compute_step(sets[i % n_sets], torch.cuda.current_stream().cuda_stream)
+
+    def step(i):
+        bufs = sets[i % n_sets]
+        compute_only(i)
         if reducer is not None:
-            reducer.reduce([b["dw"] for b in bufs])
+            if pending[0] is not None:
+                reducer.finish(pending[0])
+            pending[0] = [b["dw"] for b in bufs]
+            reducer.start(pending[0])
+
+    def drain():
+        if reducer is not None and pending[0] is not None:
+            reducer.finish(pending[0])
+            pending[0] = None
 
     def barrier():
         if world > 1:
@@ -308,6 +323,7 @@ def gpu_arm(args, layers):
         e0.record(stream)
         for i in range(args.steps):
             step(i)
+        drain()
         e1.record(stream)
         barrier()
         ms_total = e0.elapsed_time(e1)
@@ -346,7 +362,7 @@ def gpu_arm(args, layers):
             t_need = t_load0 + 0.8
             i = 0
             while time.perf_counter() < t_need:
-                step(i)
+                compute_only(i)  # rank 0 only: no collective in here
                 i += 1
                 if i % 64 == 0:
                     stream.synchronize()
