@@ -196,4 +196,173 @@ rows_bigk_conv_kernel(const RowsParams p, const int K, const uint32_t inv_KK, in
   }
 }
 
+// Backward-filter for large filters.  Work items and tiles as in rows_filter_kernel (group of
+// G consecutive channels x slice of the image list; a tile = the x planes and dy planes of the
+// group in one image, two bulk copies).  A task (channel g, block of dy rows rb) belongs to one
+// whole warp, and here lane = tap COLUMN tx: the lane builds, for every x row, the window
+// x[row][tx-P .. tx-P+W-1] with shuffles (the same window as the forward kernel, lane and column
+// swapping roles) and adds dy[r][0..W-1] . window into acc[ty] for the k tap rows ty that pair
+// this x row with a dy row r of the block; dy rows are 128-bit broadcast loads.  No reduction
+// across lanes is needed: lane tx ends up holding dW[c][0..k-1][tx], written to the slot
+// (channel, slice, row block) of the partials; the finalize kernel adds the slots in order.
+template <typename T, int KMAX, int MINB>
+__global__ void __launch_bounds__(ROWS_THREADS, MINB)
+rows_bigk_filter_kernel(const RowsFilterParams p, const int K, int *__restrict__ error_flag) {
+  extern __shared__ __align__(128) unsigned char rows_smem[];
+  RowsRing ring = rows_ring_init(rows_smem, 0, p.NST);
+
+  const T *__restrict__ gx = static_cast<const T *>(p.x);
+  const T *__restrict__ gdy = static_cast<const T *>(p.dy);
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int P = K / 2;
+  const size_t plane = (size_t)p.H * p.W;  // x and dy planes have the same extent
+  const int nitems = p.NCG * p.SL;
+
+  if (warp == ROWS_CWARPS) {
+    // ------------------------------- producer warp -------------------------------
+    bool stop = false;
+    int stage = -1, use = 0;
+    for (int item = blockIdx.x; item < nitems && !stop; item += gridDim.x) {
+      const int cg = item / p.SL;
+      const int slice = item - cg * p.SL;
+      const int c0 = cg * p.G;
+      const int gcount = min(p.G, p.C - c0);
+      const int t_begin = (int)(((long long)slice * p.TPC) / p.SL);
+      const int t_end = (int)(((long long)(slice + 1) * p.TPC) / p.SL);
+      for (int n = t_begin; n < t_end; ++n) {
+        if (++stage == p.NST) {
+          stage = 0;
+          ++use;
+        }
+        if (use > 0 && !mbar_wait_bounded(&ring.empty[stage], (use - 1) & 1)) {
+          *ring.abort_flag = 1;
+          atomicExch(error_flag, 2);
+        }
+        if (*ring.abort_flag) {
+          stop = true;
+          break;
+        }
+        unsigned char *sb = ring.stage(stage);
+        const size_t pl0 = (size_t)n * p.C + c0;
+        uint32_t tx = 0;
+        if (lane == 0) {
+          fence_proxy_async_smem();
+          tx = stage_range(reinterpret_cast<T *>(sb + 16), gx + pl0 * plane, gcount * (int)plane,
+                           &ring.full[stage]);
+        } else if (lane == 1) {
+          fence_proxy_async_smem();
+          tx = stage_range(reinterpret_cast<T *>(sb + p.DYOFF), gdy + pl0 * plane,
+                           gcount * (int)plane, &ring.full[stage]);
+        }
+        tx = warp_sum(tx);
+        __syncwarp();
+        if (lane == 0) {
+          if (tx)
+            mbar_arrive_expect_tx(&ring.full[stage], tx);
+          else
+            mbar_arrive(&ring.full[stage]);
+        }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------- consumer warps -------------------------------
+  const int ntasks = p.G * p.NRB;  // <= consumer warps
+  const int g = magic_div(warp, p.inv_NRB);
+  const int rb = warp - g * p.NRB;
+  const bool col_alive = lane < p.W;
+  // window entry jj is x column lane - P + jj; real data iff inside the map, for a real tap column
+  uint32_t win_mask[32];
+#pragma unroll
+  for (int jj = 0; jj < 32; ++jj) {
+    const int col = lane - P + jj;
+    win_mask[jj] = (lane < K && jj < p.W && col >= 0 && col < p.W) ? 0xffffffffu : 0u;
+  }
+  const int lane_base = lane - P;
+  const uint32_t row_bytes = (uint32_t)p.W * (uint32_t)sizeof(T);
+  int r_begin, r_end;
+  task_rows_fast<1>(rb, p.NRB, p.inv_NRB, 0, p.Ho, r_begin, r_end);
+
+  int stage = -1, use = 0;
+  bool aborted = false;
+  for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+    const int cg = item / p.SL;
+    const int slice = item - cg * p.SL;
+    const int c0 = cg * p.G;
+    const int gcount = min(p.G, p.C - c0);
+    const int t_begin = (int)(((long long)slice * p.TPC) / p.SL);
+    const int t_end = (int)(((long long)(slice + 1) * p.TPC) / p.SL);
+    const bool active = (warp < ntasks) && (g < gcount);
+
+    float acc[KMAX];
+#pragma unroll
+    for (int ty = 0; ty < KMAX; ++ty) acc[ty] = 0.f;
+
+    for (int n = t_begin; n < t_end; ++n) {
+      if (++stage == p.NST) {
+        stage = 0;
+        ++use;
+      }
+      if (!aborted && (*ring.abort_flag || !mbar_wait_bounded(&ring.full[stage], use & 1))) {
+        aborted = true;
+        *ring.abort_flag = 1;
+        atomicExch(error_flag, 2);
+      }
+      if (aborted) continue;
+      unsigned char *sb = ring.stage(stage);
+      const size_t pl0 = (size_t)n * p.C + c0;
+      const uint32_t zaddr = smem_u32(sb);
+      const int xphase = slot_phase(gx + pl0 * plane);
+      const int dphase = slot_phase(gdy + pl0 * plane);
+      if (active) {  // warp-uniform
+        const uint32_t xplane =
+            zaddr + 16u + (uint32_t)((xphase + g * (int)plane + lane) * (int)sizeof(T));
+        const uint32_t dplane =
+            smem_u32(sb + p.DYOFF) + (uint32_t)((dphase + g * (int)plane) * (int)sizeof(T));
+        const int lim = col_alive ? p.H : 0;
+        // x rows r_begin - P .. r_end - 1 + P pair with the dy rows of the block
+        int q = r_begin - P;
+        uint32_t a = xplane + (uint32_t)q * row_bytes;
+        for (; q < r_end + P; ++q, a += row_bytes) {
+          float own[1];
+          SmemLd<T, 1>::ld(((unsigned)q < (unsigned)lim) ? a : zaddr, own);
+          float win[32];
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj)
+            win[jj] = __uint_as_float(
+                __shfl_sync(0xffffffffu, __float_as_uint(own[0]), (lane_base + jj) & 31) & win_mask[jj]);
+#pragma unroll
+          for (int ty = 0; ty < KMAX; ++ty) {
+            const int r = q - ty + P;  // dy row this x row meets through tap row ty
+            if (ty < K && r >= r_begin && r < r_end) {
+              const uint32_t drow = dplane + (uint32_t)r * row_bytes;
+#pragma unroll
+              for (int j4 = 0; j4 < 8; ++j4) {
+                if (j4 * 4 < p.W) {
+                  float d4[4];
+                  SmemLd<T, 4>::ld(drow + j4 * 4 * (int)sizeof(T), d4);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) acc[ty] = fmaf(d4[e], win[j4 * 4 + e], acc[ty]);
+                }
+              }
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ring.empty[stage]);
+    }
+    // lane tx holds dW[c0+g][ty][tx] of this (slice, row block)
+    if (active && lane < K) {
+      float *dst = p.partial + (((size_t)(c0 + g) * p.SL + slice) * p.NRB + rb) * (size_t)(K * K) + lane;
+#pragma unroll
+      for (int ty = 0; ty < KMAX; ++ty)
+        if (ty < K) dst[ty * K] = acc[ty];
+    }
+  }
+}
+
 }  // namespace dwb
+

@@ -3,6 +3,9 @@
 
 namespace dwb {
 
+template <typename T> int rows_bigk_conv(const RowsParams &p, int K, cudaStream_t st);  // rows_bigk.cu
+int rows_bigk_take_error();
+
 namespace {
 
 __device__ int g_conv_error_flag;
@@ -15,7 +18,7 @@ template <typename T> struct RowsDtype { static constexpr bool ok = false; };
 template <> struct RowsDtype<float> { static constexpr bool ok = true; };
 template <> struct RowsDtype<__half> { static constexpr bool ok = true; };
 
-constexpr int conv_minb(int K) { return K <= 5 ? 2 : 1; }
+constexpr int conv_minb(int K) { return 2; }  // K = 7 keeps its taps in shared memory to fit
 
 // Rows-per-chunk choices compiled for each (K, S, MODE); the planner picks per shape.
 template <int K, int S, int MODE> struct ConvU;
@@ -146,10 +149,12 @@ int select_k(const RowsParams &p, int K, int S, cudaStream_t st) {
   }
 }
 
-// The family covers square odd filters 3/5/7, equal strides 1 or 2, padding k/2, and the
-// output extent that padding implies.
-inline bool conv_shape_ok(const Shape &s) {
-  if (s.kh != s.kw || (s.kh != 3 && s.kh != 5 && s.kh != 7)) return false;
+// The family covers square odd filters, equal strides 1 or 2, padding k/2, and the output
+// extent that padding implies: 3/5/7 here, 9..31 at stride 1 in rows_bigk.cu.
+inline bool conv_shape_ok(const Shape &s, bool big) {
+  if (s.kh != s.kw) return false;
+  if (!big && s.kh != 3 && s.kh != 5 && s.kh != 7) return false;
+  if (big && (s.kh < 9 || s.kh > 31 || (s.kh & 1) == 0 || s.sh != 1)) return false;
   if (s.sh != s.sw || (s.sh != 1 && s.sh != 2)) return false;
   if (s.ph != s.kh / 2 || s.pw != s.kw / 2) return false;
   if (s.Ho != (s.H + 2 * s.ph - s.kh) / s.sh + 1 || s.Wo != (s.W + 2 * s.pw - s.kw) / s.sw + 1)
@@ -164,12 +169,14 @@ int rows_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st) 
   if constexpr (!RowsDtype<T>::ok) {
     return ROWS_DECLINED;
   } else {
-    if (!conv_shape_ok(s)) return ROWS_DECLINED;
+    const bool big = s.kh > 7;
+    if (!conv_shape_ok(s, big)) return ROWS_DECLINED;
     RowsParams p{};
     p.in = x; p.w = w; p.out = y;
     p.NC = s.N * s.C; p.C = s.C;
     p.Hin = s.H; p.Win = s.W; p.Hout = s.Ho; p.Wout = s.Wo;
     p.flip = 0;
+    if (big) return t_plan_out ? ROWS_DECLINED : rows_bigk_conv<T>(p, s.kh, st);
     return select_k<T, MODE_FWD>(p, s.kh, s.sh, st);
   }
 }
@@ -179,12 +186,14 @@ int rows_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStre
   if constexpr (!RowsDtype<T>::ok) {
     return ROWS_DECLINED;
   } else {
-    if (!conv_shape_ok(s)) return ROWS_DECLINED;
+    const bool big = s.kh > 7;
+    if (!conv_shape_ok(s, big)) return ROWS_DECLINED;
     RowsParams p{};
     p.in = dy; p.w = w; p.out = dx;
     p.NC = s.N * s.C; p.C = s.C;
     p.Hin = s.Ho; p.Win = s.Wo; p.Hout = s.H; p.Wout = s.W;
     p.flip = 1;
+    if (big) return t_plan_out ? ROWS_DECLINED : rows_bigk_conv<T>(p, s.kh, st);
     // stride 1: the transposed operation is the same correlation with the flipped filter
     return select_k<T, MODE_BWD>(p, s.kh, s.sh, st);
   }
@@ -217,7 +226,7 @@ int rows_conv_take_error() {
     const int zero = 0;
     (void)cudaMemcpyToSymbol(g_conv_error_flag, &zero, sizeof(int));
   }
-  return v;
+  return v | rows_bigk_take_error();
 }
 
 template int rows_forward<float>(const float *, const float *, float *, const Shape &, cudaStream_t);

@@ -594,7 +594,13 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
       int r_begin, r_end;
       task_rows_fast<RS>(rb, p.NRB, p.inv_NRB, t.R0, t.th, r_begin, r_end);
 
-      float taps[K][K];
+      // K <= 5: the K*K taps live in registers for the task.  K = 7: 49 tap registers would cap
+      // the kernel at one CTA per SM, so the segment re-lays its taps as fp32 rows of 8 in a
+      // private scratch and reads them back (two 128-bit broadcast loads per tap row) as needed.
+      constexpr bool TAPS_IN_SMEM = (K == 7);
+      constexpr int TK = TAPS_IN_SMEM ? 1 : K;
+      float taps[TK][TK];
+      const uint32_t seg_taps = smem_u32(ring.scratch) + (uint32_t)(seg * (K * 8 * 4));
       {
         // this plane's taps in the stage; backward-input reads them back to front
         const int cw = tl.c_base + g;
@@ -605,13 +611,22 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
                             : staps + tl.offB16 + tl.phaseB + (cw - p.C) * KK;
         }
         const int t_first = p.flip ? KK - 1 : 0, t_step = p.flip ? -1 : 1;
+        if constexpr (TAPS_IN_SMEM) {
+          __syncwarp();  // the previous task's reads of the scratch are over
+          float *dst = ring.scratch + seg * (K * 8);
+          for (int idx = j; idx < K * 8; idx += LW) {
+            const int ty = idx >> 3, tx = idx & 7;
+            dst[idx] = (active && tx < K) ? Elem<T>::to_acc(tp[t_first + t_step * (ty * K + tx)]) : 0.f;
+          }
+          __syncwarp();
+        } else {
 #pragma unroll
-        for (int ty = 0; ty < K; ++ty)
+          for (int ty = 0; ty < K; ++ty)
 #pragma unroll
-          for (int tx = 0; tx < K; ++tx)
-            taps[ty][tx] = active ? Elem<T>::to_acc(tp[t_first + t_step * (ty * K + tx)]) : 0.f;
+            for (int tx = 0; tx < K; ++tx)
+              taps[ty][tx] = active ? Elem<T>::to_acc(tp[t_first + t_step * (ty * K + tx)]) : 0.f;
+        }
       }
-
       // row index (inside the plane's staged rows) of window row 0, its shared address, and the
       // row pitch; lanes with nothing to read have lim = 0 and only ever read the zero bytes
       int q = (MODE == MODE_FWD ? r_begin * S : r_begin / S) + Geo::RMIN - t.in_lo;
@@ -653,12 +668,24 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
           for (int ty = 0; ty < K; ++ty) {
             if (!Geo::used(u, ty)) continue;
             const int ri = Geo::rel(u, ty) - Geo::RMIN;
+            float trow[8];
+            if constexpr (TAPS_IN_SMEM) {
+              float lo[4], hi[4];
+              SmemLd<float, 4>::ld(seg_taps + ty * 32, lo);
+              SmemLd<float, 4>::ld(seg_taps + ty * 32 + 16, hi);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                trow[i] = lo[i];
+                trow[4 + i] = hi[i];
+              }
+            }
 #pragma unroll
             for (int tx = 0; tx < K; ++tx) {
+              const float tap = TAPS_IN_SMEM ? trow[tx & 7] : taps[TAPS_IN_SMEM ? 0 : ty][TAPS_IN_SMEM ? 0 : tx];
 #pragma unroll
               for (int e = 0; e < VO; ++e) {
                 if (!Geo::used(e, tx)) continue;
-                acc[e] = fmaf(rows[ri][Geo::rel(e, tx) - Geo::CMIN], taps[ty][tx], acc[e]);
+                acc[e] = fmaf(rows[ri][Geo::rel(e, tx) - Geo::CMIN], tap, acc[e]);
               }
             }
           }

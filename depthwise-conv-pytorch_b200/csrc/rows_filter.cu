@@ -3,6 +3,12 @@
 
 namespace dwb {
 
+// large filters: rows_bigk.cu
+template <typename T> int rows_bigk_filter_slices(const Shape &s);
+template <typename T>
+int rows_bigk_filter(const T *x, const T *dy, float *partial, const Shape &s, cudaStream_t st,
+                     int *slices_out);
+
 namespace {
 
 __device__ int g_filter_error_flag;
@@ -169,6 +175,7 @@ template <typename T> int rows_backward_filter_slices(const Shape &s) {
     return 0;
   } else {
     // alignment is not known here: report the largest slice count either choice would use
+    if (s.kh > 7) return rows_bigk_filter_slices<T>(s);
     FilterPlan f{};
     int best = 0;
     for (int a16 = 0; a16 < 2; ++a16)
@@ -183,6 +190,7 @@ int rows_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *parti
   if constexpr (!RowsDtype<T>::ok) {
     return ROWS_DECLINED;
   } else {
+    if (s.kh > 7) return rows_bigk_filter<T>(x, dy, partial, s, st, slices_out);
     const bool a16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy)) & 15) == 0;
     FilterPlan f{};
     if (!plan_filter<T>(s, a16, f)) return ROWS_DECLINED;

@@ -194,6 +194,20 @@ def test_irregular_geometries(cfg, dtn):
         _check_three_ops(x, w, dy, st, pd, dt, path, f"irregular{cfg[:6]}[{path}]")
 
 
+@pytest.mark.parametrize("dtn", ["f32", "f16"])
+@pytest.mark.parametrize("cfg", [(32, 32, 13), (32, 32, 31), (28, 28, 9), (16, 16, 15), (12, 20, 17),
+                                 (8, 8, 11), (31, 30, 13), (24, 32, 21), (7, 7, 9)],
+                         ids=lambda c: "x".join(map(str, c)))
+def test_large_filters(cfg, dtn):
+    """Odd filters 9..31 at stride 1 with padding k/2 on maps up to 32 wide (the large-filter
+    kernels), several planes per channel, against the oracle bit for bit."""
+    H, W, k = cfg
+    dt = NP_DT[dtn]
+    x, w, dy = seeded((5, 9, H, W), (k, k), 1, k // 2, dt, seed=H * 100 + W + k)
+    for path in ("auto", "rows"):
+        _check_three_ops(x, w, dy, 1, k // 2, dt, path, f"large{cfg}[{path}]")
+
+
 def test_backward_filter_is_deterministic():
     for (shape, k, s, p) in [((16, 24, 14, 14), 3, 1, 1), ((4, 8, 56, 56), 5, 2, 2),
                              ((8, 6, 28, 28), 7, 1, 3)]:
