@@ -18,7 +18,7 @@ template <typename T> struct RowsDtype { static constexpr bool ok = false; };
 template <> struct RowsDtype<float> { static constexpr bool ok = true; };
 template <> struct RowsDtype<__half> { static constexpr bool ok = true; };
 
-constexpr int conv_minb(int K) { return 2; }  // K = 7 keeps its taps in shared memory to fit
+constexpr int conv_minb(int K) { return K <= 5 ? 2 : 1; }  // 49 tap registers: one CTA per SM
 
 // Rows-per-chunk choices compiled for each (K, S, MODE); the planner picks per shape.
 template <int K, int S, int MODE> struct ConvU;

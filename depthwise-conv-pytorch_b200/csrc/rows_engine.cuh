@@ -594,10 +594,12 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
       int r_begin, r_end;
       task_rows_fast<RS>(rb, p.NRB, p.inv_NRB, t.R0, t.th, r_begin, r_end);
 
-      // K <= 5: the K*K taps live in registers for the task.  K = 7: 49 tap registers would cap
-      // the kernel at one CTA per SM, so the segment re-lays its taps as fp32 rows of 8 in a
-      // private scratch and reads them back (two 128-bit broadcast loads per tap row) as needed.
-      constexpr bool TAPS_IN_SMEM = (K == 7);
+      // The K*K taps live in registers for the task.  (Measured alternative for K = 7, kept
+      // behind this switch: re-laying the taps as fp32 rows of 8 in a per-segment scratch and
+      // reading them back per tap row frees 49 registers and allows two CTAs per SM, but the
+      // extra shared-memory loads cost more than the occupancy returns: 108 vs 71 us on the
+      // 56x56 fp16 layer.)
+      constexpr bool TAPS_IN_SMEM = false;
       constexpr int TK = TAPS_IN_SMEM ? 1 : K;
       float taps[TK][TK];
       const uint32_t seg_taps = smem_u32(ring.scratch) + (uint32_t)(seg * (K * 8 * 4));
