@@ -2,5 +2,6 @@
 from .dwconv import (DepthwiseConv2d, DepthwiseConv2dFunction, check_options,  # noqa: F401
                      depthwise_conv2d, depthwise_conv2d_fn, make_tuple, use_dwconv2d_small)
 from . import _C  # noqa: F401
+from .host import HostMapsStep  # noqa: F401
 
-__all__ = ["depthwise_conv2d", "DepthwiseConv2d"]
+__all__ = ["depthwise_conv2d", "DepthwiseConv2d", "HostMapsStep"]

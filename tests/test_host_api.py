@@ -175,3 +175,17 @@ def test_missing_library_fails_loudly(tmp_path, monkeypatch):
                                      os.path.join(ROOT, "depthwise-conv-pytorch_b200"))
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True)
     assert r.returncode != 0 and "no CPU or PyTorch fallback" in r.stderr
+
+
+def test_chunk_bounds_cover_the_batch_once():
+    from dwconv_b200.host import chunk_bounds
+    for n, image_bytes, chunk in ((128, 451584, None), (1, 100, None), (2, 1 << 20, None),
+                                  (128, 1605632, None), (7, 1 << 30, None), (1000, 1000, None),
+                                  (13, 5000, 4), (5, 5000, 99)):
+        b = chunk_bounds(n, image_bytes, chunk)
+        assert b[0][0] == 0 and b[-1][1] == n
+        assert all(b[i][1] == b[i + 1][0] for i in range(len(b) - 1))
+        assert all(hi > lo for lo, hi in b)
+    assert len(chunk_bounds(128, 451584)) == 8            # eight chunks of 16 images
+    assert len(chunk_bounds(1000, 1000)) == 1             # too small to be worth cutting
+    assert [hi - lo for lo, hi in chunk_bounds(13, 5000, 4)] == [4, 4, 4, 1]
