@@ -137,8 +137,17 @@ int backward_filter_t(const void *x, const void *dy, void *dw, void *ws, size_t 
     int e = launch_status();
     if (e != DWCONV_B200_OK) return e;
   }
-  backward_filter_finalize_kernel<T><<<ceil_div(s.C * kk, 256), 256, 0, st>>>((const A *)ws,
-                                                                              (T *)dw, s.C, kk, S);
+  // second pass, launched so that it can be resident before the first pass has drained
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(finalize_blocks(s.C, kk));
+  cfg.blockDim = dim3(FINALIZE_THREADS);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  (void)cudaLaunchKernelEx(&cfg, backward_filter_finalize_kernel<T>, (const A *)ws, (T *)dw, s.C, kk, S);
   return launch_status();
 }
 

@@ -36,6 +36,16 @@ template <> struct Elem<double> {
 __device__ __forceinline__ float fma_acc(float a, float b, float c) { return fmaf(a, b, c); }
 __device__ __forceinline__ double fma_acc(double a, double b, double c) { return fma(a, b, c); }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization
+// attribute may become resident while the kernel before it in the stream is still running (as soon
+// as every CTA of that kernel has called pdl_launch_dependents() or exited); it must call
+// pdl_wait() before it touches global memory, which returns once the earlier kernel has
+// completed and its writes are visible.  Both are no-ops when the launch has no such attribute.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ __forceinline__ long long ceil_div_ll(long long a, long long b) {
   return (a + b - 1) / b;

@@ -88,6 +88,7 @@ direct_backward_filter_partial_kernel(const T *__restrict__ x, const T *__restri
                                       typename Elem<T>::acc_t *__restrict__ partial,
                                       const Shape s, const int S) {
   using A = typename Elem<T>::acc_t;
+  pdl_launch_dependents();  // the second pass may take its place on the SMs early
   const int c = blockIdx.x / S;
   const int slice = blockIdx.x - c * S;
   const int n0 = (int)((long long)slice * s.N / S);
@@ -118,20 +119,44 @@ direct_backward_filter_partial_kernel(const T *__restrict__ x, const T *__restri
   }
 }
 
-// Backward-filter, second pass: dw[c,tap] = partial[c,0,tap] + partial[c,1,tap] + ...
-// in slice order, so the result does not depend on scheduling.
+// Backward-filter, second pass: dw[c,tap] = sum over the S slices of partial[c,sl,tap].
+// A warp owns 32 consecutive outputs (coalesced reads of every slice); the block's 8 warps take
+// the slices sl = part, part + 8, ... of the same 32 outputs, each adding in ascending order, and
+// the 8 part sums are added in part order.  The order is fixed, so the result does not depend on
+// scheduling; eight short chains instead of one long one keep the pass from being latency-bound.
+constexpr int FINALIZE_OUTPUTS = 32;  // per block
+constexpr int FINALIZE_PARTS = 8;
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(FINALIZE_OUTPUTS * FINALIZE_PARTS)
 backward_filter_finalize_kernel(const typename Elem<T>::acc_t *__restrict__ partial,
                                 T *__restrict__ dw, const int C, const int kk, const int S) {
   using A = typename Elem<T>::acc_t;
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= C * kk) return;
-  const int c = idx / kk;
-  const int tap = idx - c * kk;
+  __shared__ A part_sum[FINALIZE_PARTS][FINALIZE_OUTPUTS];
+  const int o = threadIdx.x & (FINALIZE_OUTPUTS - 1);
+  const int part = threadIdx.x / FINALIZE_OUTPUTS;
+  const int idx = blockIdx.x * FINALIZE_OUTPUTS + o;
+  const bool live = idx < C * kk;
   A acc = 0;
-  for (int sl = 0; sl < S; ++sl) acc += partial[((long long)c * S + sl) * kk + tap];
-  dw[idx] = Elem<T>::from_acc(acc);
+  pdl_wait();  // the first pass has finished and its partial sums are visible
+  if (live) {
+    const int c = idx / kk;
+    const int tap = idx - c * kk;
+    const A *src = partial + (long long)c * S * kk + tap;
+#pragma unroll 4
+    for (int sl = part; sl < S; sl += FINALIZE_PARTS) acc += src[(long long)sl * kk];
+  }
+  part_sum[part][o] = acc;
+  __syncthreads();
+  if (part == 0 && live) {
+    A total = part_sum[0][o];
+#pragma unroll
+    for (int q = 1; q < FINALIZE_PARTS; ++q) total += part_sum[q][o];
+    dw[idx] = Elem<T>::from_acc(total);
+  }
 }
+
+// Launch geometry of the second pass.
+inline int finalize_blocks(int C, int kk) { return ceil_div(C * kk, FINALIZE_OUTPUTS); }
+constexpr int FINALIZE_THREADS = FINALIZE_OUTPUTS * FINALIZE_PARTS;
 
 }  // namespace dwb

@@ -209,6 +209,7 @@ template <typename T, int KMAX, int MINB>
 __global__ void __launch_bounds__(ROWS_THREADS, MINB)
 rows_bigk_filter_kernel(const RowsFilterParams p, const int K, int *__restrict__ error_flag) {
   extern __shared__ __align__(128) unsigned char rows_smem[];
+  pdl_launch_dependents();  // the second pass may take its place on the SMs early
   RowsRing ring = rows_ring_init(rows_smem, 0, p.NST);
 
   const T *__restrict__ gx = static_cast<const T *>(p.x);

@@ -762,6 +762,7 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
   using Geo = RowsGeo<K, S, MODE_FWD, VI, VO, U>;
   constexpr int KK = K * K;
   extern __shared__ __align__(128) unsigned char rows_smem[];
+  pdl_launch_dependents();  // the second pass may take its place on the SMs early
   RowsRing ring = rows_ring_init(rows_smem, 0, p.NST);
 
   const T *__restrict__ gx = static_cast<const T *>(p.x);

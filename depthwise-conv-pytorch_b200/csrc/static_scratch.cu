@@ -61,7 +61,7 @@ int run(const void *x, const void *dy, void *dw, const Shape &s, cudaStream_t st
     (void)cudaGetLastError();
     return DWCONV_B200_CUDA_ERROR;
   }
-  backward_filter_finalize_kernel<T><<<ceil_div(s.C * kk, 256), 256, 0, st>>>(
+  backward_filter_finalize_kernel<T><<<finalize_blocks(s.C, kk), FINALIZE_THREADS, 0, st>>>(
       (const A *)scratch, (T *)dw, s.C, kk, S);
   if (cudaPeekAtLastError() != cudaSuccess) {
     (void)cudaGetLastError();
