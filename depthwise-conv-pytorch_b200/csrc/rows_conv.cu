@@ -56,7 +56,7 @@ int launch_variant(const RowsParams &p, cudaStream_t st) {
   int *flag = conv_flag_address();
   if (flag == nullptr) return ROWS_DECLINED;
   const int grid = (int)min((long long)sm_count() * MINB, (long long)p.ntiles);
-  kernel<<<grid, ROWS_THREADS, ROWS_SMEM_BYTES, st>>>(p, flag);
+  launch_dependent(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, p, flag);
   return ROWS_SERVED;
 }
 

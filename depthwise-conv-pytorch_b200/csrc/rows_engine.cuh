@@ -481,7 +481,9 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
   using Geo = RowsGeo<K, S, MODE, VI, VO, U>;
   constexpr int KK = K * K;
   extern __shared__ __align__(128) unsigned char rows_smem[];
+  pdl_launch_dependents();  // the next kernel in the stream may take freed SMs early
   RowsRing ring = rows_ring_init(rows_smem, p.TAPB, p.NST);
+  pdl_wait();  // everything earlier in the stream has completed; global memory may be touched
 
   const T *__restrict__ gin = static_cast<const T *>(p.in);
   const T *__restrict__ gw = static_cast<const T *>(p.w);
@@ -764,6 +766,7 @@ rows_filter_kernel(const RowsFilterParams p, int *__restrict__ error_flag) {
   extern __shared__ __align__(128) unsigned char rows_smem[];
   pdl_launch_dependents();  // the second pass may take its place on the SMs early
   RowsRing ring = rows_ring_init(rows_smem, 0, p.NST);
+  pdl_wait();  // everything earlier in the stream has completed; global memory may be touched
 
   const T *__restrict__ gx = static_cast<const T *>(p.x);
   const T *__restrict__ gdy = static_cast<const T *>(p.dy);

@@ -129,7 +129,7 @@ int launch_variant(const RowsFilterParams &p, cudaStream_t st) {
   if (flag == nullptr) return ROWS_DECLINED;
   const long long items = (long long)p.NCG * p.SL;
   const int grid = (int)min((long long)sm_count() * MINB, items);
-  kernel<<<grid, ROWS_THREADS, ROWS_SMEM_BYTES, st>>>(p, flag);
+  launch_dependent(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, p, flag);
   return ROWS_SERVED;
 }
 

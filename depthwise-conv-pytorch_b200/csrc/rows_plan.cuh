@@ -41,6 +41,24 @@ inline bool ensure_smem(KernelT kernel, int bytes, std::atomic<unsigned long lon
   return true;
 }
 
+// Launch with the programmatic-serialization attribute: the kernel may become resident while the
+// kernel before it in the stream drains; it calls pdl_wait() before touching global memory.
+template <typename KernelT, typename... Args>
+inline void launch_dependent(KernelT kernel, int grid, int block, int smem_bytes, cudaStream_t st,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  (void)cudaLaunchKernelEx(&cfg, kernel, args...);  // errors are read by the caller (peek)
+}
+
 // What the planner needs to know about one problem.
 struct PlanInput {
   int K, S, mode;    // mode of the x/in window (backward-filter: MODE_FWD)
