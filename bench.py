@@ -204,7 +204,7 @@ def gpu_arm(args, layers):
     import torch.distributed as dist
     import dwconv_b200
     from dwconv_b200 import _lib
-    from dwconv_b200.dist import FilterGradReducer
+    from dwconv_b200.dist import FilterGradReducer, PeerFilterExchange
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -255,21 +255,48 @@ def gpu_arm(args, layers):
                                                  b["dw"].data_ptr(), b["ws"].data_ptr(), b["nws"],
                                                  b["code"], b["shape"], st), "backward_filter")
 
+    # N > 1: the filter gradient is summed over the GPUs inside its second pass (peer stores over
+    # NVLink, one exchange object per layer); if peer mapping is not possible on this machine the
+    # step falls back to one NCCL all-reduce of the packed gradients on a side stream
+    exchanges = None
+    if world > 1 and not args.nccl_reduce:
+        try:
+            exchanges = [PeerFilterExchange(C, k, tdt[dt], dev) for (N, C, H, k, s, p, dt) in layers]
+        except RuntimeError as e:
+            if rank == 0:
+                sys.stderr.write(f"[bench] peer exchange unavailable ({e}); using NCCL all-reduce\n")
+            exchanges = None
+        ok = torch.tensor([1 if exchanges is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            exchanges = None
+
+    def op_backward_filter_exchange(li, b, st, prev=None):
+        # sends this step's gradient to all ranks; the previous step's world sum lands in the
+        # previous buffer set's dw (the exchange is pipelined by one step)
+        exchanges[li].launch(b["x"].data_ptr(), b["dy"].data_ptr(),
+                             prev["dw"].data_ptr() if prev is not None else None,
+                             b["ws"].data_ptr(), b["nws"], b["shape"], st)
+
     OPS = (("forward", op_forward, 1), ("backward_input", op_backward_input, 1),
            ("backward_filter", op_backward_filter, 2))  # launches per call
 
-    def compute_step(bufs, st):
+    def compute_step(bufs, st, local=False, prev=None):
         for b in bufs:
             op_forward(b, st)
-        for b in reversed(bufs):
+        for li in reversed(range(len(bufs))):
+            b = bufs[li]
             op_backward_input(b, st)
-            op_backward_filter(b, st)
+            if exchanges is not None and not local:
+                op_backward_filter_exchange(li, b, st, prev[li] if prev is not None else None)
+            else:
+                op_backward_filter(b, st)
 
     # dW all-reduce: packed into one flat fp32 buffer, on a side stream, overlapped with the
     # next step's kernels; the result is awaited before the next all-reduce starts
     reducer = None
     pending = [None]
-    if world > 1:
+    if world > 1 and exchanges is None:
         reducer = FilterGradReducer([b["dw"].shape for b in sets[0]], dev, side_stream=True)
 
     # ---- one CUDA graph per buffer set (compute only; the collective stays eager) -------
@@ -277,25 +304,27 @@ def gpu_arm(args, layers):
     graphs = None
     torch.cuda.synchronize()
     with torch.cuda.stream(stream):
-        for bufs in sets:  # also the first-call set-up of every kernel, outside capture
-            compute_step(bufs, stream.cuda_stream)
+        for si, bufs in enumerate(sets):  # also every kernel's first-call set-up, outside capture
+            compute_step(bufs, stream.cuda_stream, prev=sets[si - 1])
     stream.synchronize()
     if not args.no_graph:
         graphs = []
-        for bufs in sets:
+        for si, bufs in enumerate(sets):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
-                compute_step(bufs, torch.cuda.current_stream().cuda_stream)
+                compute_step(bufs, torch.cuda.current_stream().cuda_stream, prev=sets[si - 1])
             graphs.append(g)
 
     def compute_only(i):
         if graphs is not None:
             graphs[i % n_sets].replay()
         else:
-            compute_step(sets[i % n_sets], torch.cuda.current_stream().cuda_stream)
+            compute_step(sets[i % n_sets], torch.cuda.current_stream().cuda_stream,
+                         prev=sets[(i - 1) % n_sets])
 
     def step(i):
         bufs = sets[i % n_sets]
+        last_step[0] = i
         compute_only(i)
         if reducer is not None:
             if pending[0] is not None:
@@ -303,10 +332,15 @@ def gpu_arm(args, layers):
             pending[0] = [b["dw"] for b in bufs]
             reducer.start(pending[0])
 
+    last_step = [0]
+
     def drain():
         if reducer is not None and pending[0] is not None:
             reducer.finish(pending[0])
             pending[0] = None
+        if exchanges is not None:  # complete the last step's sum
+            for ex, b in zip(exchanges, sets[last_step[0] % n_sets]):
+                ex.finish(b["dw"], stream=torch.cuda.current_stream().cuda_stream)
 
     def barrier():
         if world > 1:
@@ -342,6 +376,26 @@ def gpu_arm(args, layers):
             z.record(stream)
             stream.synchronize()
             op_ms[name] = a.elapsed_time(z) / reps
+        # N > 1: every rank's step without the exchange, and the filter gradient with it, so that
+        # the cost of the exchange can be read off (all ranks run this loop together)
+        multi = None
+        if world > 1 and exchanges is not None:
+            multi = {}
+            for name, fn in (("local_step_ms", lambda i: compute_step(sets[i % n_sets], stream.cuda_stream, local=True)),
+                             ("filter_exchange_ms", lambda i: [op_backward_filter_exchange(li, b, stream.cuda_stream)
+                                                               for li, b in enumerate(sets[i % n_sets])])):
+                for i in range(3):
+                    fn(i)
+                a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                for i in range(reps):
+                    fn(i)
+                z.record(stream)
+                stream.synchronize()
+                t = torch.tensor([a.elapsed_time(z) / reps], device=dev, dtype=torch.float64)
+                gathered = [torch.zeros_like(t) for _ in range(world)]
+                dist.all_gather(gathered, t)
+                multi[name] = [round(float(v.item()), 5) for v in gathered]
         # context for the roofline: what a plain device copy of one operator's traffic (read |x|,
         # write |y| of the first layer) achieves at THIS size, same stream and timing
         b0 = sets[0][0]
@@ -362,7 +416,8 @@ def gpu_arm(args, layers):
             t_need = t_load0 + 0.8
             i = 0
             while time.perf_counter() < t_need:
-                compute_only(i)  # rank 0 only: no collective in here
+                # rank 0 only: nothing in here may wait for another rank
+                compute_step(sets[i % n_sets], stream.cuda_stream, local=True)
                 i += 1
                 if i % 64 == 0:
                     stream.synchronize()
@@ -448,8 +503,10 @@ def gpu_arm(args, layers):
                       f"between reuses; L2 is 126 MB)",
                 "cuda_graph": graphs is not None,
                 "algorithmic_bytes_per_step": sb,
-                "parallelism": f"dp{world} (batch-sharded, one all-reduce of dW)" if world > 1
-                               else "single GPU",
+                "parallelism": "single GPU" if world == 1 else (
+                    f"dp{world} (batch-sharded; dW summed over the GPUs inside the filter-gradient "
+                    "kernel by peer stores over NVLink)" if exchanges is not None else
+                    f"dp{world} (batch-sharded; one NCCL all-reduce of dW per step, overlapped)"),
             },
             "frac_of_8TBs": round(value / world / 8000.0, 4),
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 2),
@@ -466,6 +523,7 @@ def gpu_arm(args, layers):
                        f"batch cut into chunks of {pipes[0].chunk} images, upload / kernels / "
                        "download on three streams",
                 "gpu_launches_per_step": sum(p.launches_per_run for p in pipes)},
+            "per_rank": multi,
             "gpu_launches": launches,
             "clocks": clocks,
             "cpu_baseline": cpu_entry,
@@ -484,6 +542,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly")
+    ap.add_argument("--nccl-reduce", action="store_true",
+                    help="N > 1: sum dW with an NCCL all-reduce instead of the in-kernel exchange")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)

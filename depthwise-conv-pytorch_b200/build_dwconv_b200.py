@@ -42,14 +42,28 @@ def is_stale():
     return any(os.path.getmtime(f) > t for f in _deps())
 
 
+def _recorded_deps(dep_file):
+    """Project files a translation unit included, from the dependency file nvcc wrote."""
+    try:
+        with open(dep_file) as f:
+            words = f.read().replace("\\\n", " ").split()
+    except OSError:
+        return None
+    roots = (os.path.realpath(CSRC), os.path.realpath(INCLUDE))
+    deps = [w for w in words[1:] if os.path.realpath(w).startswith(roots)]
+    return deps if all(os.path.exists(d) for d in deps) else None
+
+
 def _compile_one(nvcc, src, verbose):
     obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
-    newest = max(os.path.getmtime(f) for f in [src] + glob.glob(os.path.join(CSRC, "*.cuh"))
-                 + glob.glob(os.path.join(INCLUDE, "*.h")))
-    if os.path.exists(obj) and os.path.getmtime(obj) >= newest:
-        return obj, ""
+    dep_file = obj[:-2] + ".d"
+    deps = _recorded_deps(dep_file) if os.path.exists(obj) else None
+    if deps is not None:
+        newest = max(os.path.getmtime(f) for f in [src] + deps)
+        if os.path.getmtime(obj) >= newest:
+            return obj, ""
     cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
-        "-I", INCLUDE, "-I", CSRC, "-c", "-o", obj, src]
+        "-I", INCLUDE, "-I", CSRC, "-MD", "-MF", dep_file, "-c", "-o", obj, src]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"nvcc failed on {os.path.basename(src)}:\n{res.stdout}{res.stderr}")

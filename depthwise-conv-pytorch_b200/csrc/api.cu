@@ -3,9 +3,11 @@
 #include <atomic>
 #include <cstdint>
 #include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "direct_kernels.cuh"
+#include "peer_exchange.cuh"
 #include "rows_api.cuh"
 
 using namespace dwb;
@@ -111,12 +113,12 @@ size_t filter_workspace_t(const Shape &s) {
   return b < 16 ? 16 : ((b + 15) / 16) * 16;
 }
 
+// First pass of the filter gradient: partial sums per (channel, slice, tap) into ws.
 template <typename T>
-int backward_filter_t(const void *x, const void *dy, void *dw, void *ws, size_t ws_bytes,
-                      const Shape &s, cudaStream_t st, int forced) {
+int filter_first_pass_t(const void *x, const void *dy, void *ws, size_t ws_bytes, const Shape &s,
+                        cudaStream_t st, int forced, int *slices) {
   using A = typename Elem<T>::acc_t;
   if (ws_bytes < filter_workspace_t<T>(s)) return DWCONV_B200_WORKSPACE_TOO_SMALL;
-  const int kk = s.kh * s.kw;
   int S = 0;
   if (forced != DWCONV_B200_PATH_DIRECT) {
     int r = rows_backward_filter<T>((const T *)x, (const T *)dy, (A *)ws, s, st, &S);
@@ -137,17 +139,88 @@ int backward_filter_t(const void *x, const void *dy, void *dw, void *ws, size_t 
     int e = launch_status();
     if (e != DWCONV_B200_OK) return e;
   }
-  // second pass, launched so that it can be resident before the first pass has drained
+  *slices = S;
+  return DWCONV_B200_OK;
+}
+
+// Second-pass launches can be resident before the first pass has drained.
+inline cudaLaunchConfig_t finalize_config(int blocks, cudaStream_t st, cudaLaunchAttribute *attr) {
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(finalize_blocks(s.C, kk));
+  cfg.gridDim = dim3(blocks);
   cfg.blockDim = dim3(FINALIZE_THREADS);
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  return cfg;
+}
+
+template <typename T>
+int backward_filter_t(const void *x, const void *dy, void *dw, void *ws, size_t ws_bytes,
+                      const Shape &s, cudaStream_t st, int forced) {
+  using A = typename Elem<T>::acc_t;
+  int S = 0;
+  int e = filter_first_pass_t<T>(x, dy, ws, ws_bytes, s, st, forced, &S);
+  if (e != DWCONV_B200_OK) return e;
+  const int kk = s.kh * s.kw;
+  cudaLaunchAttribute attr[1];
+  cudaLaunchConfig_t cfg = finalize_config(finalize_blocks(s.C, kk), st, attr);
   (void)cudaLaunchKernelEx(&cfg, backward_filter_finalize_kernel<T>, (const A *)ws, (T *)dw, s.C, kk, S);
+  return launch_status();
+}
+
+// ---- filter gradient summed over the GPUs of one node (peer_exchange.cuh) ----
+__device__ int g_exchange_error_flag = 0;
+
+}  // namespace
+
+struct dwconv_b200_exchange {
+  int world, rank, device;
+  int dtype, C, kh, kw;  // the one layer geometry this buffer is laid out for
+  size_t bytes;
+  unsigned char *local;                       // cudaMalloc'ed here, zeroed
+  unsigned char *peer[EXCHANGE_MAX_WORLD];    // peer[rank] == local; others opened by IPC
+  bool connected;
+  int *error_flag;
+};
+
+namespace {
+
+inline ExchangePeers exchange_peers(const dwconv_b200_exchange *ex) {
+  ExchangePeers px;
+  for (int r = 0; r < EXCHANGE_MAX_WORLD; ++r) px.buf[r] = r < ex->world ? ex->peer[r] : nullptr;
+  px.world = ex->world;
+  px.rank = ex->rank;
+  return px;
+}
+
+template <typename T>
+int exchange_finish_t(void *dw, dwconv_b200_exchange *ex, cudaStream_t st) {
+  const int kk = ex->kh * ex->kw;
+  exchange_finish_kernel<T><<<finalize_blocks(ex->C, kk), FINALIZE_OUTPUTS, 0, st>>>(
+      (T *)dw, ex->C * kk, exchange_peers(ex), ex->error_flag);
+  return launch_status();
+}
+
+template <typename T>
+int backward_filter_exchange_t(const void *x, const void *dy, void *dw, void *ws, size_t ws_bytes,
+                               const Shape &s, dwconv_b200_exchange *ex, cudaStream_t st,
+                               int forced) {
+  using A = typename Elem<T>::acc_t;
+  const int kk = s.kh * s.kw;
+  const int blocks = finalize_blocks(s.C, kk);
+  if (ex->C != s.C || ex->kh != s.kh || ex->kw != s.kw || sizeof(A) != (ex->dtype == DWCONV_B200_F64 ? 8 : 4) ||
+      ex->bytes < exchange_bytes<A>(ex->world, s.C * kk, blocks))
+    return DWCONV_B200_BAD_ARGUMENT;
+  int S = 0;
+  int e = filter_first_pass_t<T>(x, dy, ws, ws_bytes, s, st, forced, &S);
+  if (e != DWCONV_B200_OK) return e;
+  const ExchangePeers px = exchange_peers(ex);
+  cudaLaunchAttribute attr[1];
+  cudaLaunchConfig_t cfg = finalize_config(blocks, st, attr);
+  (void)cudaLaunchKernelEx(&cfg, backward_filter_finalize_exchange_kernel<T>, (const A *)ws, (T *)dw,
+                           s.C, kk, S, px, ex->error_flag);
   return launch_status();
 }
 
@@ -202,7 +275,126 @@ int dwconv_b200_device_status(void) {
     t_last_cuda_error = (int)cudaGetLastError();
     return -1;
   }
-  return rows_take_device_error();
+  int v = rows_take_device_error();
+  int ex = 0;
+  if (cudaMemcpyFromSymbol(&ex, g_exchange_error_flag, sizeof(int)) == cudaSuccess && ex != 0) {
+    const int zero = 0;
+    (void)cudaMemcpyToSymbol(g_exchange_error_flag, &zero, sizeof(int));
+    v |= 4;
+  } else {
+    (void)cudaGetLastError();
+  }
+  return v;
+}
+
+size_t dwconv_b200_exchange_bytes(int dtype, int C, int kh, int kw, int world) {
+  if (C <= 0 || kh <= 0 || kw <= 0 || world <= 0 || world > EXCHANGE_MAX_WORLD) return 0;
+  const int n = C * kh * kw, blocks = finalize_blocks(C, kh * kw);
+  if ((long long)C * kh * kw > (1ll << 26)) return 0;
+  if (dtype == DWCONV_B200_F64) return exchange_bytes<double>(world, n, blocks);
+  if (dtype == DWCONV_B200_F32 || dtype == DWCONV_B200_F16) return exchange_bytes<float>(world, n, blocks);
+  return 0;
+}
+
+int dwconv_b200_exchange_create(int dtype, int C, int kh, int kw, int world, int rank,
+                                dwconv_b200_exchange **out, unsigned char *handle64) {
+  const size_t bytes = dwconv_b200_exchange_bytes(dtype, C, kh, kw, world);
+  if (out == nullptr || handle64 == nullptr || bytes == 0 || rank < 0 || rank >= world)
+    return DWCONV_B200_BAD_ARGUMENT;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
+  dwconv_b200_exchange *ex = new dwconv_b200_exchange();
+  ex->world = world;
+  ex->rank = rank;
+  ex->dtype = dtype;
+  ex->C = C;
+  ex->kh = kh;
+  ex->kw = kw;
+  ex->bytes = bytes;
+  ex->local = nullptr;
+  ex->connected = (world == 1);
+  for (int r = 0; r < EXCHANGE_MAX_WORLD; ++r) ex->peer[r] = nullptr;
+  cudaIpcMemHandle_t h;
+  if (cudaGetDevice(&ex->device) != cudaSuccess ||
+      cudaMalloc((void **)&ex->local, bytes) != cudaSuccess ||
+      cudaMemset(ex->local, 0, bytes) != cudaSuccess ||
+      cudaDeviceSynchronize() != cudaSuccess ||
+      cudaGetSymbolAddress((void **)&ex->error_flag, g_exchange_error_flag) != cudaSuccess ||
+      (world > 1 && cudaIpcGetMemHandle(&h, ex->local) != cudaSuccess)) {
+    t_last_cuda_error = (int)cudaGetLastError();
+    if (ex->local) (void)cudaFree(ex->local);
+    delete ex;
+    return DWCONV_B200_CUDA_ERROR;
+  }
+  ex->peer[rank] = ex->local;
+  if (world > 1) memcpy(handle64, &h, 64); else memset(handle64, 0, 64);
+  *out = ex;
+  return DWCONV_B200_OK;
+}
+
+int dwconv_b200_exchange_connect(dwconv_b200_exchange *ex, const unsigned char *handles) {
+  if (ex == nullptr || (ex->world > 1 && handles == nullptr)) return DWCONV_B200_BAD_ARGUMENT;
+  if (ex->connected) return DWCONV_B200_OK;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev != ex->device) return DWCONV_B200_BAD_ARGUMENT;
+  for (int r = 0; r < ex->world; ++r) {
+    if (r == ex->rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handles + (size_t)64 * r, 64);
+    void *p = nullptr;
+    // opened with this rank's GPU current: maps the peer's buffer here and enables peer access
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+      t_last_cuda_error = (int)cudaGetLastError();
+      return DWCONV_B200_CUDA_ERROR;
+    }
+    ex->peer[r] = (unsigned char *)p;
+  }
+  ex->connected = true;
+  return DWCONV_B200_OK;
+}
+
+int dwconv_b200_exchange_destroy(dwconv_b200_exchange *ex) {
+  if (ex == nullptr) return DWCONV_B200_OK;
+  (void)cudaDeviceSynchronize();
+  for (int r = 0; r < ex->world; ++r)
+    if (r != ex->rank && ex->peer[r] != nullptr) (void)cudaIpcCloseMemHandle(ex->peer[r]);
+  if (ex->local) (void)cudaFree(ex->local);
+  (void)cudaGetLastError();
+  delete ex;
+  return DWCONV_B200_OK;
+}
+
+int dwconv_b200_exchange_finish(void *dw, dwconv_b200_exchange *ex, void *stream) {
+  if (ex == nullptr || !ex->connected || dw == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  if (!aligned_to(dw, elem_size(ex->dtype))) return DWCONV_B200_MISALIGNED;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (ex->dtype) {
+    case DWCONV_B200_F32: return exchange_finish_t<float>(dw, ex, st);
+    case DWCONV_B200_F16: return exchange_finish_t<__half>(dw, ex, st);
+    default: return exchange_finish_t<double>(dw, ex, st);
+  }
+}
+
+int dwconv_b200_backward_filter_exchange(const void *x, const void *dy, void *dw_prev, void *workspace,
+                                         size_t workspace_bytes, int dtype,
+                                         const dwconv_b200_shape *shape, dwconv_b200_exchange *ex,
+                                         void *stream) {
+  const void *dw = dw_prev != nullptr ? dw_prev : x;  // dw_prev is optional
+  int e = check_ptrs(dtype, x, dy, dw);
+  if (e) return e;
+  e = check_shape(shape);
+  if (e) return e;
+  if (ex == nullptr || !ex->connected || workspace == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  if (!aligned_to(workspace, 16)) return DWCONV_B200_MISALIGNED;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int forced = g_forced_path.load();
+  switch (dtype) {
+    case DWCONV_B200_F32:
+      return backward_filter_exchange_t<float>(x, dy, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+    case DWCONV_B200_F16:
+      return backward_filter_exchange_t<__half>(x, dy, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+    default:
+      return backward_filter_exchange_t<double>(x, dy, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+  }
 }
 
 int dwconv_b200_out_size(int in, int up, int pad0, int pad1, int k, int down) {

@@ -4,14 +4,15 @@ Images are independent, so forward and backward-input need no communication: eac
 (one process per GPU) runs them on its contiguous slice of the batch.  The filter gradient
 is a sum over the batch, so the local dW of every layer is packed into one flat fp32
 buffer and summed with a single ``all_reduce`` (NCCL over NVLink on GPUs, gloo in the CPU
-tests), on a side stream so it can overlap the next step's forward.
+tests), on a side stream so it can overlap the next step's forward -- or, on the GPUs of one
+node, summed inside the kernel that finishes the gradient (``PeerFilterExchange``).
 
 The reference has no distributed code; this module is new surface, outside its API.
 """
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_bounds", "shard_batch", "FilterGradReducer"]
+__all__ = ["shard_bounds", "shard_batch", "FilterGradReducer", "PeerFilterExchange"]
 
 
 def shard_bounds(n, world_size, rank):
@@ -88,3 +89,96 @@ class FilterGradReducer:
     def reduce(self, grads):
         self.start(grads)
         return self.finish(grads)
+
+
+class PeerFilterExchange:
+    """Filter gradient of ONE layer summed over the GPUs of a node inside the kernel that
+    finishes it (``dwconv_b200_backward_filter_exchange``): no separate collective launch.
+
+    Construction is collective over ``group`` (every rank creates the object for the same
+    layers in the same order): each rank allocates its exchange buffer, the 64-byte
+    inter-process handles are all-gathered on the host, and every rank maps its peers'
+    buffers.  ``torch.distributed`` is used for that hand-shake only.
+
+    The exchange is pipelined (a store to a peer needs several microseconds to become visible
+    there): ``start(x, dy, ..., dw_prev)`` computes this call's local gradient, sends it to every
+    rank and writes the PREVIOUS call's world sum into ``dw_prev``; ``finish(dw)`` completes the
+    latest call.  ``backward_filter(x, dy)`` is ``start`` + ``finish``.  The world sum has
+    identical bits on every rank.  All ranks must make the same calls.  Needs all ranks on one
+    node with peer access between their GPUs; raises ``RuntimeError`` otherwise (use
+    ``FilterGradReducer`` then).
+    """
+
+    def __init__(self, channels, kernel_size, dtype, device, group=None):
+        from . import _lib
+        import ctypes
+        self._lib = _lib
+        kh, kw = (kernel_size, kernel_size) if isinstance(kernel_size, int) else kernel_size
+        self.C, self.kh, self.kw = int(channels), int(kh), int(kw)
+        self.dtype = dtype
+        self.code = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64}[dtype]
+        self.device = torch.device(device)
+        self.group = group
+        multi = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if multi else 1
+        self.rank = dist.get_rank(group) if multi else 0
+        self._ex = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib.dwconv_b200_exchange_create(
+                self.code, self.C, self.kh, self.kw, self.world, self.rank,
+                ctypes.byref(self._ex), handle), "exchange_create")
+            if self.world > 1:
+                handles = [None] * self.world
+                dist.all_gather_object(handles, bytes(handle.raw), group=group)
+                _lib.check(_lib.lib.dwconv_b200_exchange_connect(self._ex, b"".join(handles)),
+                           "exchange_connect")
+                dist.barrier(group=group)  # nobody sends before every rank has mapped its peers
+        self._ws = None
+
+    def start(self, x, dy, stride=1, padding=0, dw_prev=None):
+        """Local gradient of (x, dy), sent to all ranks; ``dw_prev`` (optional) receives the
+        previous call's world sum."""
+        _lib = self._lib
+        N, C, H, W = x.shape
+        sh, sw = (stride, stride) if isinstance(stride, int) else stride
+        ph, pw = (padding, padding) if isinstance(padding, int) else padding
+        shape = _lib.Shape(N, C, H, W, self.kh, self.kw, sh, sw, ph, pw, dy.shape[2], dy.shape[3])
+        nws = int(_lib.lib.dwconv_b200_backward_filter_workspace_bytes(self.code, shape))
+        if self._ws is None or self._ws.numel() < nws:
+            self._ws = torch.empty(nws, dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            self.launch(x.data_ptr(), dy.data_ptr(), dw_prev.data_ptr() if dw_prev is not None else None,
+                        self._ws.data_ptr(), nws, shape,
+                        torch.cuda.current_stream(self.device).cuda_stream)
+
+    def finish(self, dw=None, stream=None):
+        """World sum of the latest ``start`` (waits for the peers' words if still in flight)."""
+        if dw is None:
+            dw = torch.empty((self.C, 1, self.kh, self.kw), dtype=self.dtype, device=self.device)
+        with torch.cuda.device(self.device):
+            st = stream if stream is not None else torch.cuda.current_stream(self.device).cuda_stream
+            self._lib.check(self._lib.lib.dwconv_b200_exchange_finish(dw.data_ptr(), self._ex, st),
+                            "exchange_finish")
+        return dw
+
+    def backward_filter(self, x, dy, stride=1, padding=0, dw=None):
+        self.start(x, dy, stride, padding)
+        return self.finish(dw)
+
+    def launch(self, x_ptr, dy_ptr, dw_prev_ptr, ws_ptr, ws_bytes, shape, stream):
+        """Raw-pointer form of ``start`` (what a CUDA-graph capture of a training step calls)."""
+        self._lib.check(self._lib.lib.dwconv_b200_backward_filter_exchange(
+            x_ptr, dy_ptr, dw_prev_ptr, ws_ptr, ws_bytes, self.code, shape, self._ex, stream),
+            "backward_filter_exchange")
+
+    def close(self):
+        if self._ex:
+            self._lib.lib.dwconv_b200_exchange_destroy(self._ex)
+            self._ex = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001  (interpreter shutdown)
+            pass

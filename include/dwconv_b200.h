@@ -89,7 +89,8 @@ DWCONV_B200_API int dwconv_b200_last_cuda_error(void);
 /* Every wait inside a kernel (on a bulk copy landing in shared memory) is bounded; a kernel
  * whose wait expires raises a flag, finishes without hanging and leaves wrong output.
  * This call synchronises the device, returns the flags raised since the last call (0 = none;
- * bit 0 forward/backward-input kernels, bit 1 backward-filter kernels) and clears them.
+ * bit 0 forward/backward-input kernels, bit 1 backward-filter kernels, bit 2 the exchange between
+ * GPUs) and clears them.
  * Diagnostic: not needed on the hot path.  No counterpart in the reference. */
 DWCONV_B200_API int dwconv_b200_device_status(void);
 
@@ -139,6 +140,54 @@ DWCONV_B200_API size_t dwconv_b200_backward_filter_workspace_bytes(int dtype, co
 DWCONV_B200_API int dwconv_b200_backward_filter(const void *x, const void *dy, void *dw, void *workspace,
                                 size_t workspace_bytes, int dtype,
                                 const dwconv_b200_shape *shape, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Filter gradient summed over the GPUs of one node, inside the second pass.
+ *
+ * The reference has no multi-GPU code; a data-parallel caller of it sums dW
+ * with a separate all-reduce after dwconv2d_backward_kernel
+ * (torch_dwconv/dwconv.py:66-68).  Here the second pass of the reduction
+ * stores each rank's sums straight into its peers' exchange buffers (plain
+ * peer stores over NVLink, each 32-bit word in one 8-byte store together with
+ * its call number) and the receiving side adds the ranks' values in rank
+ * order: every rank ends with the same bits, run after run.  A peer store needs
+ * several microseconds to become visible, so the exchange is pipelined: call i
+ * sends call i's sums and completes call i-1's.
+ *
+ *   exchange_bytes    size of one rank's exchange buffer for a layer's filter
+ *                     (0: bad arguments; world <= 8).
+ *   exchange_create   allocates and zeroes that buffer on the current device
+ *                     (the one entry point of this library that allocates) for
+ *                     ONE layer geometry (dtype, C, kh, kw) and writes its
+ *                     64-byte inter-process handle.  Collect every rank's
+ *                     handle (rank order) with any host-side all-gather.
+ *   exchange_connect  maps the peers' buffers; `handles` = world x 64 bytes.
+ *   backward_filter_exchange
+ *                     first pass as dwconv_b200_backward_filter; the second
+ *                     pass sends this call's sums to every rank and writes the
+ *                     PREVIOUS call's world sum to dw_prev (null: not wanted;
+ *                     nothing is written on the first call).
+ *   exchange_finish   dw = the world sum of the latest call.  Waits for the
+ *                     peers' words if they are still in flight.
+ *
+ * Every rank must make the same sequence of backward_filter_exchange calls
+ * with the same geometry; one exchange object serves one layer, one call at a
+ * time (calls on one stream are).  BAD_ARGUMENT if the shape is not the
+ * object's.  A rank that waits for a peer's word longer than about two seconds
+ * stops waiting, leaves that output unwritten and raises bit 2 (value 4) of
+ * dwconv_b200_device_status.
+ * ---------------------------------------------------------------------- */
+typedef struct dwconv_b200_exchange dwconv_b200_exchange;
+DWCONV_B200_API size_t dwconv_b200_exchange_bytes(int dtype, int C, int kh, int kw, int world);
+DWCONV_B200_API int dwconv_b200_exchange_create(int dtype, int C, int kh, int kw, int world, int rank,
+                                                dwconv_b200_exchange **out, unsigned char *handle64);
+DWCONV_B200_API int dwconv_b200_exchange_connect(dwconv_b200_exchange *ex, const unsigned char *handles);
+DWCONV_B200_API int dwconv_b200_exchange_destroy(dwconv_b200_exchange *ex);
+DWCONV_B200_API int dwconv_b200_exchange_finish(void *dw, dwconv_b200_exchange *ex, void *stream);
+DWCONV_B200_API int dwconv_b200_backward_filter_exchange(const void *x, const void *dy, void *dw_prev,
+                                                         void *workspace, size_t workspace_bytes,
+                                                         int dtype, const dwconv_b200_shape *shape,
+                                                         dwconv_b200_exchange *ex, void *stream);
 
 /* ------------------------------------------------------------------------
  * Operator-form entry points: one per function of the reference's pybind

@@ -29,7 +29,8 @@ def _worker(rank, world, port, q):
         import torch.distributed as dist
         import dwconv_b200
         import oracle
-        from dwconv_b200.dist import FilterGradReducer, shard_batch, shard_bounds
+        from dwconv_b200.dist import FilterGradReducer, PeerFilterExchange, shard_batch, shard_bounds
+        from dwconv_b200 import _lib
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world,
                                 device_id=torch.device("cuda", rank))
@@ -52,6 +53,30 @@ def _worker(rank, world, port, q):
             assert torch.equal(xs.grad.cpu(), oracle.backward_input_seq(dy, w, (H, H), s, p)[lo:hi])
             grads.append(ws.grad)
             checks.append((x, dy, k, s, p, dt))
+            # the same sum made inside the filter-gradient kernel by peer stores: three calls
+            # in a row (both halves of the exchange buffer get reused), identical on both ranks
+            ex = PeerFilterExchange(C, k, dt, torch.device("cuda", rank))
+            truth = oracle.backward_filter(x, dy, (k, k), s, p)
+            rel = 1e-2 if dt == torch.float16 else 1e-4
+            for _ in range(3):
+                got = ex.backward_filter(xs.detach(), shard_batch(dy, world, rank).cuda(), s, p)
+                both = [torch.empty_like(got) for _ in range(world)]
+                dist.all_gather(both, got)
+                assert torch.equal(both[0], both[1]), "ranks disagree on the exchanged dW"
+                err = (got.double().cpu() - truth).abs().max().item()
+                assert err <= rel * truth.abs().max().item(), err
+            # pipelined form: the second start() delivers the first call's sum
+            dys = shard_batch(dy, world, rank).cuda()
+            first = torch.full_like(got, float("nan"))
+            ex.start(xs.detach(), dys, s, p)
+            ex.start(xs.detach() * 2, dys, s, p, dw_prev=first)
+            second = ex.finish()
+            torch.cuda.synchronize()
+            assert torch.equal(first, got)
+            err = (second.double().cpu() - 2 * truth).abs().max().item()
+            assert err <= 2 * rel * truth.abs().max().item(), err
+            assert _lib.lib.dwconv_b200_device_status() == 0
+            ex.close()
         red = FilterGradReducer([t.shape for t in grads], torch.device("cuda", rank))
         summed = red.reduce(grads)
         torch.cuda.synchronize()

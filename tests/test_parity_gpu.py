@@ -313,3 +313,32 @@ def test_other_stream_and_device_guard():
         y = dwconv_b200.depthwise_conv2d(x, w, padding=1)
     side.synchronize()
     assert torch.equal(y.cpu(), oracle.forward_seq(x, w, 1, 1))
+
+
+@pytest.mark.parametrize("shape,k,s,p,dtype", [
+    ((6, 24, 14, 14), 3, 1, 1, torch.float32),
+    ((3, 10, 28, 28), 5, 2, 2, torch.float16),
+    ((2, 5, 9, 9), 3, 1, 1, torch.float64),
+    ((2, 7, 20, 20), 13, 1, 6, torch.float32),
+])
+def test_exchange_entry_point_with_one_rank_equals_plain(shape, k, s, p, dtype):
+    """World size 1: the fused second pass sends to itself and must give the plain result
+    bit for bit, call after call (the exchange buffer's two halves alternate)."""
+    from dwconv_b200.dist import PeerFilterExchange
+    x, w, dy = seeded(shape, (k, k), s, p, dtype, seed=21)
+    st, want = c_backward_filter(x, dy, (k, k), s, p)
+    assert st == 0
+    ex = PeerFilterExchange(shape[1], k, dtype, x.device)
+    for _ in range(4):
+        got = ex.backward_filter(x, dy, s, p)
+        assert torch.equal(got, want)
+    # pipelined form: a later start() delivers the earlier call's result
+    earlier = torch.full_like(want, float("nan"))
+    ex.start(x, dy, s, p)
+    ex.start(x * 2, dy, s, p, dw_prev=earlier)
+    later = ex.finish()
+    assert torch.equal(earlier, want)
+    st2, want2 = c_backward_filter(x * 2, dy, (k, k), s, p)
+    assert st2 == 0 and torch.equal(later, want2)
+    assert _lib.lib.dwconv_b200_device_status() == 0
+    ex.close()
