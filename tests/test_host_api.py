@@ -189,3 +189,34 @@ def test_chunk_bounds_cover_the_batch_once():
     assert len(chunk_bounds(128, 451584)) == 8            # eight chunks of 16 images
     assert len(chunk_bounds(1000, 1000)) == 1             # too small to be worth cutting
     assert [hi - lo for lo, hi in chunk_bounds(13, 5000, 4)] == [4, 4, 4, 1]
+
+
+def test_conv2d_interchange_round_trip():
+    import dwconv_b200
+    conv = torch.nn.Conv2d(6, 6, 5, stride=2, padding=2, groups=6, bias=False)
+    m = dwconv_b200.from_conv2d(conv)
+    assert isinstance(m, dwconv_b200.DepthwiseConv2d)
+    assert torch.equal(m.weight, conv.weight) and m.weight.data_ptr() != conv.weight.data_ptr()
+    assert dwconv_b200.make_tuple(m.stride, 2) == (2, 2) and m.kernel_size == 5
+    back = dwconv_b200.to_conv2d(m)
+    assert back.groups == 6 and back.bias is None and torch.equal(back.weight, conv.weight)
+    x = torch.randn(2, 6, 9, 9)
+    assert torch.equal(back(x), conv(x))
+    # state_dict keys and shapes are interchangeable as they are
+    conv.load_state_dict(m.state_dict())
+    for bad in (torch.nn.Conv2d(6, 6, 3, groups=6, bias=True), torch.nn.Conv2d(6, 6, 3, groups=3, bias=False),
+                torch.nn.Conv2d(6, 6, 3, groups=6, dilation=2, bias=False),
+                torch.nn.Conv2d(6, 12, 3, groups=6, bias=False)):
+        with pytest.raises(ValueError):
+            dwconv_b200.from_conv2d(bad)
+
+
+def test_depthwise_stack_layout():
+    import dwconv_b200
+    stack = dwconv_b200.DepthwiseStack()
+    assert len(stack.layers) == 7
+    assert stack.input_shapes(128)[0] == (128, 32, 112, 112) and stack.input_shapes(2)[-1] == (2, 1152, 7, 7)
+    assert [tuple(l.weight.shape) for l in stack.layers][2] == (144, 1, 5, 5)
+    assert sorted(stack.state_dict()) == [f"layers.{i}.weight" for i in range(7)]
+    with pytest.raises(ValueError):
+        stack([torch.zeros(1)])
