@@ -4,6 +4,7 @@
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #include "common.cuh"
 #include "direct_kernels.cuh"
@@ -13,6 +14,9 @@
 using namespace dwb;
 
 namespace {
+
+// The rows family is compiled for fp32 and fp16; everything else runs on the direct family.
+template <typename T> constexpr bool kRowsCompiled = !std::is_same<T, __nv_bfloat16>::value;
 
 std::atomic<int> g_forced_path{DWCONV_B200_PATH_AUTO};
 thread_local int t_last_path = DWCONV_B200_PATH_AUTO;
@@ -24,6 +28,7 @@ inline size_t elem_size(int dtype) {
   switch (dtype) {
     case DWCONV_B200_F32: return 4;
     case DWCONV_B200_F16: return 2;
+    case DWCONV_B200_BF16: return 2;
     case DWCONV_B200_F64: return 8;
     default: return 0;
   }
@@ -68,9 +73,30 @@ inline int direct_filter_slices(const Shape &s) {
 }
 
 template <typename T>
+int try_rows_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st) {
+  if constexpr (kRowsCompiled<T>) return rows_forward<T>(x, w, y, s, st);
+  return ROWS_DECLINED;
+}
+template <typename T>
+int try_rows_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStream_t st) {
+  if constexpr (kRowsCompiled<T>) return rows_backward_input<T>(dy, w, dx, s, st);
+  return ROWS_DECLINED;
+}
+template <typename T> int try_rows_backward_filter_slices(const Shape &s) {
+  if constexpr (kRowsCompiled<T>) return rows_backward_filter_slices<T>(s);
+  return 0;
+}
+template <typename T>
+int try_rows_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *partial, const Shape &s,
+                             cudaStream_t st, int *slices_out) {
+  if constexpr (kRowsCompiled<T>) return rows_backward_filter<T>(x, dy, partial, s, st, slices_out);
+  return ROWS_DECLINED;
+}
+
+template <typename T>
 int forward_t(const void *x, const void *w, void *y, const Shape &s, cudaStream_t st, int forced) {
   if (forced != DWCONV_B200_PATH_DIRECT) {
-    int r = rows_forward<T>((const T *)x, (const T *)w, (T *)y, s, st);
+    int r = try_rows_forward<T>((const T *)x, (const T *)w, (T *)y, s, st);
     if (r == ROWS_SERVED) {
       t_last_path = DWCONV_B200_PATH_ROWS;
       return launch_status();
@@ -88,7 +114,7 @@ template <typename T>
 int backward_input_t(const void *dy, const void *w, void *dx, const Shape &s, cudaStream_t st,
                      int forced) {
   if (forced != DWCONV_B200_PATH_DIRECT) {
-    int r = rows_backward_input<T>((const T *)dy, (const T *)w, (T *)dx, s, st);
+    int r = try_rows_backward_input<T>((const T *)dy, (const T *)w, (T *)dx, s, st);
     if (r == ROWS_SERVED) {
       t_last_path = DWCONV_B200_PATH_ROWS;
       return launch_status();
@@ -107,7 +133,7 @@ size_t filter_workspace_t(const Shape &s) {
   using A = typename Elem<T>::acc_t;
   const size_t kk = (size_t)s.kh * s.kw;
   size_t slices = (size_t)direct_filter_slices(s);
-  const size_t rs = (size_t)rows_backward_filter_slices<T>(s);
+  const size_t rs = (size_t)try_rows_backward_filter_slices<T>(s);
   if (rs > slices) slices = rs;
   size_t b = (size_t)s.C * slices * kk * sizeof(A);
   return b < 16 ? 16 : ((b + 15) / 16) * 16;
@@ -121,7 +147,7 @@ int filter_first_pass_t(const void *x, const void *dy, void *ws, size_t ws_bytes
   if (ws_bytes < filter_workspace_t<T>(s)) return DWCONV_B200_WORKSPACE_TOO_SMALL;
   int S = 0;
   if (forced != DWCONV_B200_PATH_DIRECT) {
-    int r = rows_backward_filter<T>((const T *)x, (const T *)dy, (A *)ws, s, st, &S);
+    int r = try_rows_backward_filter<T>((const T *)x, (const T *)dy, (A *)ws, s, st, &S);
     if (r == ROWS_SERVED) {
       t_last_path = DWCONV_B200_PATH_ROWS;
       int e = launch_status();
@@ -292,7 +318,8 @@ size_t dwconv_b200_exchange_bytes(int dtype, int C, int kh, int kw, int world) {
   const int n = C * kh * kw, blocks = finalize_blocks(C, kh * kw);
   if ((long long)C * kh * kw > (1ll << 26)) return 0;
   if (dtype == DWCONV_B200_F64) return exchange_bytes<double>(world, n, blocks);
-  if (dtype == DWCONV_B200_F32 || dtype == DWCONV_B200_F16) return exchange_bytes<float>(world, n, blocks);
+  if (dtype == DWCONV_B200_F32 || dtype == DWCONV_B200_F16 || dtype == DWCONV_B200_BF16)
+    return exchange_bytes<float>(world, n, blocks);
   return 0;
 }
 
@@ -370,6 +397,7 @@ int dwconv_b200_exchange_finish(void *dw, dwconv_b200_exchange *ex, void *stream
   switch (ex->dtype) {
     case DWCONV_B200_F32: return exchange_finish_t<float>(dw, ex, st);
     case DWCONV_B200_F16: return exchange_finish_t<__half>(dw, ex, st);
+    case DWCONV_B200_BF16: return exchange_finish_t<__nv_bfloat16>(dw, ex, st);
     default: return exchange_finish_t<double>(dw, ex, st);
   }
 }
@@ -392,6 +420,8 @@ int dwconv_b200_backward_filter_exchange(const void *x, const void *dy, void *dw
       return backward_filter_exchange_t<float>(x, dy, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
     case DWCONV_B200_F16:
       return backward_filter_exchange_t<__half>(x, dy, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+    case DWCONV_B200_BF16:
+      return backward_filter_exchange_t<__nv_bfloat16>(x, dy, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
     default:
       return backward_filter_exchange_t<double>(x, dy, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
   }
@@ -415,6 +445,7 @@ int dwconv_b200_forward(const void *x, const void *w, void *y, int dtype,
   switch (dtype) {
     case DWCONV_B200_F32: return forward_t<float>(x, w, y, *shape, st, forced);
     case DWCONV_B200_F16: return forward_t<__half>(x, w, y, *shape, st, forced);
+    case DWCONV_B200_BF16: return forward_t<__nv_bfloat16>(x, w, y, *shape, st, forced);
     default: return forward_t<double>(x, w, y, *shape, st, forced);
   }
 }
@@ -430,6 +461,7 @@ int dwconv_b200_backward_input(const void *dy, const void *w, void *dx, int dtyp
   switch (dtype) {
     case DWCONV_B200_F32: return backward_input_t<float>(dy, w, dx, *shape, st, forced);
     case DWCONV_B200_F16: return backward_input_t<__half>(dy, w, dx, *shape, st, forced);
+    case DWCONV_B200_BF16: return backward_input_t<__nv_bfloat16>(dy, w, dx, *shape, st, forced);
     default: return backward_input_t<double>(dy, w, dx, *shape, st, forced);
   }
 }
@@ -439,6 +471,7 @@ size_t dwconv_b200_backward_filter_workspace_bytes(int dtype, const dwconv_b200_
   switch (dtype) {
     case DWCONV_B200_F32: return filter_workspace_t<float>(*shape);
     case DWCONV_B200_F16: return filter_workspace_t<__half>(*shape);
+    case DWCONV_B200_BF16: return filter_workspace_t<__nv_bfloat16>(*shape);
     default: return filter_workspace_t<double>(*shape);
   }
 }
@@ -459,6 +492,8 @@ int dwconv_b200_backward_filter(const void *x, const void *dy, void *dw, void *w
       return backward_filter_t<float>(x, dy, dw, workspace, workspace_bytes, *shape, st, forced);
     case DWCONV_B200_F16:
       return backward_filter_t<__half>(x, dy, dw, workspace, workspace_bytes, *shape, st, forced);
+    case DWCONV_B200_BF16:
+      return backward_filter_t<__nv_bfloat16>(x, dy, dw, workspace, workspace_bytes, *shape, st, forced);
     default:
       return backward_filter_t<double>(x, dy, dw, workspace, workspace_bytes, *shape, st, forced);
   }

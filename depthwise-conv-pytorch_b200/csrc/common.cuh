@@ -1,6 +1,7 @@
 // Shared device/host helpers of libdwconv_b200: element traits, status plumbing.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -24,6 +25,12 @@ template <> struct Elem<__half> {
   static __device__ __forceinline__ float ld(const __half *p) { return __half2float(__ldg(p)); }
   static __device__ __forceinline__ float to_acc(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_acc(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {  // served by the direct family only
+  using acc_t = float;
+  static __device__ __forceinline__ float ld(const __nv_bfloat16 *p) { return __bfloat162float(__ldg(p)); }
+  static __device__ __forceinline__ float to_acc(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_acc(float v) { return __float2bfloat16_rn(v); }
 };
 template <> struct Elem<double> {
   using acc_t = double;

@@ -87,7 +87,7 @@ int dwconv_b200_backward_filter_static(const void *x, const void *dy, void *dw, 
   if ((long long)s->H * s->W >= lim || (long long)s->Ho * s->Wo >= lim ||
       (long long)s->kh * s->kw >= (1ll << 20) || (long long)s->N * s->C >= (1ll << 31) - 1)
     return DWCONV_B200_TOO_LARGE;
-  const size_t es = dtype == DWCONV_B200_F32 ? 4 : dtype == DWCONV_B200_F16 ? 2
+  const size_t es = dtype == DWCONV_B200_F32 ? 4 : (dtype == DWCONV_B200_F16 || dtype == DWCONV_B200_BF16) ? 2
                     : dtype == DWCONV_B200_F64 ? 8 : 0;
   if (es == 0) return DWCONV_B200_UNSUPPORTED_DTYPE;
   if (((uintptr_t)x % es) || ((uintptr_t)dy % es) || ((uintptr_t)dw % es))
@@ -96,6 +96,7 @@ int dwconv_b200_backward_filter_static(const void *x, const void *dy, void *dw, 
   switch (dtype) {
     case DWCONV_B200_F32: return run<float>(x, dy, dw, *s, st);
     case DWCONV_B200_F16: return run<__half>(x, dy, dw, *s, st);
+    case DWCONV_B200_BF16: return run<__nv_bfloat16>(x, dy, dw, *s, st);
     default: return run<double>(x, dy, dw, *s, st);
   }
 }

@@ -9,7 +9,8 @@ import torch
 
 from . import _lib
 
-_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64}
+_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64,
+           torch.bfloat16: _lib.BF16}
 
 
 def _check_cuda(t, name):
@@ -21,7 +22,7 @@ def _check_cuda(t, name):
 def _dtype_code(t, *others):
     code = _DTYPES.get(t.dtype)
     if code is None:
-        raise RuntimeError(f"dwconv_b200: unsupported dtype {t.dtype} (float32, float16, float64)")
+        raise RuntimeError(f"dwconv_b200: unsupported dtype {t.dtype} (float32, float16, bfloat16, float64)")
     for o in others:
         if o.dtype != t.dtype or o.device != t.device:
             raise RuntimeError("dwconv_b200: tensors must share dtype and device "

@@ -9,7 +9,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__
                         "libdwconv_b200.so")
 _BUILD_HINT = "python depthwise-conv-pytorch_b200/build_dwconv_b200.py"
 
-F32, F16, F64 = 0, 1, 2
+F32, F16, F64, BF16 = 0, 1, 2, 3
 PATH_AUTO, PATH_DIRECT, PATH_ROWS = 0, 1, 2
 OK = 0
 

@@ -116,7 +116,8 @@ class PeerFilterExchange:
         kh, kw = (kernel_size, kernel_size) if isinstance(kernel_size, int) else kernel_size
         self.C, self.kh, self.kw = int(channels), int(kh), int(kw)
         self.dtype = dtype
-        self.code = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64}[dtype]
+        self.code = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64,
+           torch.bfloat16: _lib.BF16}[dtype]
         self.device = torch.device(device)
         self.group = group
         multi = dist.is_available() and dist.is_initialized()

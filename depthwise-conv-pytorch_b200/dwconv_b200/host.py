@@ -14,7 +14,8 @@ import torch
 
 from . import _lib
 
-_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64}
+_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64,
+           torch.bfloat16: _lib.BF16}
 
 
 def _pair(v):
@@ -51,7 +52,7 @@ class HostMapsStep:
         sh, sw = _pair(stride)
         ph, pw = _pair(padding)
         if dtype not in _DTYPES:
-            raise RuntimeError(f"dwconv_b200: unsupported dtype {dtype} (float32, float16, float64)")
+            raise RuntimeError(f"dwconv_b200: unsupported dtype {dtype} (float32, float16, bfloat16, float64)")
         L = _lib.lib
         Ho = L.dwconv_b200_out_size(H, 1, ph, ph, kh, sh)
         Wo = L.dwconv_b200_out_size(W, 1, pw, pw, kw, sw)

@@ -21,7 +21,8 @@ EFFICIENTNET_B0_DEPTHWISE = (
     (480, 14, 5, 1), (672, 14, 5, 2), (1152, 7, 3, 1),
 )
 
-_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64}
+_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64,
+           torch.bfloat16: _lib.BF16}
 
 
 def from_conv2d(conv):

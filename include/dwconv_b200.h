@@ -46,8 +46,9 @@ extern "C" {
 
 typedef enum dwconv_b200_dtype {
   DWCONV_B200_F32 = 0,
-  DWCONV_B200_F16 = 1,
-  DWCONV_B200_F64 = 2
+  DWCONV_B200_F16 = 1,  /* accumulates in fp32 (the reference accumulates in half) */
+  DWCONV_B200_F64 = 2,
+  DWCONV_B200_BF16 = 3  /* not in the reference; fp32 accumulation; general-purpose kernels only */
 } dwconv_b200_dtype;
 
 typedef enum dwconv_b200_status {

@@ -6,7 +6,8 @@ import torch
 import oracle
 from dwconv_b200 import _lib
 
-CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64}
+CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.float64: _lib.F64,
+        torch.bfloat16: _lib.BF16}
 
 
 def pair(v):

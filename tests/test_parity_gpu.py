@@ -342,3 +342,34 @@ def test_exchange_entry_point_with_one_rank_equals_plain(shape, k, s, p, dtype):
     assert st2 == 0 and torch.equal(later, want2)
     assert _lib.lib.dwconv_b200_device_status() == 0
     ex.close()
+
+
+@pytest.mark.parametrize("shape,k,s,p", [
+    ((3, 6, 14, 14), (3, 3), 1, 1),
+    ((2, 4, 20, 17), (5, 5), 2, 2),
+    ((2, 3, 12, 12), (3, 5), (1, 2), (1, 2)),
+    ((1, 5, 33, 33), (7, 7), 1, 3),
+])
+def test_bfloat16_against_oracle(shape, k, s, p):
+    """bfloat16 (not a reference dtype): fp32 accumulation, one rounding at the end, compared
+    with the fp64 oracle evaluated on the same bf16-rounded inputs; autograd form included."""
+    import dwconv_b200
+    x, w, dy = seeded(shape, k, s, p, torch.bfloat16, seed=31)
+    xf, wf, dyf = x.float().cpu(), w.float().cpu(), dy.float().cpu()
+    H, W = shape[2:]
+    st, y = c_forward(x, w, s, p)
+    assert st == 0 and last_path() == _lib.PATH_DIRECT
+    st, dx = c_backward_input(dy, w, (H, W), s, p)
+    assert st == 0
+    st, dw = c_backward_filter(x, dy, k, s, p)
+    assert st == 0
+    for got, want, name in ((y, oracle.forward(xf, wf, s, p), "y"),
+                            (dx, oracle.backward_input(dyf, wf, (H, W), s, p), "dx"),
+                            (dw, oracle.backward_filter(xf, dyf, k, s, p), "dw")):
+        want = want.double()
+        err = (got.double().cpu() - want).abs().max().item()
+        assert err <= 1e-2 * max(1.0, want.abs().max().item()), f"{name}: {err}"
+    if k[0] == k[1] and isinstance(s, int):
+        xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        dwconv_b200.depthwise_conv2d(xr, wr, None, s, p).backward(dy)
+        assert torch.equal(xr.grad, dx) and torch.equal(wr.grad, dw)
