@@ -26,11 +26,25 @@ template <> struct ConvU<3, 1, MODE_FWD> { static constexpr int n = 4; static co
 template <> struct ConvU<5, 1, MODE_FWD> { static constexpr int n = 2; static constexpr int v[4] = {4, 7, 7, 7}; };
 template <> struct ConvU<7, 1, MODE_FWD> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };
 template <> struct ConvU<3, 2, MODE_FWD> { static constexpr int n = 3; static constexpr int v[4] = {2, 4, 7, 7}; };
-template <> struct ConvU<5, 2, MODE_FWD> { static constexpr int n = 2; static constexpr int v[4] = {2, 4, 4, 4}; };
+template <> struct ConvU<5, 2, MODE_FWD> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };  // 4 measured slower (and spills at VI = 4)
 template <> struct ConvU<7, 2, MODE_FWD> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };
 template <> struct ConvU<3, 2, MODE_BWD> { static constexpr int n = 3; static constexpr int v[4] = {4, 8, 14, 14}; };
 template <> struct ConvU<5, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[4] = {4, 14, 14, 14}; };
 template <> struct ConvU<7, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[4] = {2, 4, 4, 4}; };
+
+// Options above this height spill registers for the given vector width (ptxas -v) and measured
+// slower; the tables are ascending, so a cap keeps a prefix.
+constexpr int conv_u_cap(int K, int S, int mode, int VI) {
+  if (VI == 4 && K == 3 && S == 1) return 8;
+  if (VI == 4 && K == 5 && S == 1) return 4;
+  return 1 << 20;
+}
+template <int K, int S, int MODE, int VI> constexpr int conv_u_count() {
+  int n = 0;
+  for (int i = 0; i < ConvU<K, S, MODE>::n; ++i)
+    if (ConvU<K, S, MODE>::v[i] <= conv_u_cap(K, S, MODE, VI)) ++n;
+  return n;
+}
 
 int *conv_flag_address() {
   static std::atomic<int *> cached[64];
@@ -64,14 +78,15 @@ int launch_variant(const RowsParams &p, cudaStream_t st) {
 template <typename T, int K, int S, int MODE, int VI, int VO, int I>
 int launch_u(const RowsParams &p, int U, bool mask, bool exact, cudaStream_t st) {
   constexpr int UI = ConvU<K, S, MODE>::v[I];
-  if (U == UI || I + 1 >= ConvU<K, S, MODE>::n) {
+  constexpr int N = conv_u_count<K, S, MODE, VI>();
+  if (U == UI || I + 1 >= N) {
     if (mask)
       return exact ? launch_variant<T, K, S, MODE, VI, VO, UI, true, true>(p, st)
                    : launch_variant<T, K, S, MODE, VI, VO, UI, true, false>(p, st);
     return exact ? launch_variant<T, K, S, MODE, VI, VO, UI, false, true>(p, st)
                  : launch_variant<T, K, S, MODE, VI, VO, UI, false, false>(p, st);
   }
-  if constexpr (I + 1 < ConvU<K, S, MODE>::n)
+  if constexpr (I + 1 < N)
     return launch_u<T, K, S, MODE, VI, VO, I + 1>(p, U, mask, exact, st);
   else
     return ROWS_DECLINED;
@@ -86,7 +101,7 @@ int launch_conv(RowsParams p, cudaStream_t st) {
   if (p.LW == 0) return ROWS_DECLINED;
   PlanInput in{K, S, MODE, p.Hin, p.Win, p.Hout, p.Wout, (int)sizeof(T),
                ROWS_CWARPS * (32 / p.LW), p.NC, 0, sm_count() * conv_minb(K), false};
-  const TilePlan t = plan_best(in, ConvU<K, S, MODE>::v, ConvU<K, S, MODE>::n);
+  const TilePlan t = plan_best(in, ConvU<K, S, MODE>::v, conv_u_count<K, S, MODE, VI>());
   if (!t.ok) return ROWS_DECLINED;
   p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;
   p.inv_NRB = magic_of(p.NRB);

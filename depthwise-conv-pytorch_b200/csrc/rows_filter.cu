@@ -20,7 +20,7 @@ template <int K, int S> struct FilterU;
 template <> struct FilterU<3, 1> { static constexpr int n = 4; static constexpr int v[4] = {4, 7, 8, 14}; };
 template <> struct FilterU<5, 1> { static constexpr int n = 2; static constexpr int v[4] = {2, 4, 4, 4}; };
 template <> struct FilterU<7, 1> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };
-template <> struct FilterU<3, 2> { static constexpr int n = 3; static constexpr int v[4] = {2, 4, 7, 7}; };
+template <> struct FilterU<3, 2> { static constexpr int n = 2; static constexpr int v[4] = {2, 4, 4, 4}; };  // 7 measured slower
 template <> struct FilterU<5, 2> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };
 template <> struct FilterU<7, 2> { static constexpr int n = 1; static constexpr int v[4] = {1, 1, 1, 1}; };
 
@@ -52,6 +52,18 @@ struct FilterPlan {
   bool mask, exact;
 };
 
+// Options above this height spill registers for the given vector width (ptxas -v); the tables
+// are ascending, so a cap keeps a prefix.
+constexpr int filter_u_cap(int K, int S, int VI) {
+  return (VI == 4 && K == 3 && S == 1) ? 8 : (1 << 20);
+}
+template <int K, int S> constexpr int filter_u_count(int VI) {
+  int n = 0;
+  for (int i = 0; i < FilterU<K, S>::n; ++i)
+    if (FilterU<K, S>::v[i] <= filter_u_cap(K, S, VI)) ++n;
+  return n;
+}
+
 template <typename T, int K, int S>
 bool plan_filter_ks(const Shape &s, bool a16, FilterPlan &f) {
   if (!pick_v(S, s.W, s.Wo, a16, f.VI, f.VO)) return false;
@@ -62,7 +74,7 @@ bool plan_filter_ks(const Shape &s, bool a16, FilterPlan &f) {
   if (p.LW == 0) return false;
   PlanInput in{K, S, MODE_FWD, s.H, s.W, s.Ho, s.Wo, (int)sizeof(T),
                ROWS_CWARPS * (32 / p.LW), s.C, 0, 0, true};
-  const TilePlan t = plan_best(in, FilterU<K, S>::v, FilterU<K, S>::n);
+  const TilePlan t = plan_best(in, FilterU<K, S>::v, filter_u_count<K, S>(f.VI));
   if (!t.ok) return false;
   p.N = s.N; p.C = s.C; p.H = s.H; p.W = s.W; p.Ho = s.Ho; p.Wo = s.Wo;
   p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;
@@ -136,14 +148,15 @@ int launch_variant(const RowsFilterParams &p, cudaStream_t st) {
 template <typename T, int K, int S, int VI, int VO, int I>
 int launch_filter_u(const FilterPlan &f, cudaStream_t st) {
   constexpr int UI = FilterU<K, S>::v[I];
-  if (f.U == UI || I + 1 >= FilterU<K, S>::n) {
+  constexpr int N = filter_u_count<K, S>(VI);
+  if (f.U == UI || I + 1 >= N) {
     if (f.mask)
       return f.exact ? launch_variant<T, K, S, VI, VO, UI, true, true>(f.p, st)
                      : launch_variant<T, K, S, VI, VO, UI, true, false>(f.p, st);
     return f.exact ? launch_variant<T, K, S, VI, VO, UI, false, true>(f.p, st)
                    : launch_variant<T, K, S, VI, VO, UI, false, false>(f.p, st);
   }
-  if constexpr (I + 1 < FilterU<K, S>::n)
+  if constexpr (I + 1 < N)
     return launch_filter_u<T, K, S, VI, VO, I + 1>(f, st);
   else
     return ROWS_DECLINED;

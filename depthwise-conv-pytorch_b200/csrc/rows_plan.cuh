@@ -2,6 +2,8 @@
 #pragma once
 
 #include <atomic>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -203,7 +205,49 @@ inline TilePlan plan_search(PlanInput in, const int *u_options, int n_options) {
 
 // Planning walks a few hundred candidates; results are remembered per problem so that a
 // repeated launch costs one table lookup.
+// Tuning aid: DWCONV_B200_FORCE_PLAN="fwd=U,G,NRT,TH,NRB,NST;bwd=...;flt=..." (read once per
+// process) replaces the planner's choice for forward (and stride-1 backward-input, which is the
+// same kernel), stride-2 backward-input, or backward-filter.  A tiling that does not fit is refused.
+inline bool forced_plan(const PlanInput &in, TilePlan &out) {
+  static const char *env = std::getenv("DWCONV_B200_FORCE_PLAN");
+  if (env == nullptr) return false;
+  const char *key = in.filter ? "flt=" : (in.mode == MODE_BWD ? "bwd=" : "fwd=");
+  const char *at = std::strstr(env, key);
+  if (at == nullptr) return false;
+  int v[6] = {0, 0, 0, 0, 0, 0};
+  if (std::sscanf(at + 4, "%d,%d,%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3], &v[4], &v[5]) != 6) return false;
+  PlanInput pin = in;
+  TilePlan c{};
+  c.G = v[1]; c.NRT = v[2]; c.TH = v[3]; c.NRB = v[4];
+  if (v[5] < 2 || v[5] > 3 || c.G < 1 || c.NRT < 1 || c.TH < 1 || c.NRB < 1 || c.G > in.maxG ||
+      ceil_div(in.Hout, c.TH) != c.NRT)
+    return false;
+  pin.stage_bytes = ROWS_RING_BYTES / v[5];
+  if (!plan_finish(pin, v[0], c)) return false;
+  c.NST = v[5];
+  out = c;
+  return true;
+}
+
+// Tuning aid: DWCONV_B200_FORCE_U="fwd=U;bwd=U;flt=U" restricts the planner to one chunk height.
+inline int forced_u(const PlanInput &in) {
+  static const char *env = std::getenv("DWCONV_B200_FORCE_U");
+  if (env == nullptr) return 0;
+  const char *at = std::strstr(env, in.filter ? "flt=" : (in.mode == MODE_BWD ? "bwd=" : "fwd="));
+  return at ? std::atoi(at + 4) : 0;
+}
+
 inline TilePlan plan_best(const PlanInput &in, const int *u_options, int n_options) {
+  {
+    TilePlan forced{};
+    if (forced_plan(in, forced)) {
+      for (int i = 0; i < n_options; ++i)
+        if (u_options[i] == forced.U) return forced;
+    }
+    const int fu = forced_u(in);
+    for (int i = 0; fu > 0 && i < n_options; ++i)
+      if (u_options[i] == fu) return plan_search(in, &u_options[i], 1);
+  }
   struct Entry {
     int key[16];
     TilePlan plan;
