@@ -260,27 +260,32 @@ template <> struct SmemLd<__half, 4> {
   }
 };
 
-// V fp32 registers to global memory as one vector store of T.
+// V fp32 registers to global memory as one vector store of T.  The stores are streaming
+// (evict-first): an output map is not read again by the kernel that writes it, and keeping it from
+// displacing the input maps lets the next operator of a training step find x / dy still in L2.
 template <typename T, int V> struct GmemSt;
 template <> struct GmemSt<float, 1> {
-  static __device__ __forceinline__ void st(float *p, const float (&v)[1]) { *p = v[0]; }
+  static __device__ __forceinline__ void st(float *p, const float (&v)[1]) { __stcs(p, v[0]); }
 };
 template <> struct GmemSt<float, 2> {
   static __device__ __forceinline__ void st(float *p, const float (&v)[2]) {
-    *reinterpret_cast<float2 *>(p) = make_float2(v[0], v[1]);
+    __stcs(reinterpret_cast<float2 *>(p), make_float2(v[0], v[1]));
   }
 };
 template <> struct GmemSt<float, 4> {
   static __device__ __forceinline__ void st(float *p, const float (&v)[4]) {
-    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
   }
 };
 template <> struct GmemSt<__half, 1> {
-  static __device__ __forceinline__ void st(__half *p, const float (&v)[1]) { *p = __float2half_rn(v[0]); }
+  static __device__ __forceinline__ void st(__half *p, const float (&v)[1]) {
+    __stcs(reinterpret_cast<unsigned short *>(p), __half_as_ushort(__float2half_rn(v[0])));
+  }
 };
 template <> struct GmemSt<__half, 2> {
   static __device__ __forceinline__ void st(__half *p, const float (&v)[2]) {
-    *reinterpret_cast<__half2 *>(p) = __halves2half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
+    __half2 a = __halves2half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
+    __stcs(reinterpret_cast<unsigned int *>(p), *reinterpret_cast<unsigned int *>(&a));
   }
 };
 template <> struct GmemSt<__half, 4> {
@@ -290,7 +295,7 @@ template <> struct GmemSt<__half, 4> {
     uint2 raw;
     raw.x = *reinterpret_cast<uint32_t *>(&a);
     raw.y = *reinterpret_cast<uint32_t *>(&b);
-    *reinterpret_cast<uint2 *>(p) = raw;
+    __stcs(reinterpret_cast<uint2 *>(p), raw);
   }
 };
 

@@ -20,7 +20,7 @@ template <int K, int S> struct FilterU;
 template <> struct FilterU<3, 1> { static constexpr int n = 4; static constexpr int v[4] = {4, 7, 8, 14}; };
 template <> struct FilterU<5, 1> { static constexpr int n = 2; static constexpr int v[4] = {2, 4, 4, 4}; };
 template <> struct FilterU<7, 1> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };
-template <> struct FilterU<3, 2> { static constexpr int n = 2; static constexpr int v[4] = {2, 4, 4, 4}; };  // 7 measured slower
+template <> struct FilterU<3, 2> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };  // 4 and 7 measured slower
 template <> struct FilterU<5, 2> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };
 template <> struct FilterU<7, 2> { static constexpr int n = 1; static constexpr int v[4] = {1, 1, 1, 1}; };
 
