@@ -307,7 +307,7 @@ def gpu_arm(args, layers):
         for si, bufs in enumerate(sets):  # also every kernel's first-call set-up, outside capture
             compute_step(bufs, stream.cuda_stream, prev=sets[si - 1])
     stream.synchronize()
-    if not args.no_graph:
+    if not args.no_graph and args.launch != "eager":
         graphs = []
         for si, bufs in enumerate(sets):
             g = torch.cuda.CUDAGraph()
@@ -315,8 +315,10 @@ def gpu_arm(args, layers):
                 compute_step(bufs, torch.cuda.current_stream().cuda_stream, prev=sets[si - 1])
             graphs.append(g)
 
+    use_graph = [graphs is not None]
+
     def compute_only(i):
-        if graphs is not None:
+        if use_graph[0]:
             graphs[i % n_sets].replay()
         else:
             compute_step(sets[i % n_sets], torch.cuda.current_stream().cuda_stream,
@@ -348,9 +350,35 @@ def gpu_arm(args, layers):
         torch.cuda.synchronize()
 
     sampler = ClockSampler(local) if rank == 0 else None
+    calibration = None
     with torch.cuda.stream(stream):
+        if graphs is not None and args.launch == "auto":
+            # Replaying a graph saves host time per launch; launching eagerly lets each kernel
+            # become resident while the previous step's last kernel drains (programmatic dependent
+            # launch does not reach across graph boundaries).  Which wins depends on the step's
+            # length, so time a few steps each way and keep the faster (same choice on all ranks).
+            calibration = {}
+            for mode in (True, False):
+                use_graph[0] = mode
+                for i in range(10):
+                    step(i)
+                drain()
+                barrier()
+                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                c0.record(stream)
+                for i in range(120):
+                    step(i)
+                drain()
+                c1.record(stream)
+                barrier()
+                t = torch.tensor([c0.elapsed_time(c1) / 120], device=dev, dtype=torch.float64)
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                calibration["graph_ms" if mode else "eager_ms"] = round(float(t.item()), 5)
+            use_graph[0] = calibration["graph_ms"] <= calibration["eager_ms"]
         for i in range(max(args.warmup, 3)):
             step(i)
+        drain()
         barrier()
         t_load0 = time.perf_counter()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -501,7 +529,8 @@ def gpu_arm(args, layers):
                 "per_gpu_batch": layers[0][0],
                 "l2": f"rotating {n_sets} buffer sets ({n_sets * per_set / 1e6:.0f} MB touched "
                       f"between reuses; L2 is 126 MB)",
-                "cuda_graph": graphs is not None,
+                "cuda_graph": use_graph[0],
+                "launch_calibration": calibration,
                 "algorithmic_bytes_per_step": sb,
                 "parallelism": "single GPU" if world == 1 else (
                     f"dp{world} (batch-sharded; dW summed over the GPUs inside the filter-gradient "
@@ -542,6 +571,9 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly")
+    ap.add_argument("--launch", default="auto", choices=["auto", "graph", "eager"],
+                    help="replay one CUDA graph per step, launch eagerly, or time both and keep "
+                         "the faster (default)")
     ap.add_argument("--nccl-reduce", action="store_true",
                     help="N > 1: sum dW with an NCCL all-reduce instead of the in-kernel exchange")
     ap.add_argument("--no-cpu-baseline", action="store_true")
