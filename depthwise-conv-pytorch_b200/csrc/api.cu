@@ -427,6 +427,16 @@ int dwconv_b200_backward_filter_exchange(const void *x, const void *dy, void *dw
   }
 }
 
+int dwconv_b200_copy_async(void *dst, const void *src, size_t bytes, void *stream) {
+  if (bytes == 0) return DWCONV_B200_OK;
+  if (dst == nullptr || src == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  if (cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, (cudaStream_t)stream) != cudaSuccess) {
+    t_last_cuda_error = (int)cudaGetLastError();
+    return DWCONV_B200_CUDA_ERROR;
+  }
+  return DWCONV_B200_OK;
+}
+
 int dwconv_b200_out_size(int in, int up, int pad0, int pad1, int k, int down) {
   if (down <= 0) return 0;
   const long long num = (long long)in * up + pad0 + pad1 - k + down;

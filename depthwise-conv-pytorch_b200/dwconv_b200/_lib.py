@@ -48,6 +48,7 @@ def _load():
         "dwconv_b200_dwconv2d_backward_kernel": (ci, [vp, vp, vp, vp, sz, ci] + [ci] * 14 + [vp]),
         "dwconv_b200_static_scratch_bytes": (sz, []),
         "dwconv_b200_backward_filter_static": (ci, [vp, vp, vp, ci, sp, vp]),
+        "dwconv_b200_copy_async": (ci, [vp, vp, sz, vp]),
         "dwconv_b200_exchange_bytes": (sz, [ci] * 5),
         "dwconv_b200_exchange_create": (ci, [ci] * 6 + [ctypes.POINTER(vp), ctypes.c_char_p]),
         "dwconv_b200_exchange_connect": (ci, [vp, ctypes.c_char_p]),
@@ -76,6 +77,7 @@ EXPORTS = (
     "dwconv_b200_use_dwconv2d_small", "dwconv_b200_dwconv2d", "dwconv_b200_dwconv2d_small",
     "dwconv_b200_dwconv2d_backward_kernel", "dwconv_b200_static_scratch_bytes",
     "dwconv_b200_backward_filter_static",
+    "dwconv_b200_copy_async",
     "dwconv_b200_exchange_bytes", "dwconv_b200_exchange_create", "dwconv_b200_exchange_connect",
     "dwconv_b200_exchange_destroy", "dwconv_b200_exchange_finish",
     "dwconv_b200_backward_filter_exchange",

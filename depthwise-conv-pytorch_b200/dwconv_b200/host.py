@@ -24,9 +24,18 @@ def _pair(v):
 
 def chunk_bounds(n_images, image_bytes, chunk_images=None, target_chunks=8, min_bytes=2 << 20):
     """Cuts a batch into runs of whole images.  By default about ``target_chunks`` equal
-    chunks, but none smaller than ``min_bytes``: measured on PCIe 5 x16 with traffic in both
-    directions, every copy pays about 40 us before its first byte moves, so many small
-    chunks cost more than the shorter un-overlapped first upload and last download save."""
+    chunks, but none smaller than ``min_bytes``: every chunk adds about 30 us of launch work
+    (a dozen stream operations) to the step, measured on PCIe 5 x16, so many small chunks
+    cost more than the shorter un-overlapped first upload and last download save; schedules
+    with small first and last chunks measured the same as equal chunks."""
+    if isinstance(chunk_images, (list, tuple)):  # explicit chunk sizes, in order
+        if sum(chunk_images) != n_images or min(chunk_images) < 1:
+            raise ValueError(f"chunk sizes {list(chunk_images)} do not add up to {n_images} images")
+        bounds, a = [], 0
+        for n in chunk_images:
+            bounds.append((a, a + int(n)))
+            a += int(n)
+        return bounds
     if chunk_images is None:
         chunk_images = max(-(-n_images // target_chunks), -(-min_bytes // max(1, image_bytes)))
     step = max(1, min(int(chunk_images), n_images))
@@ -92,6 +101,15 @@ class HostMapsStep:
         self.d2h_bytes = (N * C * (H * W + Ho * Wo) + C * kh * kw) * esize
         self.launches_per_run = 4 * len(self.bounds)  # forward, backward-input, filter partial + finalize
 
+    def _copy(self, dev_buf, host, a, b, up, stream):
+        """Images a..b of a host map to / from the start of a staging buffer: one bare
+        asynchronous copy (torch's ``copy_`` records an event per pinned copy, which costs tens of
+        microseconds per chunk while the other direction is busy)."""
+        per_image = host.stride(0) * host.element_size()
+        hp, dp, nbytes = host.data_ptr() + a * per_image, dev_buf.data_ptr(), (b - a) * per_image
+        dst, src = (dp, hp) if up else (hp, dp)
+        _lib.check(_lib.lib.dwconv_b200_copy_async(dst, src, nbytes, stream.cuda_stream), "copy_async")
+
     def _shape(self, n):
         C, H, W, kh, kw, sh, sw, ph, pw, Ho, Wo = self._geo
         return _lib.Shape(n, C, H, W, kh, kw, sh, sw, ph, pw, Ho, Wo)
@@ -154,8 +172,8 @@ class HostMapsStep:
             with torch.cuda.stream(self.s_up):
                 if i - self.SLOTS in ran:  # the kernels that read this slot have finished
                     self.s_up.wait_event(ran[i - self.SLOTS])
-                self.x_[k][:n].copy_(x[a:b], non_blocking=True)
-                self.dy_[k][:n].copy_(dy[a:b], non_blocking=True)
+                self._copy(self.x_[k], x, a, b, True, self.s_up)
+                self._copy(self.dy_[k], dy, a, b, True, self.s_up)
                 up = ev()
                 up.record(self.s_up)
             with torch.cuda.stream(self.s_run):
@@ -177,8 +195,8 @@ class HostMapsStep:
                 ran[i].record(self.s_run)
             with torch.cuda.stream(self.s_down):
                 self.s_down.wait_event(ran[i])
-                y[a:b].copy_(yk[:n], non_blocking=True)
-                dx[a:b].copy_(dxk[:n], non_blocking=True)
+                self._copy(yk, y, a, b, False, self.s_down)
+                self._copy(dxk, dx, a, b, False, self.s_down)
                 drained[i] = ev()
                 drained[i].record(self.s_down)
         for s in (self.s_up, self.s_run, self.s_down):

@@ -142,6 +142,14 @@ DWCONV_B200_API int dwconv_b200_backward_filter(const void *x, const void *dy, v
                                 size_t workspace_bytes, int dtype,
                                 const dwconv_b200_shape *shape, void *stream);
 
+/* One asynchronous copy between any two of: device memory, pinned host memory
+ * (direction inferred from the pointers), on `stream`.  A bare copy with nothing recorded
+ * around it, for pipelines that move maps between pinned host memory and the
+ * device (measured: an event recorded after every chunk's copy costs tens of
+ * microseconds per chunk while the other direction is busy).  No counterpart in
+ * the reference, whose callers copy with torch. */
+DWCONV_B200_API int dwconv_b200_copy_async(void *dst, const void *src, size_t bytes, void *stream);
+
 /* ------------------------------------------------------------------------
  * Filter gradient summed over the GPUs of one node, inside the second pass.
  *

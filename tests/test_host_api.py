@@ -189,6 +189,9 @@ def test_chunk_bounds_cover_the_batch_once():
     assert len(chunk_bounds(128, 451584)) == 8            # eight chunks of 16 images
     assert len(chunk_bounds(1000, 1000)) == 1             # too small to be worth cutting
     assert [hi - lo for lo, hi in chunk_bounds(13, 5000, 4)] == [4, 4, 4, 1]
+    assert chunk_bounds(10, 5000, [2, 5, 3]) == [(0, 2), (2, 7), (7, 10)]
+    with pytest.raises(ValueError):
+        chunk_bounds(10, 5000, [2, 5])
 
 
 def test_conv2d_interchange_round_trip():
