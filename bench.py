@@ -204,7 +204,7 @@ def gpu_arm(args, layers):
     import torch.distributed as dist
     import dwconv_b200
     from dwconv_b200 import _lib
-    from dwconv_b200.dist import FilterGradReducer, PeerFilterExchange
+    from dwconv_b200.dist import FilterGradReducer, PeerFilterExchange, bind_to_gpu_numa_node
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -214,6 +214,8 @@ def gpu_arm(args, layers):
             raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # before any pinned host buffer exists: keep this rank on its GPU's NUMA node
+    numa = bind_to_gpu_numa_node(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         from datetime import timedelta
@@ -553,6 +555,7 @@ def gpu_arm(args, layers):
                        "download on three streams",
                 "gpu_launches_per_step": sum(p.launches_per_run for p in pipes)},
             "per_rank": multi,
+            "numa_binding": numa,
             "gpu_launches": launches,
             "clocks": clocks,
             "cpu_baseline": cpu_entry,

@@ -12,7 +12,46 @@ The reference has no distributed code; this module is new surface, outside its A
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_bounds", "shard_batch", "FilterGradReducer", "PeerFilterExchange"]
+import os
+
+__all__ = ["shard_bounds", "shard_batch", "FilterGradReducer", "PeerFilterExchange",
+           "bind_to_gpu_numa_node"]
+
+
+def _parse_cpulist(text):
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def bind_to_gpu_numa_node(device_index, sysfs="/sys"):
+    """Restricts the calling thread (and the threads it starts later) to the CPUs of the NUMA
+    node the GPU is attached to, so that pinned host buffers allocated afterwards live in that
+    node's memory and host<->device copies do not cross sockets.  With one process per GPU on a
+    two-socket machine, unbound ranks otherwise allocate wherever they happen to run.
+    Returns what was done; never raises (a container may hide sysfs)."""
+    info = {"bound": False}
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        addr = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        info["pci"] = addr
+        with open(f"{sysfs}/bus/pci/devices/{addr}/numa_node") as f:
+            node = int(f.read().strip())
+        info["node"] = node
+        if node < 0:
+            return info
+        with open(f"{sysfs}/devices/system/node/node{node}/cpulist") as f:
+            cpus = _parse_cpulist(f.read()) & os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            info.update(bound=True, cpus=len(cpus))
+    except (OSError, ValueError, AttributeError, RuntimeError) as e:
+        info["why"] = f"{type(e).__name__}: {e}"
+    return info
 
 
 def shard_bounds(n, world_size, rank):

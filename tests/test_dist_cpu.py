@@ -110,3 +110,11 @@ def test_rank_failure_surfaces_as_error_not_hang():
     out = _run("rank_fails")
     assert "injected failure" in out[1]
     assert out[0] != "ok"
+
+
+def test_cpulist_parsing_and_binding_never_raises(tmp_path):
+    from dwconv_b200.dist import _parse_cpulist, bind_to_gpu_numa_node
+    assert _parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert _parse_cpulist("") == set()
+    info = bind_to_gpu_numa_node(0, sysfs=str(tmp_path))  # no GPU / no sysfs here: reports, no raise
+    assert info["bound"] is False
