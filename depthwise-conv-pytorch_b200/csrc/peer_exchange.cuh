@@ -84,34 +84,62 @@ __device__ __forceinline__ void exchange_send(const ExchangePeers &px, size_t he
   }
 }
 
-// Adds value idx of call `call` over the ranks, in rank order.  false: a word did not arrive.
+// The words of value idx of call `call`, one load each, all in flight together (a system-scope
+// load takes about a microsecond; eight in a row would take eight).
+template <typename A>
+__device__ __forceinline__ void exchange_preload(const ExchangePeers &px, size_t header, int n, int idx,
+                                                 unsigned call,
+                                                 unsigned long long (&v)[EXCHANGE_MAX_WORLD][ExchangeWords<A>::W]) {
+  constexpr int W = ExchangeWords<A>::W;
+  const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(px.buf[px.rank] + header);
+#pragma unroll
+  for (int r = 0; r < EXCHANGE_MAX_WORLD; ++r) {
+    if (r < px.world) {
+      const unsigned long long *words =
+          mine + ((size_t)(call % EXCHANGE_SLOTS) * px.world + r) * n * W + (size_t)idx * W;
+#pragma unroll
+      for (int k = 0; k < W; ++k) v[r][k] = ld_word_sys(words + k);
+    }
+  }
+}
+
+// Adds value idx of call `call` over the ranks, in rank order, from the preloaded words; a word
+// that had not arrived yet is polled (bounded).  false: a word did not arrive.
 template <typename A>
 __device__ __forceinline__ bool exchange_receive(const ExchangePeers &px, size_t header, int n,
-                                                 int idx, unsigned call, A &sum) {
+                                                 int idx, unsigned call,
+                                                 unsigned long long (&v)[EXCHANGE_MAX_WORLD][ExchangeWords<A>::W],
+                                                 A &sum) {
   constexpr int W = ExchangeWords<A>::W;
   const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(px.buf[px.rank] + header);
   sum = 0;
-  for (int r = 0; r < px.world; ++r) {
-    const unsigned long long *words =
-        mine + ((size_t)(call % EXCHANGE_SLOTS) * px.world + r) * n * W + (size_t)idx * W;
-    unsigned w[W];
 #pragma unroll
-    for (int k = 0; k < W; ++k) {
-      unsigned polls = 0;
-      unsigned long long v = ld_word_sys(words + k);
-      while ((unsigned)(v >> 32) != call) {
-        if (++polls > EXCHANGE_MAX_POLLS) return false;
-        __nanosleep(200);
-        v = ld_word_sys(words + k);
+  for (int r = 0; r < EXCHANGE_MAX_WORLD; ++r) {
+    if (r < px.world) {
+      const unsigned long long *words =
+          mine + ((size_t)(call % EXCHANGE_SLOTS) * px.world + r) * n * W + (size_t)idx * W;
+      unsigned w[W];
+#pragma unroll
+      for (int k = 0; k < W; ++k) {
+        unsigned polls = 0;
+        unsigned long long word = v[r][k];
+        while ((unsigned)(word >> 32) != call) {
+          if (++polls > EXCHANGE_MAX_POLLS) return false;
+          __nanosleep(200);
+          word = ld_word_sys(words + k);
+        }
+        w[k] = (unsigned)word;
       }
-      w[k] = (unsigned)v;
+      sum += ExchangeWords<A>::join(w);
     }
-    sum += ExchangeWords<A>::join(w);
   }
   return true;
 }
 
 // dw_prev: where the PREVIOUS call's world sum goes (may be null: not wanted).
+// (Measured alternative, not kept: staging the sums and sending them from a small kernel on a
+// second stream, to hide the time the peer stores take to be acknowledged, was slower on two
+// GPUs: 80.8 against 78.3 us per step.)
 template <typename T>
 __global__ void __launch_bounds__(FINALIZE_THREADS)
 backward_filter_finalize_exchange_kernel(const typename Elem<T>::acc_t *__restrict__ partial,
@@ -127,6 +155,16 @@ backward_filter_finalize_exchange_kernel(const typename Elem<T>::acc_t *__restri
   const int idx = b * FINALIZE_OUTPUTS + o;
   const bool live = idx < n;
   A acc = 0;
+  // The previous call's words do not depend on this call's first pass: warp 0 starts loading
+  // them before waiting for it (reads of this rank's own exchange buffer only).
+  const size_t header = exchange_header_bytes(gridDim.x);
+  unsigned *my_calls = reinterpret_cast<unsigned *>(px.buf[px.rank]);
+  unsigned call = 0;
+  unsigned long long words[EXCHANGE_MAX_WORLD][ExchangeWords<A>::W];
+  if (part == 0) {
+    call = my_calls[b] + 1u;  // the same on every rank: all ranks make the same calls
+    if (live && call > 1u) exchange_preload<A>(px, header, n, idx, call - 1u, words);
+  }
   pdl_wait();  // the first pass has finished and its partial sums are visible
   if (live) {
     const int c = idx / kk;
@@ -142,16 +180,13 @@ backward_filter_finalize_exchange_kernel(const typename Elem<T>::acc_t *__restri
 #pragma unroll
   for (int q = 1; q < FINALIZE_PARTS; ++q) total += part_sum[q][o];
 
-  const size_t header = exchange_header_bytes(gridDim.x);
-  unsigned *my_calls = reinterpret_cast<unsigned *>(px.buf[px.rank]);
-  const unsigned call = my_calls[b] + 1u;  // the same on every rank: all ranks make the same calls
   bool ok = true;
   if (live) {
     // receive before sending: a peer that sees this call's words knows that this rank is done
     // reading the previous call's, which is what makes three slots enough (see the top)
     if (call > 1u) {
       A sum;
-      ok = exchange_receive<A>(px, header, n, idx, call - 1u, sum);
+      ok = exchange_receive<A>(px, header, n, idx, call - 1u, words, sum);
       if (ok && dw_prev != nullptr) dw_prev[idx] = Elem<T>::from_acc(sum);
     }
     exchange_send<A>(px, header, n, idx, call, total);
@@ -176,7 +211,9 @@ exchange_finish_kernel(T *__restrict__ dw, const int n, const ExchangePeers px,
   bool ok = true;
   if (idx < n && call > 0u) {
     A sum;
-    ok = exchange_receive<A>(px, header, n, idx, call, sum);
+    unsigned long long words[EXCHANGE_MAX_WORLD][ExchangeWords<A>::W];
+    exchange_preload<A>(px, header, n, idx, call, words);
+    ok = exchange_receive<A>(px, header, n, idx, call, words, sum);
     if (ok) dw[idx] = Elem<T>::from_acc(sum);
   }
   ok = __all_sync(0xffffffffu, ok);
