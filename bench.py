@@ -15,7 +15,9 @@ gradient over ranks with one all-reduce).  Rank 0 prints ONE JSON line:
 * ``roofline``   the slowest of the three operators, timed alone with CUDA events, against
                  the measured HBM copy bandwidth (MEASURED_PEAKS.json);
 * ``cpu_baseline`` the reference's CPU route timed on this machine's host cores (rank 0);
-* ``clocks``     SM clock / throttle reasons sampled with nvidia-smi while the GPU was loaded.
+* ``clocks``     SM clock / throttle reasons sampled with nvidia-smi while the GPU was loaded;
+* ``timing_spread`` median and best of 60 steps timed one by one, and the L2-warm step (one
+                 buffer set reused), beside the headline mean over the rotating sets.
 
 ``--impl reference`` times only the reference's CPU route (see oracle/cpu_baseline.py) and
 prints the same line with ``"impl": "reference"``.
@@ -391,6 +393,30 @@ def gpu_arm(args, layers):
         e1.record(stream)
         barrier()
         ms_total = e0.elapsed_time(e1)
+        # ---- spread of single steps (each bracketed by its own events, which costs a little
+        # overlap), and the same step with L2 warm (one buffer set over and over) ------------
+        n_single = 60
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(n_single + 1)]
+        for i in range(n_single):
+            marks[i].record(stream)
+            step(i)
+        drain()
+        marks[n_single].record(stream)
+        stream.synchronize()
+        singles = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(n_single))
+        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(5):
+            compute_step(sets[0], stream.cuda_stream, local=True)
+        w0.record(stream)
+        for _ in range(n_single):
+            compute_step(sets[0], stream.cuda_stream, local=True)
+        w1.record(stream)
+        stream.synchronize()
+        spread = {"single_step_median_ms": round(statistics.median(singles), 5),
+                  "single_step_best_ms": round(singles[0], 5),
+                  "l2_warm_ms_per_step": round(w0.elapsed_time(w1) / n_single, 5),
+                  "l2_warm_note": "same buffer set every step, launched eagerly, no exchange; "
+                                  f"one set is {per_set / 1e6:.0f} MB against 126 MB of L2"}
         # ---- per-operator timing (first layer set rotation), same stream, CUDA events ---
         op_ms = {}
         reps = max(20, min(args.steps, 200))
@@ -545,6 +571,7 @@ def gpu_arm(args, layers):
                          "peak_source": peak_src, "traffic": traffic,
                          "algorithmic_bytes_per_launch": op_bytes,
                          "torch_copy_of_first_layer_x_gbps": round(copy_gbps, 1)},
+            "timing_spread": spread,
             "ops_ms": {k: round(v, 5) for k, v in op_ms.items()},
             "ops_gbps": {k: round(op_bytes / (v * 1e-3) / 1e9, 1) for k, v in op_ms.items()},
             "e2e": None if e2e_val is None else {
