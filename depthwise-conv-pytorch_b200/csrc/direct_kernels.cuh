@@ -137,6 +137,7 @@ backward_filter_finalize_kernel(const typename Elem<T>::acc_t *__restrict__ part
   const int idx = blockIdx.x * FINALIZE_OUTPUTS + o;
   const bool live = idx < C * kk;
   A acc = 0;
+  pdl_launch_dependents();  // the next kernel in the stream may take its place early
   pdl_wait();  // the first pass has finished and its partial sums are visible
   if (live) {
     const int c = idx / kk;

@@ -155,6 +155,7 @@ backward_filter_finalize_exchange_kernel(const typename Elem<T>::acc_t *__restri
   const int idx = b * FINALIZE_OUTPUTS + o;
   const bool live = idx < n;
   A acc = 0;
+  pdl_launch_dependents();  // the next kernel in the stream may take its place early
   // The previous call's words do not depend on this call's first pass: warp 0 starts loading
   // them before waiting for it (reads of this rank's own exchange buffer only).
   const size_t header = exchange_header_bytes(gridDim.x);
