@@ -128,9 +128,15 @@ inline bool plan_finish(const PlanInput &in, int U, TilePlan &t) {
   t.eff = (double)in.Hout * t.G /
           ((double)t.NRT * in.NSEG * (rounds * task_rows_cost + 2.0));
   if (t.exact) t.eff *= 1.03;  // no per-row tests in the inner loop
-  if (in.slots > 0) {             // too few tiles leave SMs idle
+  if (in.slots > 0) {
     const double ntiles = (double)ceil_div(in.maxG, t.G) * t.NRT;
-    if (ntiles < in.slots) t.eff *= ntiles / in.slots;
+    if (ntiles < in.slots) {
+      t.eff *= ntiles / in.slots;  // too few tiles leave SMs idle
+    } else {
+      // tiles are dealt round-robin to the resident CTAs: the last round is only partly full
+      const double rounds_of_tiles = ntiles / in.slots;
+      t.eff *= rounds_of_tiles / (double)ceil_div((int)ntiles, in.slots);
+    }
   }
   t.U = U;
   t.ok = true;
