@@ -3,21 +3,31 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl b200|reference]
 
-One "step" is one pass of the three operators over one batch of seeded synthetic data of the
-named workload (per-GPU batch fixed: weak scaling; with N > 1 each step also sums the filter
-gradient over ranks with one all-reduce).  Rank 0 prints ONE JSON line:
+One "step" is one training step's worth of the path over one batch of seeded synthetic data
+of the named workload: every layer's forward, then every layer's two gradients (by default
+from the fused backward call, which reads dy once).  The per-GPU batch is fixed (weak
+scaling).  With N > 1 every step also sums the filter gradient over the ranks, and the step
+is SYNCHRONOUS: the world sum of step i's dW is in memory before step i ends (the sum is made
+by peer stores inside the kernel that finishes the gradient; an exchange_finish call per layer
+closes the step).  Rank 0 prints ONE JSON line:
 
 * ``value``      algorithmic GB/s, inputs resident in HBM, device-timed (CUDA events), max over
-                 ranks; algorithmic bytes per step = 3 * (|x| + |y| + |w|) summed over layers;
+                 ranks; algorithmic bytes per step = 3 * (|x| + |y| + |w|) summed over layers
+                 (the unfused definition, whether or not the backward is fused);
 * ``e2e``        the same metric through the public Python API with pinned HOST buffers:
                  host->device copies of x, w, dy and device->host copies of y, dx, dW inside
-                 the timed region;
-* ``roofline``   the slowest of the three operators, timed alone with CUDA events, against
-                 the measured HBM copy bandwidth (MEASURED_PEAKS.json);
-* ``cpu_baseline`` the reference's CPU route timed on this machine's host cores (rank 0);
+                 the timed region; ``copy_ceiling_ms`` beside it is the same bytes moved both
+                 ways at once with no kernel at all;
+* ``roofline``   the slowest kernel of the step, timed alone with CUDA events, its own
+                 algorithmic bytes against the measured HBM copy bandwidth (MEASURED_PEAKS.json);
+* ``cpu_baseline`` the reference's CPU route timed on this machine's host cores (rank 0, N = 1);
 * ``clocks``     SM clock / throttle reasons sampled with nvidia-smi while the GPU was loaded;
-* ``timing_spread`` median and best of 60 steps timed one by one, and the L2-warm step (one
-                 buffer set reused), beside the headline mean over the rotating sets.
+* ``stack``      the other half of the metric: the EfficientNet-B0 depthwise stack (c3), images/s;
+* ``strong``     strong scaling: c4a (global batch 64) and c5k3 (global batch 256) with the
+                 batch divided by N, step time and images/s for the whole job;
+* ``dw_check``   N > 1: the last step's exchanged dW against an NCCL all-reduce of the ranks'
+                 local gradients, and whether all ranks hold identical bits;
+* ``timing_spread`` median and best of 60 steps timed one by one, and the L2-warm step.
 
 ``--impl reference`` times only the reference's CPU route (see oracle/cpu_baseline.py) and
 prints the same line with ``"impl": "reference"``.
@@ -64,6 +74,8 @@ DESCR = {
     "c4a": "ConvNeXt-T-style 7x7 N64 C96 56x56 fp16 (fp32 accumulate)",
     "c4b": "ConvNeXt-T-style 7x7 N64 C192 28x28 fp16 (fp32 accumulate)",
 }
+# strong scaling (fixed global batch, divided over the ranks): workload -> global batch
+STRONG = {"c4a": 64, "c5k3": 256}
 ESIZE = {"f32": 4, "f16": 2, "f64": 8}
 METRIC = "dwconv_fwd_bwd_achieved_hbm_gbps"
 UNIT = "GB/s"
@@ -95,6 +107,12 @@ def load_peaks():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
+def config_of(args, layers):
+    """The keys both arms print under ``config``."""
+    return {"workload": f"{args.workload}: {DESCR.get(args.workload, args.workload)}",
+            "per_gpu_batch": layers[0][0]}
+
+
 # --------------------------------------------------------------------------------------
 # reference arm / CPU baseline: the reference's CPU route in a child process
 # --------------------------------------------------------------------------------------
@@ -102,7 +120,10 @@ def run_cpu_route(layers, images, steps, warmup, seconds):
     cmd = [sys.executable, os.path.join(ROOT, "oracle", "cpu_baseline.py"),
            "--layers", json.dumps(layers), "--images", str(images), "--steps", str(steps),
            "--warmup", str(warmup), "--seconds", str(seconds)]
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=1800)
+    # the child uses every host core: a launcher's per-rank thread limits do not apply to it
+    env = {k: v for k, v in os.environ.items()
+           if k not in ("OMP_NUM_THREADS", "MKL_NUM_THREADS", "OPENBLAS_NUM_THREADS")}
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=1800, env=env)
     if res.returncode != 0:
         raise RuntimeError("cpu_baseline.py failed: " + res.stderr[-400:])
     return json.loads(res.stdout.strip().splitlines()[-1])
@@ -135,8 +156,8 @@ def reference_arm(args, layers):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": entry["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": layers[0][6], "data": "synthetic (seeded N(0,1))",
-        "config": {"workload": f"{args.workload}: {DESCR.get(args.workload, args.workload)}",
-                   "images_per_step": images},
+        "config": config_of(args, layers),
+        "sample_images_per_step": images,
         "cpu_baseline": entry,
         "e2e": {"value": entry["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
@@ -201,12 +222,186 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------
+class Bench:
+    """Rotating buffer sets and the step of one workload at one per-GPU batch."""
+
+    def __init__(self, layers, dev, rank, world, exchange, min_sets=2, max_sets=8):
+        import torch
+        from dwconv_b200 import _lib
+        from dwconv_b200.dist import PeerFilterExchange
+        self.torch, self._lib, self.L = torch, _lib, _lib.lib
+        self.layers, self.dev, self.rank, self.world = layers, dev, rank, world
+        tdt = {"f32": torch.float32, "f16": torch.float16, "f64": torch.float64}
+        code = {"f32": _lib.F32, "f16": _lib.F16, "f64": _lib.F64}
+        # enough rotating sets that >= 2 x L2 is touched between reuses of a set
+        self.per_set = sum(2 * (bx + by) for bx, by, _ in map(layer_bytes, layers))  # x, dx, y, dy
+        self.n_sets = max(min_sets, min(max_sets, int(2 * L2_BYTES // self.per_set) + 2))
+        self.sets = []
+        for si in range(self.n_sets):
+            bufs = []
+            for li, (N, C, H, k, s, p, dt) in enumerate(layers):
+                g = torch.Generator(device=dev).manual_seed(1000 * rank + 10 * li + si)
+                ho = out_hw(H, k, s, p)
+                x = torch.randn((N, C, H, H), generator=g, device=dev).to(tdt[dt])
+                w = (torch.randn((C, 1, k, k), generator=g, device=dev) / k).to(tdt[dt])
+                dy = torch.randn((N, C, ho, ho), generator=g, device=dev).to(tdt[dt])
+                shape = _lib.Shape(N, C, H, H, k, k, s, s, p, p, ho, ho)
+                nws = self.L.dwconv_b200_backward_filter_workspace_bytes(code[dt], shape)
+                bufs.append(dict(x=x, w=w, dy=dy, y=torch.empty_like(dy), dx=torch.empty_like(x),
+                                 dw=torch.empty_like(w),
+                                 ws=torch.empty(nws, dtype=torch.uint8, device=dev),
+                                 nws=nws, shape=shape, code=code[dt]))
+            self.sets.append(bufs)
+        self.exchanges = None
+        if world > 1 and exchange:
+            self.exchanges = [PeerFilterExchange(C, k, tdt[dt], dev) for (N, C, H, k, s, p, dt) in layers]
+        self.graphs = {}
+
+    # ---- single operators -------------------------------------------------------------
+    def forward(self, b, st):
+        self._lib.check(self.L.dwconv_b200_forward(b["x"].data_ptr(), b["w"].data_ptr(),
+                                                   b["y"].data_ptr(), b["code"], b["shape"], st),
+                        "forward")
+
+    def backward_input(self, b, st):
+        self._lib.check(self.L.dwconv_b200_backward_input(b["dy"].data_ptr(), b["w"].data_ptr(),
+                                                          b["dx"].data_ptr(), b["code"], b["shape"], st),
+                        "backward_input")
+
+    def backward_filter(self, b, st, dw=None):
+        self._lib.check(self.L.dwconv_b200_backward_filter(
+            b["x"].data_ptr(), b["dy"].data_ptr(), (dw if dw is not None else b["dw"]).data_ptr(),
+            b["ws"].data_ptr(), b["nws"], b["code"], b["shape"], st), "backward_filter")
+
+    def backward(self, b, st):
+        self._lib.check(self.L.dwconv_b200_backward(
+            b["x"].data_ptr(), b["dy"].data_ptr(), b["w"].data_ptr(), b["dx"].data_ptr(),
+            b["dw"].data_ptr(), b["ws"].data_ptr(), b["nws"], b["code"], b["shape"], st), "backward")
+
+    # ---- steps ------------------------------------------------------------------------
+    def step_local(self, bufs, st, fused=True):
+        """Forward of every layer, then both gradients of every layer; no exchange."""
+        for b in bufs:
+            self.forward(b, st)
+        for b in reversed(bufs):
+            if fused:
+                self.backward(b, st)
+            else:
+                self.backward_input(b, st)
+                self.backward_filter(b, st)
+
+    def step_sync(self, bufs, st, fused=True):
+        """N > 1.  The filter gradient's second pass sends each rank's sums to all ranks; the
+        kernels that follow in the step hide the stores' flight; one finish call per layer at
+        the end of the step leaves the world sum of THIS step in ``dw``."""
+        ex = self.exchanges
+        for b in bufs:
+            self.forward(b, st)
+        for li in reversed(range(len(bufs))):
+            b = bufs[li]
+            if fused:
+                ex[li].launch_backward(b["x"].data_ptr(), b["dy"].data_ptr(), b["w"].data_ptr(),
+                                       b["dx"].data_ptr(), None, b["ws"].data_ptr(), b["nws"],
+                                       b["shape"], st)
+            else:
+                ex[li].launch(b["x"].data_ptr(), b["dy"].data_ptr(), None, b["ws"].data_ptr(),
+                              b["nws"], b["shape"], st)
+                self.backward_input(b, st)
+        for li in reversed(range(len(bufs))):
+            ex[li].finish(bufs[li]["dw"], stream=st)
+
+    def step_pipelined(self, bufs, prev, st):
+        """N > 1, for comparison: the sum of a step's dW is completed by the NEXT step's
+        exchange call (delayed by one step; no finish kernel)."""
+        for b in bufs:
+            self.forward(b, st)
+        for li in reversed(range(len(bufs))):
+            b = bufs[li]
+            self.backward_input(b, st)
+            self.exchanges[li].launch(b["x"].data_ptr(), b["dy"].data_ptr(), prev[li]["dw"].data_ptr(),
+                                      b["ws"].data_ptr(), b["nws"], b["shape"], st)
+
+    def run_step(self, i, mode, st):
+        bufs = self.sets[i % self.n_sets]
+        if mode == "local":
+            self.step_local(bufs, st, True)
+        elif mode == "local_unfused":
+            self.step_local(bufs, st, False)
+        elif mode == "sync":
+            self.step_sync(bufs, st, True)
+        elif mode == "sync_split":
+            self.step_sync(bufs, st, False)
+        elif mode == "pipelined":
+            self.step_pipelined(bufs, self.sets[(i - 1) % self.n_sets], st)
+        else:
+            raise ValueError(mode)
+
+    def launches_per_step(self, mode):
+        per_layer = {"local": 3, "local_unfused": 4, "sync": 4, "sync_split": 5, "pipelined": 4}[mode]
+        return per_layer * len(self.layers)
+
+    def make_graphs(self, mode, stream):
+        """One CUDA graph per buffer set for ``mode`` (after an eager pass: kernel set-up)."""
+        torch = self.torch
+        if mode in self.graphs:
+            return self.graphs[mode]
+        with torch.cuda.stream(stream):
+            for si in range(self.n_sets):
+                self.run_step(si, mode, stream.cuda_stream)
+        stream.synchronize()
+        graphs = []
+        for si in range(self.n_sets):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                self.run_step(si, mode, torch.cuda.current_stream().cuda_stream)
+            graphs.append(g)
+        self.graphs[mode] = graphs
+        return graphs
+
+    def time_steps(self, mode, steps, warmup, stream, use_graph, barrier):
+        """ms per step: CUDA events on ``stream`` around ``steps`` steps, max over ranks."""
+        torch = self.torch
+        graphs = self.make_graphs(mode, stream) if use_graph else None
+
+        def one(i):
+            if graphs is not None:
+                graphs[i % self.n_sets].replay()
+            else:
+                self.run_step(i, mode, stream.cuda_stream)
+
+        with torch.cuda.stream(stream):
+            for i in range(warmup):
+                one(i)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(steps):
+                one(i)
+            e1.record(stream)
+            barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if self.world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([ms], device=self.dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def close(self):
+        if self.exchanges is not None:
+            for ex in self.exchanges:
+                ex.close()
+            self.exchanges = None
+        self.graphs = {}
+        self.sets = []
+
+
 def gpu_arm(args, layers):
     import torch
     import torch.distributed as dist
     import dwconv_b200
     from dwconv_b200 import _lib
-    from dwconv_b200.dist import FilterGradReducer, PeerFilterExchange, bind_to_gpu_numa_node
+    from dwconv_b200.dist import bind_to_gpu_numa_node
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -221,195 +416,106 @@ def gpu_arm(args, layers):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         from datetime import timedelta
-        dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=90))
+        dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=120))
     L = _lib.lib
     tdt = {"f32": torch.float32, "f16": torch.float16, "f64": torch.float64}
-    code = {"f32": _lib.F32, "f16": _lib.F16, "f64": _lib.F64}
-
-    # ---- buffers: enough rotating sets that >= 2 x L2 is touched between reuses ----------
-    per_set = sum(2 * (bx + by) for bx, by, _ in map(layer_bytes, layers))  # x, dx, y, dy
-    n_sets = max(2, min(8, int(2 * L2_BYTES // per_set) + 2))
-    sets = []
-    for si in range(n_sets):
-        bufs = []
-        for li, (N, C, H, k, s, p, dt) in enumerate(layers):
-            g = torch.Generator(device=dev).manual_seed(1000 * rank + 10 * li + si)
-            ho = out_hw(H, k, s, p)
-            x = torch.randn((N, C, H, H), generator=g, device=dev).to(tdt[dt])
-            w = (torch.randn((C, 1, k, k), generator=g, device=dev) / k).to(tdt[dt])
-            dy = torch.randn((N, C, ho, ho), generator=g, device=dev).to(tdt[dt])
-            shape = _lib.Shape(N, C, H, H, k, k, s, s, p, p, ho, ho)
-            nws = L.dwconv_b200_backward_filter_workspace_bytes(code[dt], shape)
-            bufs.append(dict(x=x, w=w, dy=dy, y=torch.empty_like(dy), dx=torch.empty_like(x),
-                             dw=torch.empty_like(w), ws=torch.empty(nws, dtype=torch.uint8, device=dev),
-                             nws=nws, shape=shape, code=code[dt]))
-        sets.append(bufs)
-
-    def op_forward(b, st):
-        _lib.check(L.dwconv_b200_forward(b["x"].data_ptr(), b["w"].data_ptr(), b["y"].data_ptr(),
-                                         b["code"], b["shape"], st), "forward")
-
-    def op_backward_input(b, st):
-        _lib.check(L.dwconv_b200_backward_input(b["dy"].data_ptr(), b["w"].data_ptr(),
-                                                b["dx"].data_ptr(), b["code"], b["shape"], st),
-                   "backward_input")
-
-    def op_backward_filter(b, st):
-        _lib.check(L.dwconv_b200_backward_filter(b["x"].data_ptr(), b["dy"].data_ptr(),
-                                                 b["dw"].data_ptr(), b["ws"].data_ptr(), b["nws"],
-                                                 b["code"], b["shape"], st), "backward_filter")
-
-    # N > 1: the filter gradient is summed over the GPUs inside its second pass (peer stores over
-    # NVLink, one exchange object per layer); if peer mapping is not possible on this machine the
-    # step falls back to one NCCL all-reduce of the packed gradients on a side stream
-    exchanges = None
-    if world > 1 and not args.nccl_reduce:
-        try:
-            exchanges = [PeerFilterExchange(C, k, tdt[dt], dev) for (N, C, H, k, s, p, dt) in layers]
-        except RuntimeError as e:
-            if rank == 0:
-                sys.stderr.write(f"[bench] peer exchange unavailable ({e}); using NCCL all-reduce\n")
-            exchanges = None
-        ok = torch.tensor([1 if exchanges is not None else 0], device=dev)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if int(ok.item()) == 0:
-            exchanges = None
-
-    def op_backward_filter_exchange(li, b, st, prev=None):
-        # sends this step's gradient to all ranks; the previous step's world sum lands in the
-        # previous buffer set's dw (the exchange is pipelined by one step)
-        exchanges[li].launch(b["x"].data_ptr(), b["dy"].data_ptr(),
-                             prev["dw"].data_ptr() if prev is not None else None,
-                             b["ws"].data_ptr(), b["nws"], b["shape"], st)
-
-    OPS = (("forward", op_forward, 1), ("backward_input", op_backward_input, 1),
-           ("backward_filter", op_backward_filter, 2))  # launches per call
-
-    def compute_step(bufs, st, local=False, prev=None):
-        for b in bufs:
-            op_forward(b, st)
-        for li in reversed(range(len(bufs))):
-            b = bufs[li]
-            op_backward_input(b, st)
-            if exchanges is not None and not local:
-                op_backward_filter_exchange(li, b, st, prev[li] if prev is not None else None)
-            else:
-                op_backward_filter(b, st)
-
-    # dW all-reduce: packed into one flat fp32 buffer, on a side stream, overlapped with the
-    # next step's kernels; the result is awaited before the next all-reduce starts
-    reducer = None
-    pending = [None]
-    if world > 1 and exchanges is None:
-        reducer = FilterGradReducer([b["dw"].shape for b in sets[0]], dev, side_stream=True)
-
-    # ---- one CUDA graph per buffer set (compute only; the collective stays eager) -------
-    stream = torch.cuda.Stream(device=dev)
-    graphs = None
-    torch.cuda.synchronize()
-    with torch.cuda.stream(stream):
-        for si, bufs in enumerate(sets):  # also every kernel's first-call set-up, outside capture
-            compute_step(bufs, stream.cuda_stream, prev=sets[si - 1])
-    stream.synchronize()
-    if not args.no_graph and args.launch != "eager":
-        graphs = []
-        for si, bufs in enumerate(sets):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                compute_step(bufs, torch.cuda.current_stream().cuda_stream, prev=sets[si - 1])
-            graphs.append(g)
-
-    use_graph = [graphs is not None]
-
-    def compute_only(i):
-        if use_graph[0]:
-            graphs[i % n_sets].replay()
-        else:
-            compute_step(sets[i % n_sets], torch.cuda.current_stream().cuda_stream,
-                         prev=sets[(i - 1) % n_sets])
-
-    def step(i):
-        bufs = sets[i % n_sets]
-        last_step[0] = i
-        compute_only(i)
-        if reducer is not None:
-            if pending[0] is not None:
-                reducer.finish(pending[0])
-            pending[0] = [b["dw"] for b in bufs]
-            reducer.start(pending[0])
-
-    last_step = [0]
-
-    def drain():
-        if reducer is not None and pending[0] is not None:
-            reducer.finish(pending[0])
-            pending[0] = None
-        if exchanges is not None:  # complete the last step's sum
-            for ex, b in zip(exchanges, sets[last_step[0] % n_sets]):
-                ex.finish(b["dw"], stream=torch.cuda.current_stream().cuda_stream)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    wb = Bench(layers, dev, rank, world, exchange=True)
+    n_sets, per_set = wb.n_sets, wb.per_set
+    stream = torch.cuda.Stream(device=dev)
+    head_mode = "local" if world == 1 else "sync"
+    if args.unfused:
+        head_mode = "local_unfused" if world == 1 else "sync_split"
+
     sampler = ClockSampler(local) if rank == 0 else None
-    calibration = None
+    # ---- launch calibration: graph replay or eager launches; at N > 1 also which order of
+    # the backward kernels hides the exchange better (same choice on all ranks) -------------
+    calibration = {}
+    candidates = [head_mode]
+    if world > 1 and not args.unfused:
+        candidates.append("sync_split")
+    best = None
+    for mode in candidates:
+        for use_graph in ((True, False) if args.launch == "auto" else
+                          ((True,) if args.launch == "graph" else (False,))):
+            ms = wb.time_steps(mode, 120, 10, stream, use_graph, barrier)
+            calibration[f"{mode}_{'graph' if use_graph else 'eager'}_ms"] = round(ms, 5)
+            if best is None or ms < best[0]:
+                best = (ms, mode, use_graph)
+    _, head_mode, use_graph = best
+
+    # ---- the headline: exactly --steps steps after >= 3 warm-up steps ---------------------
+    t_load0 = time.perf_counter()
+    ms_step = wb.time_steps(head_mode, args.steps, max(args.warmup, 3), stream, use_graph, barrier)
+    sb = step_bytes(layers)
+    value = sb * world / (ms_step * 1e-3) / 1e9
+
+    # ---- N > 1: is the summed gradient right?  (outside the timed region) -----------------
+    dw_check = None
+    variants = None
+    if world > 1:
+        with torch.cuda.stream(stream):
+            wb.run_step(0, head_mode, stream.cuda_stream)
+            stream.synchronize()
+            worst, same = 0.0, True
+            for b in wb.sets[0]:
+                got = b["dw"].clone()
+                mine = torch.empty_like(b["dw"])
+                wb.backward_filter(b, stream.cuda_stream, dw=mine)
+                stream.synchronize()
+                want = mine.double()
+                dist.all_reduce(want, op=dist.ReduceOp.SUM)
+                scale = float(want.abs().max().item())
+                worst = max(worst, float((got.double() - want).abs().max().item()) / max(scale, 1e-30))
+                everyone = [torch.empty_like(got) for _ in range(world)]
+                dist.all_gather(everyone, got)
+                same = same and all(torch.equal(everyone[0], t) for t in everyone[1:])
+            status = int(L.dwconv_b200_device_status())
+        tol = 1e-2 if layers[0][6] == "f16" else 1e-4
+        dw_check = {"ok": bool(worst <= tol and same and status == 0), "max_rel_err": worst,
+                    "ranks_identical": bool(same), "device_status": status, "tolerance": tol,
+                    "against": "NCCL all_reduce(SUM) of every rank's local dwconv_b200_backward_filter"}
+        # the other ways to run the step, for the record
+        variants = {}
+        for mode in ("local", "sync", "sync_split", "pipelined"):
+            variants[mode + "_ms"] = round(wb.time_steps(mode, 200, 10, stream, False, barrier), 5)
+        variants["note"] = ("eager launches, 200 steps, max over ranks.  local: no exchange at all; "
+                            "sync: fused backward + in-kernel exchange + finish per step (dW of the "
+                            "step complete at its end); sync_split: filter gradient + exchange first, "
+                            "backward-input hides the stores' flight, then finish; pipelined: dW "
+                            "completed by the next step's exchange (one step late)")
+
     with torch.cuda.stream(stream):
-        if graphs is not None and args.launch == "auto":
-            # Replaying a graph saves host time per launch; launching eagerly lets each kernel
-            # become resident while the previous step's last kernel drains (programmatic dependent
-            # launch does not reach across graph boundaries).  Which wins depends on the step's
-            # length, so time a few steps each way and keep the faster (same choice on all ranks).
-            calibration = {}
-            for mode in (True, False):
-                use_graph[0] = mode
-                for i in range(10):
-                    step(i)
-                drain()
-                barrier()
-                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                c0.record(stream)
-                for i in range(120):
-                    step(i)
-                drain()
-                c1.record(stream)
-                barrier()
-                t = torch.tensor([c0.elapsed_time(c1) / 120], device=dev, dtype=torch.float64)
-                if world > 1:
-                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                calibration["graph_ms" if mode else "eager_ms"] = round(float(t.item()), 5)
-            use_graph[0] = calibration["graph_ms"] <= calibration["eager_ms"]
-        for i in range(max(args.warmup, 3)):
-            step(i)
-        drain()
-        barrier()
-        t_load0 = time.perf_counter()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for i in range(args.steps):
-            step(i)
-        drain()
-        e1.record(stream)
-        barrier()
-        ms_total = e0.elapsed_time(e1)
-        # ---- spread of single steps (each bracketed by its own events, which costs a little
-        # overlap), and the same step with L2 warm (one buffer set over and over) ------------
+        # ---- spread of single steps, and the same step with L2 warm -----------------------
         n_single = 60
+        graphs = wb.make_graphs(head_mode, stream) if use_graph else None
+
+        def one(i):
+            if graphs is not None:
+                graphs[i % n_sets].replay()
+            else:
+                wb.run_step(i, head_mode, stream.cuda_stream)
+
+        barrier()
         marks = [torch.cuda.Event(enable_timing=True) for _ in range(n_single + 1)]
         for i in range(n_single):
             marks[i].record(stream)
-            step(i)
-        drain()
+            one(i)
         marks[n_single].record(stream)
         stream.synchronize()
+        barrier()
         singles = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(n_single))
         w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         for _ in range(5):
-            compute_step(sets[0], stream.cuda_stream, local=True)
+            wb.step_local(wb.sets[0], stream.cuda_stream)
         w0.record(stream)
         for _ in range(n_single):
-            compute_step(sets[0], stream.cuda_stream, local=True)
+            wb.step_local(wb.sets[0], stream.cuda_stream)
         w1.record(stream)
         stream.synchronize()
         spread = {"single_step_median_ms": round(statistics.median(singles), 5),
@@ -417,51 +523,33 @@ def gpu_arm(args, layers):
                   "l2_warm_ms_per_step": round(w0.elapsed_time(w1) / n_single, 5),
                   "l2_warm_note": "same buffer set every step, launched eagerly, no exchange; "
                                   f"one set is {per_set / 1e6:.0f} MB against 126 MB of L2"}
-        # ---- per-operator timing (first layer set rotation), same stream, CUDA events ---
+        # ---- every operator alone, same rotation, same stream, CUDA events ----------------
+        OPS = (("forward", wb.forward), ("backward_input", wb.backward_input),
+               ("backward_filter", wb.backward_filter), ("backward_fused", wb.backward))
         op_ms = {}
         reps = max(20, min(args.steps, 200))
-        for name, fn, _ in OPS:
+        for name, fn in OPS:
             for i in range(3):
-                for b in sets[i % n_sets]:
+                for b in wb.sets[i % n_sets]:
                     fn(b, stream.cuda_stream)
             a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
             for i in range(reps):
-                for b in sets[i % n_sets]:
+                for b in wb.sets[i % n_sets]:
                     fn(b, stream.cuda_stream)
             z.record(stream)
             stream.synchronize()
             op_ms[name] = a.elapsed_time(z) / reps
-        # N > 1: every rank's step without the exchange, and the filter gradient with it, so that
-        # the cost of the exchange can be read off (all ranks run this loop together)
-        multi = None
-        if world > 1 and exchanges is not None:
-            multi = {}
-            for name, fn in (("local_step_ms", lambda i: compute_step(sets[i % n_sets], stream.cuda_stream, local=True)),
-                             ("filter_exchange_ms", lambda i: [op_backward_filter_exchange(li, b, stream.cuda_stream)
-                                                               for li, b in enumerate(sets[i % n_sets])])):
-                for i in range(3):
-                    fn(i)
-                a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(stream)
-                for i in range(reps):
-                    fn(i)
-                z.record(stream)
-                stream.synchronize()
-                t = torch.tensor([a.elapsed_time(z) / reps], device=dev, dtype=torch.float64)
-                gathered = [torch.zeros_like(t) for _ in range(world)]
-                dist.all_gather(gathered, t)
-                multi[name] = [round(float(v.item()), 5) for v in gathered]
         # context for the roofline: what a plain device copy of one operator's traffic (read |x|,
         # write |y| of the first layer) achieves at THIS size, same stream and timing
-        b0 = sets[0][0]
+        b0 = wb.sets[0][0]
         cp_a, cp_z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        scratch = [torch.empty_like(sets[i % n_sets][0]["x"]) for i in range(n_sets)]
+        scratch = [torch.empty_like(wb.sets[i % n_sets][0]["x"]) for i in range(n_sets)]
         for i in range(3):
-            scratch[i % n_sets].copy_(sets[i % n_sets][0]["x"])
+            scratch[i % n_sets].copy_(wb.sets[i % n_sets][0]["x"])
         cp_a.record(stream)
         for i in range(reps):
-            scratch[i % n_sets].copy_(sets[i % n_sets][0]["x"])
+            scratch[i % n_sets].copy_(wb.sets[i % n_sets][0]["x"])
         cp_z.record(stream)
         stream.synchronize()
         copy_ms = cp_a.elapsed_time(cp_z) / reps
@@ -473,21 +561,46 @@ def gpu_arm(args, layers):
             i = 0
             while time.perf_counter() < t_need:
                 # rank 0 only: nothing in here may wait for another rank
-                compute_step(sets[i % n_sets], stream.cuda_stream, local=True)
+                wb.step_local(wb.sets[i % n_sets], stream.cuda_stream)
                 i += 1
                 if i % 64 == 0:
                     stream.synchronize()
             stream.synchronize()
         t_load1 = time.perf_counter()
     clocks = sampler.stop(t_load0, t_load1) if sampler is not None else None
+    barrier()
+    head_launches = wb.launches_per_step(head_mode)
+    wb.close()
+    del wb
+    torch.cuda.empty_cache()
 
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
-    sb = step_bytes(layers)
-    value = sb * world / (ms_step * 1e-3) / 1e9
+    # ---- the other half of the metric: the EfficientNet-B0 depthwise stack ------------------
+    stack_entry, strong = None, None
+    if not args.no_extras:
+        def timed_workload(name, batch, steps):
+            lay = [[batch] + list(l[1:]) for l in WORKLOADS[name]]
+            w2 = Bench(lay, dev, rank, world, exchange=True, min_sets=2, max_sets=4)
+            mode = "local" if world == 1 else "sync"
+            ms = w2.time_steps(mode, steps, 5, stream, True, barrier)
+            out = {"per_gpu_batch": batch, "ms_per_step": round(ms, 5),
+                   "images_per_s": round(batch * world / (ms * 1e-3), 1),
+                   "algorithmic_gbps": round(step_bytes(lay) * world / (ms * 1e-3) / 1e9, 1),
+                   "buffer_sets": w2.n_sets, "set_mb": round(w2.per_set / 1e6, 1)}
+            barrier()
+            w2.close()
+            del w2
+            torch.cuda.empty_cache()
+            return out
+
+        stack_entry = dict(workload="c3: " + DESCR["c3"], **timed_workload("c3", 128, 40))
+        stack_entry["scaling"] = "weak (128 images per GPU)"
+        strong = {}
+        for name, gb in STRONG.items():
+            if gb % world == 0 and gb // world >= 1:
+                strong[name] = dict(global_batch=gb, **timed_workload(name, gb // world, 200))
+        strong["note"] = ("fixed global batch divided over the ranks; dW summed over the ranks "
+                          "inside the step (synchronous); one CUDA graph per step; small shards "
+                          "fit the 126 MB L2 (see set_mb x buffer_sets)")
 
     # ---- e2e: public Python API, pinned host buffers, copies inside the timed region ----
     host = []
@@ -512,6 +625,13 @@ def gpu_arm(args, layers):
         for pipe, (hx, hw_, hdy, outs, s, p) in zip(pipes, host):
             pipe.run(hx, hw_, hdy, outs[0], outs[1], outs[2])
 
+    def max_over_ranks(v):
+        if world > 1 and v is not None:
+            t = torch.tensor([v], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return v
+
     e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 20))
     for _ in range(3 if e2e_steps else 0):
         e2e_step()
@@ -520,19 +640,43 @@ def gpu_arm(args, layers):
     for _ in range(e2e_steps):
         e2e_step()
     torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps if e2e_steps else None
-    if world > 1 and e2e_s is not None:
-        t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_s = max_over_ranks((time.perf_counter() - t0) / e2e_steps if e2e_steps else None)
     e2e_val = sb * world / e2e_s / 1e9 if e2e_s else None
+    # the bare ceiling of that leg: the same bytes up and down at once, no kernel at all
+    ceiling_s = None
+    if e2e_steps:
+        s_up, s_down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        dbuf = [(torch.empty_like(hx, device=dev), torch.empty_like(hdy, device=dev))
+                for hx, hw_, hdy, outs, s, p in host]
+
+        def copies():
+            for (hx, hw_, hdy, outs, s, p), (dx_, dy_) in zip(host, dbuf):
+                for dst, src, st in ((dx_, hx, s_up), (dy_, hdy, s_up), (outs[1], dx_, s_down),
+                                     (outs[0], dy_, s_down)):
+                    _lib.check(L.dwconv_b200_copy_async(dst.data_ptr(), src.data_ptr(),
+                                                        src.numel() * src.element_size(),
+                                                        st.cuda_stream), "copy_async")
+        for _ in range(2):
+            copies()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            copies()
+        torch.cuda.synchronize()
+        ceiling_s = max_over_ranks((time.perf_counter() - t0) / e2e_steps)
+        del dbuf
 
     if rank == 0:
         peak, peak_src = load_peaks()
-        # dominant operator = the slowest of the three; each moves |x|+|y|+|w| bytes per layer
-        dom = max(op_ms, key=op_ms.get)
-        op_bytes = sb / 3
-        achieved = op_bytes / (op_ms[dom] * 1e-3) / 1e9
+        # the dominant kernel of the headline step and its own algorithmic bytes per launch:
+        # forward |x|+|y|+|w|; fused backward |x|+|dy|+|dx|+|w|+|dw| (dy is read once)
+        bx, by, bw = (sum(v) for v in zip(*map(layer_bytes, layers)))
+        kernel_bytes = {"forward": bx + by + bw, "backward_input": bx + by + bw,
+                        "backward_filter": bx + by + bw, "backward_fused": 2 * bx + by + 2 * bw}
+        in_step = (("forward", "backward_fused") if head_mode in ("local", "sync") else
+                   ("forward", "backward_input", "backward_filter"))
+        dom = max(in_step, key=lambda k: op_ms[k])
+        achieved = kernel_bytes[dom] / (op_ms[dom] * 1e-3) / 1e9
         traffic = None
         tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
         if os.path.exists(tpath):
@@ -546,51 +690,64 @@ def gpu_arm(args, layers):
             except Exception as e:  # noqa: BLE001
                 cpu_entry = {"value": None, "unit": UNIT, "cores": None, "kind": "port",
                              "sample": f"failed: {e}"}
-        launches = sum(n for _, _, n in OPS) * len(layers) * args.steps
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 5),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": layers[0][6], "data": "synthetic (seeded N(0,1); w ~ N(0,1/k^2))",
-            "config": {
-                "workload": f"{args.workload}: {DESCR.get(args.workload, args.workload)}",
-                "per_gpu_batch": layers[0][0],
+            "config": config_of(args, layers),
+            "details": {
                 "l2": f"rotating {n_sets} buffer sets ({n_sets * per_set / 1e6:.0f} MB touched "
                       f"between reuses; L2 is 126 MB)",
-                "cuda_graph": use_graph[0],
+                "step": {"local": "forward, fused backward (dx + dW from one read of dy)",
+                         "local_unfused": "forward, backward-input, backward-filter",
+                         "sync": "forward, fused backward whose second pass sends dW to all ranks, "
+                                 "exchange_finish (dW of this step complete at its end)",
+                         "sync_split": "forward, backward-filter whose second pass sends dW to all "
+                                       "ranks, backward-input, exchange_finish (dW of this step "
+                                       "complete at its end)"}[head_mode],
+                "cuda_graph": use_graph,
                 "launch_calibration": calibration,
                 "algorithmic_bytes_per_step": sb,
                 "parallelism": "single GPU" if world == 1 else (
                     f"dp{world} (batch-sharded; dW summed over the GPUs inside the filter-gradient "
-                    "kernel by peer stores over NVLink)" if exchanges is not None else
-                    f"dp{world} (batch-sharded; one NCCL all-reduce of dW per step, overlapped)"),
+                    "kernel by peer stores over NVLink, synchronous)"),
             },
             "frac_of_8TBs": round(value / world / 8000.0, 4),
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 2),
                          "peak": peak, "unit": UNIT, "frac": round(achieved / peak, 4),
                          "peak_source": peak_src, "traffic": traffic,
-                         "algorithmic_bytes_per_launch": op_bytes,
+                         "algorithmic_bytes_per_launch": kernel_bytes[dom],
                          "torch_copy_of_first_layer_x_gbps": round(copy_gbps, 1)},
             "timing_spread": spread,
             "ops_ms": {k: round(v, 5) for k, v in op_ms.items()},
-            "ops_gbps": {k: round(op_bytes / (v * 1e-3) / 1e9, 1) for k, v in op_ms.items()},
+            "ops_gbps": {k: round(kernel_bytes[k] / (v * 1e-3) / 1e9, 1) for k, v in op_ms.items()},
             "e2e": None if e2e_val is None else {
                 "value": round(e2e_val, 3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 4),
+                "copy_ceiling_ms": round(ceiling_s * 1e3, 4),
                 "api": "dwconv_b200.HostMapsStep.run: pinned host x, w, dy -> pinned host y, dx, dw; "
                        f"batch cut into chunks of {pipes[0].chunk} images, upload / kernels / "
                        "download on three streams",
                 "gpu_launches_per_step": sum(p.launches_per_run for p in pipes)},
-            "per_rank": multi,
+            "stack": stack_entry,
+            "strong": strong,
+            "dw_check": dw_check,
+            "step_variants_ms": variants,
             "numa_binding": numa,
-            "gpu_launches": launches,
+            "gpu_launches": head_launches * args.steps,
             "clocks": clocks,
             "cpu_baseline": cpu_entry,
             "kernel_family": {1: "direct", 2: "rows"}.get(L.dwconv_b200_last_path(), "auto"),
         }
         print(json.dumps(line))
+    ok = dw_check is None or dw_check["ok"]
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        raise SystemExit("bench.py: the exchanged filter gradient failed its check: "
+                         + json.dumps(dw_check))
 
 
 def main():
@@ -600,14 +757,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly")
     ap.add_argument("--launch", default="auto", choices=["auto", "graph", "eager"],
                     help="replay one CUDA graph per step, launch eagerly, or time both and keep "
                          "the faster (default)")
-    ap.add_argument("--nccl-reduce", action="store_true",
-                    help="N > 1: sum dW with an NCCL all-reduce instead of the in-kernel exchange")
+    ap.add_argument("--unfused", action="store_true",
+                    help="backward-input and backward-filter as separate operators")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the stack and strong-scaling legs (profiling)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     args = ap.parse_args()
     layers = [list(l) for l in WORKLOADS[args.workload]]

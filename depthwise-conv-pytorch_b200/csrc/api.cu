@@ -93,6 +93,17 @@ int try_rows_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *p
   return ROWS_DECLINED;
 }
 
+template <typename T> int try_rows_backward_slices(const Shape &s) {
+  if constexpr (kRowsCompiled<T>) return rows_backward_slices<T>(s);
+  return 0;
+}
+template <typename T>
+int try_rows_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<T>::acc_t *partial,
+                      const Shape &s, cudaStream_t st, int *slices_out) {
+  if constexpr (kRowsCompiled<T>) return rows_backward<T>(x, dy, w, dx, partial, s, st, slices_out);
+  return ROWS_DECLINED;
+}
+
 template <typename T>
 int forward_t(const void *x, const void *w, void *y, const Shape &s, cudaStream_t st, int forced) {
   if (forced != DWCONV_B200_PATH_DIRECT) {
@@ -135,6 +146,8 @@ size_t filter_workspace_t(const Shape &s) {
   size_t slices = (size_t)direct_filter_slices(s);
   const size_t rs = (size_t)try_rows_backward_filter_slices<T>(s);
   if (rs > slices) slices = rs;
+  const size_t fs = (size_t)try_rows_backward_slices<T>(s);  // the fused backward shares the workspace
+  if (fs > slices) slices = fs;
   size_t b = (size_t)s.C * slices * kk * sizeof(A);
   return b < 16 ? 16 : ((b + 15) / 16) * 16;
 }
@@ -196,6 +209,49 @@ int backward_filter_t(const void *x, const void *dy, void *dw, void *ws, size_t 
   return launch_status();
 }
 
+// First pass of the fused backward: dx, and the partial sums of dW into ws.  One kernel when
+// the rows family serves the shape (dy is read once); otherwise backward-input followed by the
+// filter gradient's own first pass.
+template <typename T>
+int backward_first_pass_t(const void *x, const void *dy, const void *w, void *dx, void *ws,
+                          size_t ws_bytes, const Shape &s, cudaStream_t st, int forced, int *slices) {
+  using A = typename Elem<T>::acc_t;
+  if (ws_bytes < filter_workspace_t<T>(s)) return DWCONV_B200_WORKSPACE_TOO_SMALL;
+  if (forced != DWCONV_B200_PATH_DIRECT) {
+    int S = 0;
+    int r = try_rows_backward<T>((const T *)x, (const T *)dy, (const T *)w, (T *)dx, (A *)ws, s, st, &S);
+    if (r == ROWS_SERVED) {
+      t_last_path = DWCONV_B200_PATH_ROWS;
+      *slices = S;
+      return launch_status();
+    }
+  }
+  int e = backward_input_t<T>(dy, w, dx, s, st, forced);
+  if (e != DWCONV_B200_OK) return e;
+  return filter_first_pass_t<T>(x, dy, ws, ws_bytes, s, st, forced, slices);
+}
+
+// dw_is_acc: dw is an accumulator-typed buffer (fp32, fp64 for fp64 data); accumulate: add to it.
+template <typename T>
+int backward_t(const void *x, const void *dy, const void *w, void *dx, void *dw, void *ws,
+               size_t ws_bytes, const Shape &s, cudaStream_t st, int forced, bool dw_is_acc,
+               int accumulate) {
+  using A = typename Elem<T>::acc_t;
+  int S = 0;
+  int e = dx != nullptr ? backward_first_pass_t<T>(x, dy, w, dx, ws, ws_bytes, s, st, forced, &S)
+                        : filter_first_pass_t<T>(x, dy, ws, ws_bytes, s, st, forced, &S);
+  if (e != DWCONV_B200_OK) return e;
+  const int kk = s.kh * s.kw;
+  cudaLaunchAttribute attr[1];
+  cudaLaunchConfig_t cfg = finalize_config(finalize_blocks(s.C, kk), st, attr);
+  if (dw_is_acc)
+    (void)cudaLaunchKernelEx(&cfg, backward_filter_finalize_acc_kernel<A>, (const A *)ws, (A *)dw, s.C,
+                             kk, S, accumulate);
+  else
+    (void)cudaLaunchKernelEx(&cfg, backward_filter_finalize_kernel<T>, (const A *)ws, (T *)dw, s.C, kk, S);
+  return launch_status();
+}
+
 // ---- filter gradient summed over the GPUs of one node (peer_exchange.cuh) ----
 __device__ int g_exchange_error_flag = 0;
 
@@ -224,15 +280,19 @@ inline ExchangePeers exchange_peers(const dwconv_b200_exchange *ex) {
 template <typename T>
 int exchange_finish_t(void *dw, dwconv_b200_exchange *ex, cudaStream_t st) {
   const int kk = ex->kh * ex->kw;
-  exchange_finish_kernel<T><<<finalize_blocks(ex->C, kk), FINALIZE_OUTPUTS, 0, st>>>(
-      (T *)dw, ex->C * kk, exchange_peers(ex), ex->error_flag);
+  cudaLaunchAttribute attr[1];
+  cudaLaunchConfig_t cfg = finalize_config(finalize_blocks(ex->C, kk), st, attr);
+  cfg.blockDim = dim3(FINALIZE_OUTPUTS);
+  (void)cudaLaunchKernelEx(&cfg, exchange_finish_kernel<T>, (T *)dw, ex->C * kk, exchange_peers(ex),
+                           ex->error_flag);
   return launch_status();
 }
 
+// w and dx null: filter gradient only; otherwise the fused backward's first pass.
 template <typename T>
-int backward_filter_exchange_t(const void *x, const void *dy, void *dw, void *ws, size_t ws_bytes,
-                               const Shape &s, dwconv_b200_exchange *ex, cudaStream_t st,
-                               int forced) {
+int backward_filter_exchange_t(const void *x, const void *dy, const void *w, void *dx, void *dw,
+                               void *ws, size_t ws_bytes, const Shape &s, dwconv_b200_exchange *ex,
+                               cudaStream_t st, int forced) {
   using A = typename Elem<T>::acc_t;
   const int kk = s.kh * s.kw;
   const int blocks = finalize_blocks(s.C, kk);
@@ -240,7 +300,8 @@ int backward_filter_exchange_t(const void *x, const void *dy, void *dw, void *ws
       ex->bytes < exchange_bytes<A>(ex->world, s.C * kk, blocks))
     return DWCONV_B200_BAD_ARGUMENT;
   int S = 0;
-  int e = filter_first_pass_t<T>(x, dy, ws, ws_bytes, s, st, forced, &S);
+  int e = dx != nullptr ? backward_first_pass_t<T>(x, dy, w, dx, ws, ws_bytes, s, st, forced, &S)
+                        : filter_first_pass_t<T>(x, dy, ws, ws_bytes, s, st, forced, &S);
   if (e != DWCONV_B200_OK) return e;
   const ExchangePeers px = exchange_peers(ex);
   cudaLaunchAttribute attr[1];
@@ -267,7 +328,7 @@ int dwconv_b200_version(void) { return DWCONV_B200_VERSION; }
 const char *dwconv_b200_status_string(int status) {
   switch (status) {
     case DWCONV_B200_OK: return "ok";
-    case DWCONV_B200_BAD_ARGUMENT: return "bad argument (null pointer, non-positive or inconsistent extent)";
+    case DWCONV_B200_BAD_ARGUMENT: return "bad argument (null pointer, non-positive extent, or an exchange object made for another layer)";
     case DWCONV_B200_UNSUPPORTED_DTYPE: return "unsupported dtype (expected f32, f16 or f64)";
     case DWCONV_B200_MISALIGNED: return "pointer not aligned to its element size (workspace: 16 bytes)";
     case DWCONV_B200_WORKSPACE_TOO_SMALL: return "workspace smaller than dwconv_b200_backward_filter_workspace_bytes";
@@ -293,6 +354,7 @@ int dwconv_b200_debug_plan(int op, int dtype, const dwconv_b200_shape *shape, in
   const int es = (int)elem_size(dtype);
   if (es != 4 && es != 2) return 0;
   if (op == 2) return rows_debug_filter_plan(es, *shape, aligned16, out24);
+  if (op == 3) return rows_debug_backward_plan(es, *shape, aligned16, out24);
   return rows_debug_conv_plan(op, es, *shape, aligned16, out24);
 }
 
@@ -402,13 +464,16 @@ int dwconv_b200_exchange_finish(void *dw, dwconv_b200_exchange *ex, void *stream
   }
 }
 
-int dwconv_b200_backward_filter_exchange(const void *x, const void *dy, void *dw_prev, void *workspace,
-                                         size_t workspace_bytes, int dtype,
-                                         const dwconv_b200_shape *shape, dwconv_b200_exchange *ex,
-                                         void *stream) {
+static int exchange_call(const void *x, const void *dy, const void *w, void *dx, void *dw_prev,
+                         void *workspace, size_t workspace_bytes, int dtype,
+                         const dwconv_b200_shape *shape, dwconv_b200_exchange *ex, void *stream) {
   const void *dw = dw_prev != nullptr ? dw_prev : x;  // dw_prev is optional
   int e = check_ptrs(dtype, x, dy, dw);
   if (e) return e;
+  if (dx != nullptr) {
+    e = check_ptrs(dtype, w, dx, dx);
+    if (e) return e;
+  }
   e = check_shape(shape);
   if (e) return e;
   if (ex == nullptr || !ex->connected || workspace == nullptr) return DWCONV_B200_BAD_ARGUMENT;
@@ -417,14 +482,30 @@ int dwconv_b200_backward_filter_exchange(const void *x, const void *dy, void *dw
   const int forced = g_forced_path.load();
   switch (dtype) {
     case DWCONV_B200_F32:
-      return backward_filter_exchange_t<float>(x, dy, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+      return backward_filter_exchange_t<float>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
     case DWCONV_B200_F16:
-      return backward_filter_exchange_t<__half>(x, dy, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+      return backward_filter_exchange_t<__half>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
     case DWCONV_B200_BF16:
-      return backward_filter_exchange_t<__nv_bfloat16>(x, dy, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+      return backward_filter_exchange_t<__nv_bfloat16>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
     default:
-      return backward_filter_exchange_t<double>(x, dy, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+      return backward_filter_exchange_t<double>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
   }
+}
+
+int dwconv_b200_backward_filter_exchange(const void *x, const void *dy, void *dw_prev, void *workspace,
+                                         size_t workspace_bytes, int dtype,
+                                         const dwconv_b200_shape *shape, dwconv_b200_exchange *ex,
+                                         void *stream) {
+  return exchange_call(x, dy, nullptr, nullptr, dw_prev, workspace, workspace_bytes, dtype, shape, ex,
+                       stream);
+}
+
+int dwconv_b200_backward_exchange(const void *x, const void *dy, const void *w, void *dx, void *dw_prev,
+                                  void *workspace, size_t workspace_bytes, int dtype,
+                                  const dwconv_b200_shape *shape, dwconv_b200_exchange *ex,
+                                  void *stream) {
+  if (w == nullptr || dx == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  return exchange_call(x, dy, w, dx, dw_prev, workspace, workspace_bytes, dtype, shape, ex, stream);
 }
 
 int dwconv_b200_copy_async(void *dst, const void *src, size_t bytes, void *stream) {
@@ -507,6 +588,48 @@ int dwconv_b200_backward_filter(const void *x, const void *dy, void *dw, void *w
     default:
       return backward_filter_t<double>(x, dy, dw, workspace, workspace_bytes, *shape, st, forced);
   }
+}
+
+static int backward_call(const void *x, const void *dy, const void *w, void *dx, void *dw,
+                         void *workspace, size_t workspace_bytes, int dtype,
+                         const dwconv_b200_shape *shape, void *stream, bool dw_is_acc, int accumulate) {
+  int e = check_ptrs(dtype, x, dy, dx != nullptr ? dx : x);
+  if (e) return e;
+  if (dx != nullptr && w == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  if (dw == nullptr || workspace == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  const size_t acc_size = dtype == DWCONV_B200_F64 ? 8 : 4;
+  if (!aligned_to(dw, dw_is_acc ? acc_size : elem_size(dtype)) || (w != nullptr && !aligned_to(w, elem_size(dtype))))
+    return DWCONV_B200_MISALIGNED;
+  e = check_shape(shape);
+  if (e) return e;
+  if (!aligned_to(workspace, 16)) return DWCONV_B200_MISALIGNED;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int forced = g_forced_path.load();
+  switch (dtype) {
+    case DWCONV_B200_F32:
+      return backward_t<float>(x, dy, w, dx, dw, workspace, workspace_bytes, *shape, st, forced, dw_is_acc, accumulate);
+    case DWCONV_B200_F16:
+      return backward_t<__half>(x, dy, w, dx, dw, workspace, workspace_bytes, *shape, st, forced, dw_is_acc, accumulate);
+    case DWCONV_B200_BF16:
+      return backward_t<__nv_bfloat16>(x, dy, w, dx, dw, workspace, workspace_bytes, *shape, st, forced, dw_is_acc, accumulate);
+    default:
+      return backward_t<double>(x, dy, w, dx, dw, workspace, workspace_bytes, *shape, st, forced, dw_is_acc, accumulate);
+  }
+}
+
+int dwconv_b200_backward(const void *x, const void *dy, const void *w, void *dx, void *dw,
+                         void *workspace, size_t workspace_bytes, int dtype,
+                         const dwconv_b200_shape *shape, void *stream) {
+  if (dx == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  return backward_call(x, dy, w, dx, dw, workspace, workspace_bytes, dtype, shape, stream, false, 0);
+}
+
+int dwconv_b200_backward_accumulate(const void *x, const void *dy, const void *w, void *dx,
+                                    void *dw_acc, int accumulate, void *workspace,
+                                    size_t workspace_bytes, int dtype,
+                                    const dwconv_b200_shape *shape, void *stream) {
+  return backward_call(x, dy, w, dx, dw_acc, workspace, workspace_bytes, dtype, shape, stream, true,
+                       accumulate ? 1 : 0);
 }
 
 int dwconv_b200_use_dwconv2d_small(int in_h, int in_w, int kh, int kw, int up_h, int up_w,

@@ -126,19 +126,16 @@ direct_backward_filter_partial_kernel(const T *__restrict__ x, const T *__restri
 // scheduling; eight short chains instead of one long one keep the pass from being latency-bound.
 constexpr int FINALIZE_OUTPUTS = 32;  // per block
 constexpr int FINALIZE_PARTS = 8;
-template <typename T>
-__global__ void __launch_bounds__(FINALIZE_OUTPUTS * FINALIZE_PARTS)
-backward_filter_finalize_kernel(const typename Elem<T>::acc_t *__restrict__ partial,
-                                T *__restrict__ dw, const int C, const int kk, const int S) {
-  using A = typename Elem<T>::acc_t;
-  __shared__ A part_sum[FINALIZE_PARTS][FINALIZE_OUTPUTS];
+
+// The sum of output idx's S partial values, in the fixed order described above; valid in the
+// threads with part == 0.  Every thread of the block must call it (it synchronises).
+template <typename A>
+__device__ __forceinline__ A finalize_sum(const A *__restrict__ partial, const int idx, const bool live,
+                                          const int kk, const int S,
+                                          A (&part_sum)[FINALIZE_PARTS][FINALIZE_OUTPUTS]) {
   const int o = threadIdx.x & (FINALIZE_OUTPUTS - 1);
   const int part = threadIdx.x / FINALIZE_OUTPUTS;
-  const int idx = blockIdx.x * FINALIZE_OUTPUTS + o;
-  const bool live = idx < C * kk;
   A acc = 0;
-  pdl_launch_dependents();  // the next kernel in the stream may take its place early
-  pdl_wait();  // the first pass has finished and its partial sums are visible
   if (live) {
     const int c = idx / kk;
     const int tap = idx - c * kk;
@@ -148,12 +145,40 @@ backward_filter_finalize_kernel(const typename Elem<T>::acc_t *__restrict__ part
   }
   part_sum[part][o] = acc;
   __syncthreads();
-  if (part == 0 && live) {
-    A total = part_sum[0][o];
+  A total = part_sum[0][o];
 #pragma unroll
-    for (int q = 1; q < FINALIZE_PARTS; ++q) total += part_sum[q][o];
-    dw[idx] = Elem<T>::from_acc(total);
-  }
+  for (int q = 1; q < FINALIZE_PARTS; ++q) total += part_sum[q][o];
+  return total;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(FINALIZE_OUTPUTS * FINALIZE_PARTS)
+backward_filter_finalize_kernel(const typename Elem<T>::acc_t *__restrict__ partial,
+                                T *__restrict__ dw, const int C, const int kk, const int S) {
+  using A = typename Elem<T>::acc_t;
+  __shared__ A part_sum[FINALIZE_PARTS][FINALIZE_OUTPUTS];
+  const int idx = blockIdx.x * FINALIZE_OUTPUTS + (threadIdx.x & (FINALIZE_OUTPUTS - 1));
+  const bool live = idx < C * kk;
+  pdl_launch_dependents();  // the next kernel in the stream may take its place early
+  pdl_wait();  // the first pass has finished and its partial sums are visible
+  const A total = finalize_sum<A>(partial, idx, live, kk, S, part_sum);
+  if (threadIdx.x < FINALIZE_OUTPUTS && live) dw[idx] = Elem<T>::from_acc(total);
+}
+
+// The same second pass writing to an accumulator-typed gradient (fp32; fp64 for fp64 data):
+// dw_acc = total, or dw_acc += total when `accumulate` is set.  For callers that sum the
+// gradient over several calls (a batch processed in chunks) without a pass of their own.
+template <typename A>
+__global__ void __launch_bounds__(FINALIZE_OUTPUTS * FINALIZE_PARTS)
+backward_filter_finalize_acc_kernel(const A *__restrict__ partial, A *__restrict__ dw_acc,
+                                    const int C, const int kk, const int S, const int accumulate) {
+  __shared__ A part_sum[FINALIZE_PARTS][FINALIZE_OUTPUTS];
+  const int idx = blockIdx.x * FINALIZE_OUTPUTS + (threadIdx.x & (FINALIZE_OUTPUTS - 1));
+  const bool live = idx < C * kk;
+  pdl_launch_dependents();
+  pdl_wait();
+  const A total = finalize_sum<A>(partial, idx, live, kk, S, part_sum);
+  if (threadIdx.x < FINALIZE_OUTPUTS && live) dw_acc[idx] = accumulate ? dw_acc[idx] + total : total;
 }
 
 // Launch geometry of the second pass.

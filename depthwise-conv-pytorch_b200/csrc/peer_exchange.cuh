@@ -26,7 +26,10 @@ namespace dwb {
 
 constexpr int EXCHANGE_MAX_WORLD = 8;
 constexpr int EXCHANGE_SLOTS = 3;
-constexpr unsigned EXCHANGE_MAX_POLLS = 1u << 21;  // each poll is about 1 us: gives up after about 2 s
+// A kernel stops waiting for its peers' words this long after it started (whatever the world
+// size and however many words are late), or after this many polls of one word.
+constexpr unsigned long long EXCHANGE_WAIT_NS = 2000000000ull;  // 2 s
+constexpr unsigned EXCHANGE_MAX_POLLS = 1u << 22;
 
 struct ExchangePeers {
   unsigned char *buf[EXCHANGE_MAX_WORLD];  // every rank's buffer as mapped on this GPU
@@ -50,6 +53,23 @@ __device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long lo
   unsigned long long v;
   asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
+}
+
+// The call counter of a CTA is written by one exchange kernel and read by the next; both go
+// around the L1 cache (a kernel that became resident early may have read the line before its
+// predecessor wrote it).
+__device__ __forceinline__ unsigned ld_counter(const unsigned *p) {
+  unsigned v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_counter(unsigned *p, unsigned v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
 }
 
 template <typename A> struct ExchangeWords;
@@ -104,12 +124,13 @@ __device__ __forceinline__ void exchange_preload(const ExchangePeers &px, size_t
 }
 
 // Adds value idx of call `call` over the ranks, in rank order, from the preloaded words; a word
-// that had not arrived yet is polled (bounded).  false: a word did not arrive.
+// that does not carry the call's number (not arrived yet, or preloaded for another call) is
+// polled until `deadline` (global timer, ns).  false: a word did not arrive in time.
 template <typename A>
 __device__ __forceinline__ bool exchange_receive(const ExchangePeers &px, size_t header, int n,
                                                  int idx, unsigned call,
                                                  unsigned long long (&v)[EXCHANGE_MAX_WORLD][ExchangeWords<A>::W],
-                                                 A &sum) {
+                                                 unsigned long long deadline, A &sum) {
   constexpr int W = ExchangeWords<A>::W;
   const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(px.buf[px.rank] + header);
   sum = 0;
@@ -124,7 +145,7 @@ __device__ __forceinline__ bool exchange_receive(const ExchangePeers &px, size_t
         unsigned polls = 0;
         unsigned long long word = v[r][k];
         while ((unsigned)(word >> 32) != call) {
-          if (++polls > EXCHANGE_MAX_POLLS) return false;
+          if (++polls > EXCHANGE_MAX_POLLS || global_timer_ns() > deadline) return false;
           __nanosleep(200);
           word = ld_word_sys(words + k);
         }
@@ -154,32 +175,32 @@ backward_filter_finalize_exchange_kernel(const typename Elem<T>::acc_t *__restri
   const int n = C * kk;
   const int idx = b * FINALIZE_OUTPUTS + o;
   const bool live = idx < n;
-  A acc = 0;
   pdl_launch_dependents();  // the next kernel in the stream may take its place early
-  // The previous call's words do not depend on this call's first pass: warp 0 starts loading
-  // them before waiting for it (reads of this rank's own exchange buffer only).
+  // The previous call's words do not depend on this call's first pass, so warp 0 starts loading
+  // them before waiting for it (reads of this rank's own exchange buffer only).  Which call is
+  // "the previous one" is only known for certain after the wait: this CTA's counter is written
+  // at the end of the previous exchange kernel, which may still be running while this kernel is
+  // already resident (the kernels between the two start their dependents early).  So the early
+  // load goes by the counter as it reads now, a guess; the counter is read again after the wait,
+  // and every word is checked against the call number it must carry (exchange_receive), so a
+  // word loaded for the wrong call is simply loaded again.
   const size_t header = exchange_header_bytes(gridDim.x);
   unsigned *my_calls = reinterpret_cast<unsigned *>(px.buf[px.rank]);
-  unsigned call = 0;
   unsigned long long words[EXCHANGE_MAX_WORLD][ExchangeWords<A>::W];
+  unsigned guess = 0;
   if (part == 0) {
-    call = my_calls[b] + 1u;  // the same on every rank: all ranks make the same calls
-    if (live && call > 1u) exchange_preload<A>(px, header, n, idx, call - 1u, words);
+    guess = ld_counter(my_calls + b);
+    if (live && guess > 0u) exchange_preload<A>(px, header, n, idx, guess, words);
   }
-  pdl_wait();  // the first pass has finished and its partial sums are visible
-  if (live) {
-    const int c = idx / kk;
-    const int tap = idx - c * kk;
-    const A *src = partial + (long long)c * S * kk + tap;
-#pragma unroll 4
-    for (int sl = part; sl < S; sl += FINALIZE_PARTS) acc += src[(long long)sl * kk];
+  pdl_wait();  // the first pass has finished, and with it everything earlier in the stream
+  const unsigned long long deadline = global_timer_ns() + EXCHANGE_WAIT_NS;
+  unsigned call = 0;
+  if (part == 0) {
+    call = ld_counter(my_calls + b) + 1u;  // the same on every rank: all ranks make the same calls
+    if (live && call > 1u && call - 1u != guess) exchange_preload<A>(px, header, n, idx, call - 1u, words);
   }
-  part_sum[part][o] = acc;
-  __syncthreads();
+  const A total = finalize_sum<A>(partial, idx, live, kk, S, part_sum);
   if (part != 0) return;  // the exchange is warp 0's job: lane o owns output idx
-  A total = part_sum[0][o];
-#pragma unroll
-  for (int q = 1; q < FINALIZE_PARTS; ++q) total += part_sum[q][o];
 
   bool ok = true;
   if (live) {
@@ -187,19 +208,20 @@ backward_filter_finalize_exchange_kernel(const typename Elem<T>::acc_t *__restri
     // reading the previous call's, which is what makes three slots enough (see the top)
     if (call > 1u) {
       A sum;
-      ok = exchange_receive<A>(px, header, n, idx, call - 1u, words, sum);
+      ok = exchange_receive<A>(px, header, n, idx, call - 1u, words, deadline, sum);
       if (ok && dw_prev != nullptr) dw_prev[idx] = Elem<T>::from_acc(sum);
     }
     exchange_send<A>(px, header, n, idx, call, total);
   }
   ok = __all_sync(0xffffffffu, ok);
   if (o == 0) {
-    my_calls[b] = call;
+    st_counter(my_calls + b, call);
     if (!ok) atomicExch(error_flag, 1);
   }
 }
 
-// Completes the latest call: dw = its world sum.
+// Completes the latest call: dw = its world sum.  Launched as a programmatic dependent: it
+// may be resident while the kernel before it drains, and touches memory only after the wait.
 template <typename T>
 __global__ void __launch_bounds__(FINALIZE_OUTPUTS)
 exchange_finish_kernel(T *__restrict__ dw, const int n, const ExchangePeers px,
@@ -208,13 +230,16 @@ exchange_finish_kernel(T *__restrict__ dw, const int n, const ExchangePeers px,
   const int o = threadIdx.x, b = blockIdx.x;
   const int idx = b * FINALIZE_OUTPUTS + o;
   const size_t header = exchange_header_bytes(gridDim.x);
-  const unsigned call = reinterpret_cast<const unsigned *>(px.buf[px.rank])[b];
+  pdl_launch_dependents();
+  pdl_wait();  // the exchange kernel that made the latest call has stored its counter
+  const unsigned long long deadline = global_timer_ns() + EXCHANGE_WAIT_NS;
+  const unsigned call = ld_counter(reinterpret_cast<const unsigned *>(px.buf[px.rank]) + b);
   bool ok = true;
   if (idx < n && call > 0u) {
     A sum;
     unsigned long long words[EXCHANGE_MAX_WORLD][ExchangeWords<A>::W];
     exchange_preload<A>(px, header, n, idx, call, words);
-    ok = exchange_receive<A>(px, header, n, idx, call, words, sum);
+    ok = exchange_receive<A>(px, header, n, idx, call, words, deadline, sum);
     if (ok) dw[idx] = Elem<T>::from_acc(sum);
   }
   ok = __all_sync(0xffffffffu, ok);

@@ -18,6 +18,13 @@ template <typename T>
 int rows_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *partial, const Shape &s,
                          cudaStream_t st, int *slices_out);
 
+// Fused backward: dx and the first pass of dW (partial sums, as rows_backward_filter) from one
+// read of dy.
+template <typename T> int rows_backward_slices(const Shape &s);
+template <typename T>
+int rows_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<T>::acc_t *partial,
+                  const Shape &s, cudaStream_t st, int *slices_out);
+
 // Reads and clears the flags kernels raise when a bounded wait expires (synchronises the
 // device).  Bit 0: forward/backward-input kernels, bit 1: backward-filter kernels.
 int rows_take_device_error();
@@ -25,7 +32,9 @@ int rows_take_device_error();
 // VI, VO, U, mask, LW, G, NRT, TH, NRB, RBH, PS, ZT, ZBF, TAPB, DPL, DYOFF, ntiles|TPC, SL, mode.
 int rows_debug_conv_plan(int op, int esize, const Shape &s, int a16, int *out);
 int rows_debug_filter_plan(int esize, const Shape &s, int a16, int *out);
+int rows_debug_backward_plan(int esize, const Shape &s, int a16, int *out);
 int rows_conv_take_error();
 int rows_filter_take_error();
+int rows_backward_take_error();
 
 }  // namespace dwb

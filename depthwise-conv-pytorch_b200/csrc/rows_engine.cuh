@@ -601,17 +601,9 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
       int r_begin, r_end;
       task_rows_fast<RS>(rb, p.NRB, p.inv_NRB, t.R0, t.th, r_begin, r_end);
 
-      // The K*K taps live in registers for the task.  (Measured alternative for K = 7, kept
-      // behind this switch: re-laying the taps as fp32 rows of 8 in a per-segment scratch and
-      // reading them back per tap row frees 49 registers and allows two CTAs per SM, but the
-      // extra shared-memory loads cost more than the occupancy returns: 108 vs 71 us on the
-      // 56x56 fp16 layer.)
-      constexpr bool TAPS_IN_SMEM = false;
-      constexpr int TK = TAPS_IN_SMEM ? 1 : K;
-      float taps[TK][TK];
-      const uint32_t seg_taps = smem_u32(ring.scratch) + (uint32_t)(seg * (K * 8 * 4));
+      // The K*K taps live in registers for the task (backward-input reads them back to front).
+      float taps[K][K];
       {
-        // this plane's taps in the stage; backward-input reads them back to front
         const int cw = tl.c_base + g;
         const T *tp = staps;
         if (active) {
@@ -620,21 +612,11 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
                             : staps + tl.offB16 + tl.phaseB + (cw - p.C) * KK;
         }
         const int t_first = p.flip ? KK - 1 : 0, t_step = p.flip ? -1 : 1;
-        if constexpr (TAPS_IN_SMEM) {
-          __syncwarp();  // the previous task's reads of the scratch are over
-          float *dst = ring.scratch + seg * (K * 8);
-          for (int idx = j; idx < K * 8; idx += LW) {
-            const int ty = idx >> 3, tx = idx & 7;
-            dst[idx] = (active && tx < K) ? Elem<T>::to_acc(tp[t_first + t_step * (ty * K + tx)]) : 0.f;
-          }
-          __syncwarp();
-        } else {
 #pragma unroll
-          for (int ty = 0; ty < K; ++ty)
+        for (int ty = 0; ty < K; ++ty)
 #pragma unroll
-            for (int tx = 0; tx < K; ++tx)
-              taps[ty][tx] = active ? Elem<T>::to_acc(tp[t_first + t_step * (ty * K + tx)]) : 0.f;
-        }
+          for (int tx = 0; tx < K; ++tx)
+            taps[ty][tx] = active ? Elem<T>::to_acc(tp[t_first + t_step * (ty * K + tx)]) : 0.f;
       }
       // row index (inside the plane's staged rows) of window row 0, its shared address, and the
       // row pitch; lanes with nothing to read have lim = 0 and only ever read the zero bytes
@@ -677,20 +659,9 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
           for (int ty = 0; ty < K; ++ty) {
             if (!Geo::used(u, ty)) continue;
             const int ri = Geo::rel(u, ty) - Geo::RMIN;
-            float trow[8];
-            if constexpr (TAPS_IN_SMEM) {
-              float lo[4], hi[4];
-              SmemLd<float, 4>::ld(seg_taps + ty * 32, lo);
-              SmemLd<float, 4>::ld(seg_taps + ty * 32 + 16, hi);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                trow[i] = lo[i];
-                trow[4 + i] = hi[i];
-              }
-            }
 #pragma unroll
             for (int tx = 0; tx < K; ++tx) {
-              const float tap = TAPS_IN_SMEM ? trow[tx & 7] : taps[TAPS_IN_SMEM ? 0 : ty][TAPS_IN_SMEM ? 0 : tx];
+              const float tap = taps[ty][tx];
 #pragma unroll
               for (int e = 0; e < VO; ++e) {
                 if (!Geo::used(e, tx)) continue;

@@ -234,7 +234,9 @@ int rows_filter_take_error() {
   return v;
 }
 
-int rows_take_device_error() { return rows_conv_take_error() | rows_filter_take_error(); }
+int rows_take_device_error() {
+  return rows_conv_take_error() | rows_filter_take_error() | rows_backward_take_error();
+}
 
 template int rows_backward_filter_slices<float>(const Shape &);
 template int rows_backward_filter_slices<__half>(const Shape &);

@@ -30,6 +30,17 @@ def _dtype_code(t, *others):
     return code
 
 
+def _check_filter(input, kernel):
+    """The library reads C*kh*kw filter values and N*C planes through raw pointers: a tensor
+    of another shape would be read out of bounds, so it is refused here."""
+    if input.dim() != 4 or kernel.dim() != 4:
+        raise RuntimeError(f"dwconv_b200: expected 4-d input and kernel, got {tuple(input.shape)} "
+                           f"and {tuple(kernel.shape)}")
+    if kernel.shape[0] != input.shape[1] or kernel.shape[1] != 1:
+        raise RuntimeError(f"dwconv_b200: kernel must be [C, 1, kh, kw] with C = {input.shape[1]}, "
+                           f"got {tuple(kernel.shape)}")
+
+
 def _stream(t):
     return torch.cuda.current_stream(t.device).cuda_stream
 
@@ -46,6 +57,7 @@ def dwconv2d(input, kernel, up_h, up_w, down_h, down_w, pad_h0, pad_h1, pad_w0, 
     _check_cuda(input, "input")
     _check_cuda(kernel, "kernel")
     code = _dtype_code(input, kernel)
+    _check_filter(input, kernel)
     input = input.contiguous()
     kernel = kernel.contiguous()
     N, C, H, W = input.shape
@@ -74,6 +86,12 @@ def dwconv2d_backward_kernel(input, out_grad, kernel, up_h, up_w, down_h, down_w
     _check_cuda(input, "input")
     _check_cuda(out_grad, "out_grad")
     code = _dtype_code(input, out_grad)
+    if input.dim() != 4 or out_grad.dim() != 4 or kernel.dim() != 4:
+        raise RuntimeError("dwconv_b200.dwconv2d_backward_kernel: expected 4-d tensors")
+    if tuple(out_grad.shape[:2]) != tuple(input.shape[:2]):
+        raise RuntimeError(f"dwconv_b200.dwconv2d_backward_kernel: out_grad is "
+                           f"{tuple(out_grad.shape)} but input is {tuple(input.shape)} "
+                           "(batch and channels must agree)")
     input = input.contiguous()
     out_grad = out_grad.contiguous()
     N, C, H, W = input.shape

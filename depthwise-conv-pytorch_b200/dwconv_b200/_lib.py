@@ -42,6 +42,8 @@ def _load():
         "dwconv_b200_backward_input": (ci, [vp, vp, vp, ci, sp, vp]),
         "dwconv_b200_backward_filter_workspace_bytes": (sz, [ci, sp]),
         "dwconv_b200_backward_filter": (ci, [vp, vp, vp, vp, sz, ci, sp, vp]),
+        "dwconv_b200_backward": (ci, [vp, vp, vp, vp, vp, vp, sz, ci, sp, vp]),
+        "dwconv_b200_backward_accumulate": (ci, [vp, vp, vp, vp, vp, ci, vp, sz, ci, sp, vp]),
         "dwconv_b200_use_dwconv2d_small": (ci, [ci] * 10),
         "dwconv_b200_dwconv2d": (ci, [vp, vp, vp, ci] + [ci] * 15 + [vp]),
         "dwconv_b200_dwconv2d_small": (ci, [vp, vp, vp, ci] + [ci] * 13 + [vp]),
@@ -55,6 +57,7 @@ def _load():
         "dwconv_b200_exchange_destroy": (ci, [vp]),
         "dwconv_b200_exchange_finish": (ci, [vp, vp, vp]),
         "dwconv_b200_backward_filter_exchange": (ci, [vp, vp, vp, vp, sz, ci, sp, vp, vp]),
+        "dwconv_b200_backward_exchange": (ci, [vp, vp, vp, vp, vp, vp, sz, ci, sp, vp, vp]),
     }
     for name, (res, args) in sig.items():
         try:
@@ -74,6 +77,7 @@ EXPORTS = (
     "dwconv_b200_debug_plan", "dwconv_b200_out_size",
     "dwconv_b200_forward", "dwconv_b200_backward_input",
     "dwconv_b200_backward_filter_workspace_bytes", "dwconv_b200_backward_filter",
+    "dwconv_b200_backward", "dwconv_b200_backward_accumulate", "dwconv_b200_backward_exchange",
     "dwconv_b200_use_dwconv2d_small", "dwconv_b200_dwconv2d", "dwconv_b200_dwconv2d_small",
     "dwconv_b200_dwconv2d_backward_kernel", "dwconv_b200_static_scratch_bytes",
     "dwconv_b200_backward_filter_static",
@@ -86,6 +90,29 @@ EXPORTS = (
 
 def status_string(code):
     return lib.dwconv_b200_status_string(int(code)).decode()
+
+
+def device_status():
+    """Synchronises the current device and returns (and clears) the flags its kernels raised
+    when one of their bounded waits ran out: 0 = none, bit 0 forward / backward-input, bit 1
+    backward-filter, bit 2 the exchange between GPUs, -1 = the device reported an error."""
+    return int(lib.dwconv_b200_device_status())
+
+
+def check_device_status(what):
+    """Raises if a kernel gave up waiting since the last check (its output is then incomplete)."""
+    v = device_status()
+    if v != 0:
+        names = [n for bit, n in ((1, "forward/backward-input"), (2, "backward-filter"),
+                                  (4, "exchange between GPUs")) if v > 0 and v & bit]
+        raise RuntimeError(f"dwconv_b200.{what}: a kernel's bounded wait expired "
+                           f"(device status {v}: {', '.join(names) or 'CUDA error'}); "
+                           "the results of the calls since the last check are incomplete")
+
+
+# DWCONV_B200_CHECK_STATUS=1: the autograd function synchronises and checks the device flags
+# after every backward (debugging aid: costs a device synchronisation per call).
+CHECK_STATUS = os.environ.get("DWCONV_B200_CHECK_STATUS", "0") not in ("", "0")
 
 
 def check(code, what):

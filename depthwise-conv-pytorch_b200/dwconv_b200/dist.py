@@ -146,6 +146,13 @@ class PeerFilterExchange:
     identical bits on every rank.  All ranks must make the same calls.  Needs all ranks on one
     node with peer access between their GPUs; raises ``RuntimeError`` otherwise (use
     ``FilterGradReducer`` then).
+
+    Tear-down is collective too: a peer's kernel stores into this rank's buffer, so no rank may
+    free its buffer while any rank still has a call in flight.  ``close()`` therefore
+    synchronises the device and meets the other ranks at a barrier before it unmaps and frees;
+    every rank must call it (after its last ``finish``).  An object that is dropped without
+    ``close()`` in a multi-rank run keeps its buffer until the process exits rather than risk
+    freeing memory a peer is still writing.
     """
 
     def __init__(self, channels, kernel_size, dtype, device, group=None):
@@ -180,6 +187,12 @@ class PeerFilterExchange:
         """Local gradient of (x, dy), sent to all ranks; ``dw_prev`` (optional) receives the
         previous call's world sum."""
         _lib = self._lib
+        if (x.dim() != 4 or dy.dim() != 4 or tuple(dy.shape[:2]) != tuple(x.shape[:2])
+                or x.shape[1] != self.C or x.dtype != self.dtype or dy.dtype != self.dtype
+                or not x.is_contiguous() or not dy.is_contiguous()):
+            raise RuntimeError(f"dwconv_b200.PeerFilterExchange: x {tuple(x.shape)} / dy "
+                               f"{tuple(dy.shape)} must be contiguous {self.dtype} maps with the "
+                               f"same batch and {self.C} channels")
         N, C, H, W = x.shape
         sh, sw = (stride, stride) if isinstance(stride, int) else stride
         ph, pw = (padding, padding) if isinstance(padding, int) else padding
@@ -212,13 +225,31 @@ class PeerFilterExchange:
             x_ptr, dy_ptr, dw_prev_ptr, ws_ptr, ws_bytes, self.code, shape, self._ex, stream),
             "backward_filter_exchange")
 
+    def launch_backward(self, x_ptr, dy_ptr, w_ptr, dx_ptr, dw_prev_ptr, ws_ptr, ws_bytes, shape,
+                        stream):
+        """As ``launch``, with the fused backward's first pass: ``dx`` is written as well
+        (``dwconv_b200_backward_exchange``)."""
+        self._lib.check(self._lib.lib.dwconv_b200_backward_exchange(
+            x_ptr, dy_ptr, w_ptr, dx_ptr, dw_prev_ptr, ws_ptr, ws_bytes, self.code, shape, self._ex,
+            stream), "backward_exchange")
+
     def close(self):
-        if self._ex:
+        """Collective: every rank calls it, after its last ``finish``."""
+        if not self._ex:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)   # this rank's calls have left the GPU
+            if self.world > 1:
+                dist.barrier(group=self.group)    # ... and so have everybody else's
             self._lib.lib.dwconv_b200_exchange_destroy(self._ex)
-            self._ex = None
+        self._ex = None
 
     def __del__(self):
+        # Without the other ranks at a barrier it is not safe to free a buffer they may be
+        # storing into: a single-rank object is destroyed, a multi-rank one is left to the
+        # process exit.
         try:
-            self.close()
+            if getattr(self, "world", 2) == 1:
+                self.close()
         except Exception:  # noqa: BLE001  (interpreter shutdown)
             pass

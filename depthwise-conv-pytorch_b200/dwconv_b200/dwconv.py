@@ -52,6 +52,7 @@ class DepthwiseConv2dFunction(Function):
         code = _C._dtype_code(input, kernel)
         stride = tuple(int(v) for v in stride)
         pad = tuple(int(v) for v in pad)
+        _C._check_filter(input, kernel)
         input = input.contiguous()
         kernel = kernel.contiguous()
         shape = _forward_shape(input, kernel, stride, pad)
@@ -77,24 +78,40 @@ class DepthwiseConv2dFunction(Function):
     def backward(ctx, grad_output):
         input, kernel = ctx.saved_tensors
         shape, code = ctx.shape, ctx.code
+        if tuple(grad_output.shape) != (shape.N, shape.C, shape.Ho, shape.Wo):
+            raise RuntimeError(f"depthwise_conv2d backward: grad_output has shape "
+                               f"{tuple(grad_output.shape)}, expected "
+                               f"{(shape.N, shape.C, shape.Ho, shape.Wo)}")
         grad_output = grad_output.contiguous()
         grad_input = grad_kernel = None
         with torch.cuda.device(input.device):
             stream = _C._stream(input)
-            if ctx.needs_input_grad[0]:
+            want_dx, want_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+            if want_dw:
+                nbytes = _lib.lib.dwconv_b200_backward_filter_workspace_bytes(code, shape)
+                ws = torch.empty(nbytes, dtype=torch.uint8, device=input.device)
+                grad_kernel = torch.empty_like(kernel)
+            if want_dx:
                 grad_input = torch.empty_like(input)
+            if want_dx and want_dw:
+                # both gradients from one pass over grad_output
+                st = _lib.lib.dwconv_b200_backward(
+                    input.data_ptr(), grad_output.data_ptr(), kernel.data_ptr(),
+                    grad_input.data_ptr(), grad_kernel.data_ptr(), ws.data_ptr(), nbytes, code,
+                    shape, stream)
+                _lib.check(st, "backward")
+            elif want_dx:
                 st = _lib.lib.dwconv_b200_backward_input(
                     grad_output.data_ptr(), kernel.data_ptr(), grad_input.data_ptr(), code, shape,
                     stream)
                 _lib.check(st, "backward_input")
-            if ctx.needs_input_grad[1]:
-                nbytes = _lib.lib.dwconv_b200_backward_filter_workspace_bytes(code, shape)
-                ws = torch.empty(nbytes, dtype=torch.uint8, device=input.device)
-                grad_kernel = torch.empty_like(kernel)
+            elif want_dw:
                 st = _lib.lib.dwconv_b200_backward_filter(
                     input.data_ptr(), grad_output.data_ptr(), grad_kernel.data_ptr(),
                     ws.data_ptr(), nbytes, code, shape, stream)
                 _lib.check(st, "backward_filter")
+            if _lib.CHECK_STATUS:
+                _lib.check_device_status("backward")
         return grad_input, grad_kernel, None, None, None
 
 

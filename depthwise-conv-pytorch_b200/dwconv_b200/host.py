@@ -8,7 +8,10 @@ back, so that a step costs about max(upload, download) instead of their sum plus
 
 ``y`` and ``dx`` are what the one-call path gives, bit for bit (images are independent).
 ``dw`` is the fp32 sum (fp64 for float64 maps) of the per-chunk filter gradients in chunk
-order: deterministic, but not the same rounding as one call over the whole batch.
+order: deterministic, but not the same rounding as one call over the whole batch.  Each
+chunk's two gradients come from the fused backward call (one read of dy), whose second pass
+adds straight into the running fp32 gradient: no kernel other than the library's own runs
+between the copies.
 """
 import torch
 
@@ -86,7 +89,6 @@ class HostMapsStep:
             self.dy_ = [mk(nc, C, Ho, Wo) for _ in range(self.SLOTS)]
             self.y_ = [mk(nc, C, Ho, Wo) for _ in range(self.SLOTS)]
             self.w_ = mk(C, 1, kh, kw)
-            self.dw_chunk = mk(C, 1, kh, kw)
             self.dw_acc = torch.zeros((C, 1, kh, kw), dtype=self.acc_dtype, device=self.device)
             self.dw_out = mk(C, 1, kh, kw)
             self.ws_bytes = max(int(L.dwconv_b200_backward_filter_workspace_bytes(
@@ -99,7 +101,7 @@ class HostMapsStep:
             self.s_cap = torch.cuda.Stream(self.device)   # records the schedule into a graph
         self.h2d_bytes = (N * C * (H * W + Ho * Wo) + C * kh * kw) * esize
         self.d2h_bytes = (N * C * (H * W + Ho * Wo) + C * kh * kw) * esize
-        self.launches_per_run = 4 * len(self.bounds)  # forward, backward-input, filter partial + finalize
+        self.launches_per_run = 3 * len(self.bounds)  # forward, fused backward first + second pass
 
     def _copy(self, dev_buf, host, a, b, up, stream):
         """Images a..b of a host map to / from the start of a staging buffer: one bare
@@ -162,10 +164,9 @@ class HostMapsStep:
         start.record(cur)
         for s in (self.s_up, self.s_run, self.s_down):
             s.wait_event(start)
-        with torch.cuda.stream(self.s_up):
-            self.w_.copy_(w, non_blocking=True)
-        with torch.cuda.stream(self.s_run):
-            self.dw_acc.zero_()
+        _lib.check(L.dwconv_b200_copy_async(self.w_.data_ptr(), w.data_ptr(),
+                                            w.numel() * w.element_size(), self.s_up.cuda_stream),
+                   "copy_async")
         ran, drained = {}, {}
         for i, (a, b) in enumerate(self.bounds):
             k, n = i % self.SLOTS, b - a
@@ -184,13 +185,11 @@ class HostMapsStep:
                 xk, dyk, yk, dxk = self.x_[k], self.dy_[k], self.y_[k], self.dx_[k]
                 _lib.check(L.dwconv_b200_forward(xk.data_ptr(), self.w_.data_ptr(), yk.data_ptr(),
                                                  code, shp, st), "forward")
-                _lib.check(L.dwconv_b200_backward_input(dyk.data_ptr(), self.w_.data_ptr(),
-                                                        dxk.data_ptr(), code, shp, st),
-                           "backward_input")
-                _lib.check(L.dwconv_b200_backward_filter(
-                    xk.data_ptr(), dyk.data_ptr(), self.dw_chunk.data_ptr(), self.ws.data_ptr(),
-                    self.ws_bytes, code, shp, st), "backward_filter")
-                self.dw_acc.add_(self.dw_chunk)
+                # dx of the chunk, and dw_acc (+)= the chunk's filter gradient (first chunk: =)
+                _lib.check(L.dwconv_b200_backward_accumulate(
+                    xk.data_ptr(), dyk.data_ptr(), self.w_.data_ptr(), dxk.data_ptr(),
+                    self.dw_acc.data_ptr(), 1 if i > 0 else 0, self.ws.data_ptr(), self.ws_bytes,
+                    code, shp, st), "backward_accumulate")
                 ran[i] = ev()
                 ran[i].record(self.s_run)
             with torch.cuda.stream(self.s_down):
@@ -208,8 +207,11 @@ class HostMapsStep:
         """The batch's filter gradient: summed over the ranks if asked, cast, sent to the host."""
         if self.all_reduce:
             torch.distributed.all_reduce(self.dw_acc, group=self.group)
-        self.dw_out.copy_(self.dw_acc)
-        dw.copy_(self.dw_out, non_blocking=True)
+        if self.dw_acc.dtype == self.dtype:   # fp32 / fp64 maps: the accumulator is the result
+            dw.copy_(self.dw_acc, non_blocking=True)
+        else:
+            self.dw_out.copy_(self.dw_acc)    # one cast per step for 16-bit maps
+            dw.copy_(self.dw_out, non_blocking=True)
 
     def synchronize(self):
         torch.cuda.current_stream(self.device).synchronize()

@@ -74,8 +74,13 @@ class StackStep:
     through the C entry points and replayed as one CUDA graph.
 
     ``x[i]``, ``dy[i]`` are the buffers to fill; ``y[i]``, ``dx[i]``, ``dw[i]`` hold the results
-    after ``run()``.  ``exchanges`` (one ``PeerFilterExchange`` per layer, optional) makes ``dw``
-    the sum over all ranks; it then lags by one step until ``finish()``.
+    after ``run()``.  Both gradients of a layer come from the fused backward call (one read of
+    ``dy``).  ``exchanges`` (one ``PeerFilterExchange`` per layer, optional) makes ``dw`` the
+    sum over all ranks: each layer's gradient is sent to the other GPUs inside the kernel that
+    finishes it, the remaining layers' kernels hide the flight of those stores, and the step
+    ends with one small kernel per layer that adds the ranks' values, so ``dw`` is the world sum
+    of THIS step when ``run()`` has completed (as the reference returns the complete gradient
+    from ``backward``, torch_dwconv/dwconv.py:66-70).
     """
 
     def __init__(self, stack, batch, device="cuda", use_graph=True, exchanges=None):
@@ -117,16 +122,17 @@ class StackStep:
         for i in reversed(range(n)):
             shape, code, nws, ws = self._geo[i]
             w = self.stack.layers[i].weight
-            _lib.check(L.dwconv_b200_backward_input(self.dy[i].data_ptr(), w.data_ptr(),
-                                                    self.dx[i].data_ptr(), code, shape, st),
-                       "backward_input")
             if self.exchanges is not None:
-                self.exchanges[i].launch(self.x[i].data_ptr(), self.dy[i].data_ptr(),
-                                         self.dw[i].data_ptr(), ws.data_ptr(), nws, shape, st)
+                self.exchanges[i].launch_backward(
+                    self.x[i].data_ptr(), self.dy[i].data_ptr(), w.data_ptr(), self.dx[i].data_ptr(),
+                    None, ws.data_ptr(), nws, shape, st)
             else:
-                _lib.check(L.dwconv_b200_backward_filter(
-                    self.x[i].data_ptr(), self.dy[i].data_ptr(), self.dw[i].data_ptr(),
-                    ws.data_ptr(), nws, code, shape, st), "backward_filter")
+                _lib.check(L.dwconv_b200_backward(
+                    self.x[i].data_ptr(), self.dy[i].data_ptr(), w.data_ptr(), self.dx[i].data_ptr(),
+                    self.dw[i].data_ptr(), ws.data_ptr(), nws, code, shape, st), "backward")
+        if self.exchanges is not None:
+            for i in reversed(range(n)):
+                self.exchanges[i].finish(self.dw[i], stream=st)
 
     def run(self):
         """Queues one step on the current stream (the first call runs eagerly: kernel set-up;
@@ -146,10 +152,8 @@ class StackStep:
             self._ran += 1
 
     def finish(self):
-        """With ``exchanges``: completes the latest step's sum over the ranks into ``dw``."""
-        if self.exchanges is not None:
-            for ex, dw in zip(self.exchanges, self.dw):
-                ex.finish(dw)
+        """Kept for callers of the earlier, pipelined form: ``run()`` now completes the sum
+        over the ranks itself, so there is nothing left to do."""
 
     def images_per_second(self, steps=50, warmup=5):
         """Device-timed throughput of ``run()`` (CUDA events on the current stream)."""

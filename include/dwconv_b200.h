@@ -6,8 +6,10 @@
  * of rosinality/depthwise-conv-pytorch.  That extension exports four functions
  * from a pybind11 module (torch_dwconv/dwconv.cpp:60-67); each of them has a
  * counterpart below that takes raw device pointers, sizes and a stream instead
- * of torch tensors, and never allocates: the caller owns inputs, outputs and
- * the backward-filter workspace.
+ * of torch tensors.  The operators never allocate: the caller owns inputs,
+ * outputs and the backward workspace.  (The one allocating entry point is
+ * dwconv_b200_exchange_create, which makes the buffer that peers' GPUs write
+ * into for the multi-GPU sum; it is not on the per-call path.)
  *
  * Conventions
  *   - activations are contiguous NCHW, filters contiguous [C,1,kh,kw];
@@ -42,7 +44,7 @@ extern "C" {
 #define DWCONV_B200_API
 #endif
 
-#define DWCONV_B200_VERSION 100 /* major*10000 + minor*100 + patch */
+#define DWCONV_B200_VERSION 200 /* major*10000 + minor*100 + patch */
 
 typedef enum dwconv_b200_dtype {
   DWCONV_B200_F32 = 0,
@@ -53,7 +55,7 @@ typedef enum dwconv_b200_dtype {
 
 typedef enum dwconv_b200_status {
   DWCONV_B200_OK = 0,
-  DWCONV_B200_BAD_ARGUMENT = 1,       /* null pointer, non-positive extent, inconsistent sizes */
+  DWCONV_B200_BAD_ARGUMENT = 1,       /* null pointer, non-positive extent, an exchange object of another layer */
   DWCONV_B200_UNSUPPORTED_DTYPE = 2,
   DWCONV_B200_MISALIGNED = 3,         /* pointer not aligned to its element size */
   DWCONV_B200_WORKSPACE_TOO_SMALL = 4,
@@ -96,7 +98,7 @@ DWCONV_B200_API int dwconv_b200_last_cuda_error(void);
 DWCONV_B200_API int dwconv_b200_device_status(void);
 
 /* Host-only: the kernel variant and tiling the rows family would use for an operator
- * (op 0 forward, 1 backward-input, 2 backward-filter), as 24 ints; returns 0 if that family
+ * (op 0 forward, 1 backward-input, 2 backward-filter, 3 fused backward), as 24 ints; returns 0 if that family
  * declines the problem.  For tests that model the kernels' index arithmetic on the CPU.
  * No counterpart in the reference. */
 DWCONV_B200_API int dwconv_b200_debug_plan(int op, int dtype, const dwconv_b200_shape *shape,
@@ -142,6 +144,31 @@ DWCONV_B200_API int dwconv_b200_backward_filter(const void *x, const void *dy, v
                                 size_t workspace_bytes, int dtype,
                                 const dwconv_b200_shape *shape, void *stream);
 
+/* Both gradients from ONE pass over dy: dx as dwconv_b200_backward_input (bit for bit),
+ * dw as dwconv_b200_backward_filter (same two-pass reduction; the partial sums are
+ * accumulated in another order, so dw agrees to rounding, not bit for bit).  For the
+ * shapes the tiled kernels serve (3x3 / 5x5 / 7x7, stride 1 or 2, padding k/2, fp32 and
+ * fp16, maps up to 128 columns) the first pass is one kernel that stages the dy rows and
+ * the x rows of a group of planes in shared memory and uses every dy window value twice;
+ * other shapes run backward-input and backward-filter one after the other.  `workspace`
+ * as for dwconv_b200_backward_filter (same size query).
+ * Replaces the pair of calls at torch_dwconv/dwconv.py:56-68 (dwconv2d(forward=false)
+ * followed by dwconv2d_backward_kernel), which read dy from memory twice. */
+DWCONV_B200_API int dwconv_b200_backward(const void *x, const void *dy, const void *w, void *dx, void *dw,
+                                         void *workspace, size_t workspace_bytes, int dtype,
+                                         const dwconv_b200_shape *shape, void *stream);
+
+/* As dwconv_b200_backward, but the filter gradient goes to an ACCUMULATOR-typed buffer
+ * dw_acc [C,1,kh,kw] (float for f32 / f16 / bf16 data, double for f64): dw_acc = sum when
+ * `accumulate` is 0, dw_acc += sum otherwise.  For a batch processed in chunks (calls on one
+ * stream add in call order: deterministic).  dx (and then w) may be null: filter gradient only.
+ * No counterpart in the reference, which zero-fills and adds with atomics inside one call
+ * (dwconv_kernel.cu:1026-1027, :303-305). */
+DWCONV_B200_API int dwconv_b200_backward_accumulate(const void *x, const void *dy, const void *w, void *dx,
+                                                    void *dw_acc, int accumulate, void *workspace,
+                                                    size_t workspace_bytes, int dtype,
+                                                    const dwconv_b200_shape *shape, void *stream);
+
 /* One asynchronous copy between any two of: device memory, pinned host memory
  * (direction inferred from the pointers), on `stream`.  A bare copy with nothing recorded
  * around it, for pipelines that move maps between pinned host memory and the
@@ -176,13 +203,23 @@ DWCONV_B200_API int dwconv_b200_copy_async(void *dst, const void *src, size_t by
  *                     pass sends this call's sums to every rank and writes the
  *                     PREVIOUS call's world sum to dw_prev (null: not wanted;
  *                     nothing is written on the first call).
+ *   backward_exchange the same with the fused backward's first pass
+ *                     (dwconv_b200_backward): dx is written too.
  *   exchange_finish   dw = the world sum of the latest call.  Waits for the
- *                     peers' words if they are still in flight.
+ *                     peers' words if they are still in flight.  A step that
+ *                     needs its own sum before it ends calls this after the
+ *                     kernels that follow the exchange call in the step
+ *                     (they hide the stores' flight time).
+ *   exchange_destroy  unmaps the peers' buffers and frees this rank's.  A peer's
+ *                     kernel stores into this rank's buffer, so destroy only
+ *                     when EVERY rank has finished its last call: synchronise
+ *                     the device, meet the other ranks at a host barrier, then
+ *                     destroy.
  *
  * Every rank must make the same sequence of backward_filter_exchange calls
  * with the same geometry; one exchange object serves one layer, one call at a
  * time (calls on one stream are).  BAD_ARGUMENT if the shape is not the
- * object's.  A rank that waits for a peer's word longer than about two seconds
+ * object's.  A kernel that has waited two seconds for its peers' words
  * stops waiting, leaves that output unwritten and raises bit 2 (value 4) of
  * dwconv_b200_device_status.
  * ---------------------------------------------------------------------- */
@@ -197,6 +234,10 @@ DWCONV_B200_API int dwconv_b200_backward_filter_exchange(const void *x, const vo
                                                          void *workspace, size_t workspace_bytes,
                                                          int dtype, const dwconv_b200_shape *shape,
                                                          dwconv_b200_exchange *ex, void *stream);
+DWCONV_B200_API int dwconv_b200_backward_exchange(const void *x, const void *dy, const void *w, void *dx,
+                                                  void *dw_prev, void *workspace, size_t workspace_bytes,
+                                                  int dtype, const dwconv_b200_shape *shape,
+                                                  dwconv_b200_exchange *ex, void *stream);
 
 /* ------------------------------------------------------------------------
  * Operator-form entry points: one per function of the reference's pybind

@@ -15,6 +15,8 @@ so the include resolves to the toolkit's CUB.  Nothing is copied into the
 tracked tree; the only outputs are ``oracle/_ref/torch_dwconv/{_C.so,*.py}``.
 
 Usage:  python oracle/build_ref.py [/path/to/reference]
+        (default: the directory named by the environment variable DWCONV_REFERENCE_DIR,
+        else a sibling checkout ``reference/`` beside this repository)
 """
 import glob
 import os
@@ -26,8 +28,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref", "torch_dwconv")
 
 
-def build_ref(ref_root="/root/reference", verbose=False):
-    src = os.path.join(ref_root, "torch_dwconv")
+def default_reference_dir():
+    """Where the reference checkout is looked for when no path is given."""
+    return os.environ.get("DWCONV_REFERENCE_DIR") or os.path.join(
+        os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build_ref(ref_root=None, verbose=False):
+    src = os.path.join(ref_root or default_reference_dir(), "torch_dwconv")
     if not os.path.isdir(src):
         return None
     so = os.path.join(OUT, "_C.so")
@@ -58,5 +66,5 @@ def build_ref(ref_root="/root/reference", verbose=False):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else None
     print(build_ref(root, verbose=True))

@@ -49,6 +49,10 @@ def main():
     a = ap.parse_args()
 
     import torch
+    # all the host cores, whatever the launcher put into OMP_NUM_THREADS (torchrun sets it to 1
+    # for every rank it starts, which would make this a single-threaded figure)
+    ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(max(1, ncpu))
     layers = json.loads(a.layers)
     ref = None if a.force_port else load_reference()
     dts = {"f32": torch.float32, "f16": torch.float16, "f64": torch.float64}

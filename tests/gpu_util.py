@@ -65,6 +65,29 @@ def c_backward_filter(x, dy, k_hw, stride, padding):
     return st, dw
 
 
+def c_backward(x, dy, w, stride, padding):
+    """Both gradients through the fused entry point: (status, dx, dw)."""
+    s = make_shape(x.shape, w.shape[2:], stride, padding)
+    assert (s.Ho, s.Wo) == tuple(dy.shape[2:])
+    nbytes = _lib.lib.dwconv_b200_backward_filter_workspace_bytes(CODE[x.dtype], s)
+    ws = torch.full((nbytes + 256,), 0xA5, dtype=torch.uint8, device=x.device)
+    dx = torch.full(tuple(x.shape), float("nan"), dtype=x.dtype, device=x.device)
+    dw = torch.full(tuple(w.shape), float("nan"), dtype=x.dtype, device=x.device)
+    st = _lib.lib.dwconv_b200_backward(x.data_ptr(), dy.data_ptr(), w.data_ptr(), dx.data_ptr(),
+                                       dw.data_ptr(), ws.data_ptr(), nbytes, CODE[x.dtype], s,
+                                       _stream())
+    assert bool((ws[nbytes:] == 0xA5).all()), "fused backward wrote past its workspace"
+    return st, dx, dw
+
+
+def fused_backward_served(x_shape, k_hw, stride, padding, dtype, aligned16=True):
+    """Whether the one-kernel first pass of the fused backward serves this geometry."""
+    import ctypes
+    s = make_shape(x_shape, k_hw, stride, padding)
+    out = (ctypes.c_int * 24)()
+    return bool(_lib.lib.dwconv_b200_debug_plan(3, CODE[dtype], s, 1 if aligned16 else 0, out))
+
+
 def last_path():
     return _lib.lib.dwconv_b200_last_path()
 

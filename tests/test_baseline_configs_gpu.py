@@ -11,7 +11,7 @@ import torch
 
 import oracle
 from conftest import assert_close_fp, assert_dw_close
-from gpu_util import c_backward_filter, c_backward_input, c_forward, make_shape
+from gpu_util import c_backward, c_backward_filter, c_backward_input, c_forward, make_shape
 
 pytestmark = pytest.mark.gpu
 
@@ -57,6 +57,14 @@ def test_full_size_config(name):
     assert st == 0
     torch.cuda.synchronize()
     assert not torch.isnan(y).any() and not torch.isnan(dx).any() and not torch.isnan(dw).any()
+
+    # both gradients from one pass over dy: dx the same bits, dW the same sum to rounding
+    st, fdx, fdw = c_backward(x, dy, w, s, p)
+    assert st == 0
+    assert torch.equal(fdx, dx), f"{name}: fused dx differs"
+    assert not torch.isnan(fdw).any()
+    scale = dw.double().abs().max().item()
+    assert (fdw.double() - dw.double()).abs().max().item() <= (2e-2 if dt == torch.float16 else 2e-4) * scale
 
     # sampled planes: first, last, and a seeded random handful
     g = torch.Generator().manual_seed(1)

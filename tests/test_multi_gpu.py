@@ -20,12 +20,16 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, scenario="sharding"):
     try:
         for p in (ROOT, PKG):
             if p not in sys.path:
                 sys.path.insert(0, p)
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        # plain peer loads / stores only: no NVLink multicast objects in a test where a rank
+        # may stop taking part
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        if scenario != "sharding":
+            return _exchange_scenario(rank, world, q, scenario)
         import torch.distributed as dist
         import dwconv_b200
         import oracle
@@ -92,17 +96,105 @@ def _worker(rank, world, port, q):
         q.put((rank, f"{type(e).__name__}: {e}\n{traceback.format_exc()[-800:]}"))
 
 
-def test_two_gpu_batch_sharding_matches_single_gpu():
+def _exchange_scenario(rank, world, q, scenario):
+    """Two more uses of the in-kernel exchange on real GPUs.
+
+    "uneven":   six pipelined calls queued back to back while rank 1's host falls behind
+                (it sleeps between calls): every call must still deliver the sum of the call
+                before it, identical on both ranks, with no wait expiring.
+    "skipped":  rank 1 leaves out one call.  Rank 0's wait for the missing words is bounded:
+                after about two seconds its kernel gives up, the call returns, bit 2 of
+                dwconv_b200_device_status is set and the context stays usable.
+    """
+    import time
+    import torch.distributed as dist
+    import oracle
+    from dwconv_b200 import _lib
+    from dwconv_b200.dist import PeerFilterExchange, shard_batch
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    C, H, k, s, p, dt, N = 12, 14, 3, 1, 1, torch.float32, 8
+    g = torch.Generator().manual_seed(5)
+    ncalls = 6
+    xs, dys, truth = [], [], []
+    for i in range(ncalls):
+        x = torch.randn(N, C, H, H, generator=g)
+        dy = torch.randn(N, C, H, H, generator=g)
+        truth.append(oracle.backward_filter(x, dy, (k, k), s, p))
+        xs.append(shard_batch(x, world, rank).contiguous().to(dev))
+        dys.append(shard_batch(dy, world, rank).contiguous().to(dev))
+    ex = PeerFilterExchange(C, k, dt, dev)
+    if scenario == "uneven":
+        for rep in range(3):
+            prev = [torch.full((C, 1, k, k), float("nan"), device=dev) for _ in range(ncalls)]
+            torch.cuda.synchronize()
+            dist.barrier()
+            for i in range(ncalls):
+                if rank == 1 and i % 2 == 1:
+                    time.sleep(0.05)
+                ex.start(xs[i], dys[i], s, p, dw_prev=prev[i])
+            last = ex.finish()
+            torch.cuda.synchronize()
+            got = prev[1:] + [last]
+            for i, t in enumerate(got):
+                err = (t.double().cpu() - truth[i]).abs().max().item()
+                assert err <= 1e-4 * truth[i].abs().max().item(), (rep, i, err)
+                both = [torch.empty_like(t) for _ in range(world)]
+                dist.all_gather(both, t)
+                assert all(torch.equal(both[0], b) for b in both[1:]), "ranks disagree"
+            assert _lib.lib.dwconv_b200_device_status() == 0
+    else:
+        got = ex.backward_filter(xs[0], dys[0], s, p)
+        assert _lib.lib.dwconv_b200_device_status() == 0
+        err = (got.double().cpu() - truth[0]).abs().max().item()
+        assert err <= 1e-4 * truth[0].abs().max().item()
+        dist.barrier()
+        if rank == 0:
+            t0 = time.perf_counter()
+            ex.start(xs[1], dys[1], s, p)   # rank 1 never makes this call
+            ex.finish()                     # so its words never arrive
+            status = _lib.lib.dwconv_b200_device_status()   # synchronises
+            waited = time.perf_counter() - t0
+            assert status == 4, f"expected the exchange flag alone, got {status}"
+            assert 1.0 < waited < 30.0, waited
+            # the context is still usable: a plain call works and raises nothing
+            dw = torch.empty((C, 1, k, k), device=dev)
+            y = torch.empty_like(dys[0])
+            shape = _lib.Shape(xs[0].shape[0], C, H, H, k, k, s, s, p, p, H, H)
+            w = torch.randn(C, 1, k, k, device=dev)
+            _lib.check(_lib.lib.dwconv_b200_forward(xs[0].data_ptr(), w.data_ptr(), y.data_ptr(),
+                                                    _lib.F32, shape, None), "forward")
+            assert _lib.lib.dwconv_b200_device_status() == 0
+    torch.cuda.synchronize()
+    ex.close()   # collective: barrier inside
+    dist.destroy_process_group()
+    q.put((rank, "ok"))
+
+
+def _run_two_ranks(scenario, timeout=300):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 CUDA devices")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, scenario)) for r in range(2)]
     for p in procs:
         p.start()
-    out = dict(q.get(timeout=300) for _ in range(2))
+    out = dict(q.get(timeout=timeout) for _ in range(2))
     for p in procs:
         p.join(timeout=60)
     assert out == {0: "ok", 1: "ok"}, out
+
+
+def test_two_gpu_batch_sharding_matches_single_gpu():
+    _run_two_ranks("sharding")
+
+
+def test_two_gpu_exchange_with_one_rank_falling_behind():
+    _run_two_ranks("uneven")
+
+
+def test_two_gpu_exchange_wait_is_bounded_when_a_rank_skips_a_call():
+    _run_two_ranks("skipped")

@@ -7,8 +7,8 @@ import torch.nn.functional as F
 import oracle
 from conftest import NP_DT, assert_close_fp, assert_dw_close, case_names, golden
 from dwconv_b200 import _lib
-from gpu_util import (c_backward_filter, c_backward_input, c_forward, forced_path, last_path,
-                      seeded)
+from gpu_util import (c_backward, c_backward_filter, c_backward_input, c_forward, forced_path,
+                      fused_backward_served, last_path, seeded)
 
 pytestmark = pytest.mark.gpu
 
@@ -29,6 +29,15 @@ def _check_three_ops(x, w, dy, stride, padding, dt, path, what, exact=True):
         out["dx"] = (st, dx, last_path())
         st, dw = c_backward_filter(x, dy, (kh, kw), stride, padding)
         out["dw"] = (st, dw, last_path())
+        # both gradients from one pass over dy: dx is the same sum in the same order, dW the
+        # same pairs in another order
+        stf, fdx, fdw = c_backward(x, dy, w, stride, padding)
+        if out["dx"][0] == 0 and out["dw"][0] == 0:
+            assert stf == 0, f"{what}/fused backward: status {stf}"
+            assert torch.equal(fdx, dx), f"{what}: fused dx differs from backward-input's"
+            assert not torch.isnan(fdw).any(), f"{what}: fused dW not fully written"
+            assert_dw_close(fdw, oracle.backward_filter(x, dy, (kh, kw), stride, padding), dt,
+                            f"{what}/fused dw")
     assert _lib.lib.dwconv_b200_device_status() == 0, f"{what}: a bounded wait expired in a kernel"
     res = {}
     for key, (st, t, used) in out.items():
@@ -340,6 +349,142 @@ def test_exchange_entry_point_with_one_rank_equals_plain(shape, k, s, p, dtype):
     assert torch.equal(earlier, want)
     st2, want2 = c_backward_filter(x * 2, dy, (k, k), s, p)
     assert st2 == 0 and torch.equal(later, want2)
+    assert _lib.lib.dwconv_b200_device_status() == 0
+    ex.close()
+
+
+FUSED_CASES = [
+    # shape, k, s: every (K, S, VI/VO) variant of the fused kernel, planes that share a tile,
+    # row-tiled planes, channel counts that do not divide the group size, ragged batches
+    ((5, 19, 14, 14), 3, 1), ((3, 7, 7, 7), 3, 1), ((2, 5, 56, 56), 3, 1), ((1, 3, 112, 112), 3, 1),
+    ((2, 6, 32, 32), 3, 1), ((3, 4, 31, 31), 3, 1), ((2, 3, 128, 128), 3, 1),
+    ((2, 6, 112, 112), 3, 2), ((3, 10, 28, 28), 3, 2), ((2, 5, 14, 14), 3, 2),
+    ((3, 9, 14, 14), 5, 1), ((2, 4, 32, 32), 5, 1), ((1, 3, 64, 64), 5, 1),
+    ((2, 6, 56, 56), 5, 2), ((3, 7, 14, 14), 5, 2),
+    ((2, 5, 28, 28), 7, 1), ((1, 3, 56, 56), 7, 1), ((2, 4, 32, 32), 7, 1), ((2, 3, 28, 28), 7, 2),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("shape,k,s", FUSED_CASES)
+def test_fused_backward_matches_the_two_operators(shape, k, s, dtype):
+    """dwconv_b200_backward (one pass over dy) against backward-input (bit for bit), the
+    sequential-order oracle, and the fp64 filter gradient; these geometries must be served by
+    the one-kernel first pass."""
+    p = k // 2
+    assert fused_backward_served(shape, (k, k), s, p, dtype), "expected the fused kernel to serve this"
+    x, w, dy = seeded(shape, (k, k), s, p, dtype, seed=7)
+    with forced_path(_lib.PATH_ROWS):
+        st, dx, dw = c_backward(x, dy, w, s, p)
+        assert st == 0 and last_path() == _lib.PATH_ROWS
+        st2, dx2 = c_backward_input(dy, w, shape[2:], s, p)
+    assert st2 == 0
+    assert _lib.lib.dwconv_b200_device_status() == 0
+    assert not torch.isnan(dx).any() and not torch.isnan(dw).any()
+    assert torch.equal(dx, dx2)
+    assert torch.equal(dx.cpu(), oracle.backward_input_seq(dy, w, shape[2:], s, p))
+    assert_dw_close(dw, oracle.backward_filter(x, dy, (k, k), s, p), dtype, "fused dW")
+    # deterministic: the same bits on a second run
+    st, dx3, dw3 = c_backward(x, dy, w, s, p)
+    assert st == 0 and torch.equal(dw3, dw) and torch.equal(dx3, dx)
+
+
+def test_fused_backward_accumulate_and_fallback():
+    """The accumulate form adds call after call into an fp32 gradient; a geometry outside the
+    tiled kernels (rectangular filter, mixed strides) still gives both gradients."""
+    shape, k, s, p = (6, 10, 14, 14), 3, 1, 1
+    x, w, dy = seeded(shape, (k, k), s, p, torch.float16, seed=3)
+    sh = _lib.Shape(shape[0] // 2, shape[1], 14, 14, k, k, s, s, p, p, 14, 14)
+    nws = int(_lib.lib.dwconv_b200_backward_filter_workspace_bytes(_lib.F16, sh))
+    ws = torch.empty(nws, dtype=torch.uint8, device="cuda")
+    acc = torch.full((shape[1], 1, k, k), float("nan"), dtype=torch.float32, device="cuda")
+    dx = torch.full_like(x, float("nan"))
+    st0 = torch.cuda.current_stream().cuda_stream
+    for i, (a, b) in enumerate(((0, 3), (3, 6))):
+        xs, dys = x[a:b].contiguous(), dy[a:b].contiguous()
+        dxs = torch.empty_like(xs)
+        st = _lib.lib.dwconv_b200_backward_accumulate(xs.data_ptr(), dys.data_ptr(), w.data_ptr(),
+                                                      dxs.data_ptr(), acc.data_ptr(), i, ws.data_ptr(),
+                                                      nws, _lib.F16, sh, st0)
+        assert st == 0
+        dx[a:b] = dxs
+    assert torch.equal(dx.cpu(), oracle.backward_input_seq(dy, w, (14, 14), s, p))
+    truth = oracle.backward_filter(x, dy, (k, k), s, p)
+    assert (acc.double().cpu() - truth).abs().max().item() <= 1e-4 * truth.abs().max().item()
+    # filter gradient only (dx and w null)
+    acc2 = torch.zeros_like(acc)
+    st = _lib.lib.dwconv_b200_backward_accumulate(x[:3].contiguous().data_ptr(), dy[:3].contiguous().data_ptr(),
+                                                  None, None, acc2.data_ptr(), 0, ws.data_ptr(), nws,
+                                                  _lib.F16, sh, st0)
+    assert st == 0
+    t3 = oracle.backward_filter(x[:3], dy[:3], (k, k), s, p)
+    assert (acc2.double().cpu() - t3).abs().max().item() <= 1e-4 * t3.abs().max().item()
+    # outside the tiled kernels: served by the two general kernels one after the other
+    shape, kk, ss, pp = (2, 3, 12, 12), (3, 5), (1, 2), (1, 2)
+    assert not fused_backward_served(shape, kk, ss, pp, torch.float32)
+    x, w, dy = seeded(shape, kk, ss, pp, torch.float32, seed=4)
+    st, dx, dw = c_backward(x, dy, w, ss, pp)
+    assert st == 0
+    assert torch.equal(dx.cpu(), oracle.backward_input_seq(dy, w, shape[2:], ss, pp))
+    assert_dw_close(dw, oracle.backward_filter(x, dy, kk, ss, pp), torch.float32, "fallback dW")
+
+
+@pytest.mark.parametrize("shape,k,s,p,dtype", [
+    ((16, 64, 14, 14), 3, 1, 1, torch.float32),
+    ((4, 24, 28, 28), 5, 2, 2, torch.float32),
+    ((2, 8, 28, 28), 7, 1, 3, torch.float16),
+])
+def test_exchange_calls_back_to_back(shape, k, s, p, dtype):
+    """World size 1.  Eight exchange calls on ONE object, queued one behind the other with
+    nothing else between them: every exchange kernel can become resident while the previous
+    one still runs, so it must take its call number from what it reads AFTER waiting for its
+    predecessors.  Each call's ``dw_prev`` must be the plain entry point's gradient of the
+    previous call's input, bit for bit; then the same sequence replayed from a CUDA graph."""
+    from dwconv_b200.dist import PeerFilterExchange
+    ncalls = 8
+    code = _lib.F16 if dtype == torch.float16 else _lib.F32
+    xs, dys, want = [], [], []
+    for i in range(ncalls):
+        x, w, dy = seeded(shape, (k, k), s, p, dtype, seed=100 + i)
+        st, dw = c_backward_filter(x, dy, (k, k), s, p)
+        assert st == 0
+        xs.append(x), dys.append(dy), want.append(dw)
+    Ho, Wo = dys[0].shape[2:]
+    shp = _lib.Shape(shape[0], shape[1], shape[2], shape[3], k, k, s, s, p, p, Ho, Wo)
+    nws = int(_lib.lib.dwconv_b200_backward_filter_workspace_bytes(code, shp))
+    ws = torch.empty(nws, dtype=torch.uint8, device="cuda")
+    ex = PeerFilterExchange(shape[1], k, dtype, xs[0].device)
+    prev = [torch.full_like(want[0], float("nan")) for _ in range(ncalls)]
+
+    def sequence(st):
+        for i in range(ncalls):
+            ex.launch(xs[i].data_ptr(), dys[i].data_ptr(), prev[i].data_ptr(), ws.data_ptr(), nws,
+                      shp, st)
+
+    torch.cuda.synchronize()
+    sequence(torch.cuda.current_stream().cuda_stream)
+    last = ex.finish()
+    torch.cuda.synchronize()
+    assert torch.isnan(prev[0]).all()  # the first call ever has no predecessor
+    for i in range(1, ncalls):
+        assert torch.equal(prev[i], want[i - 1]), f"call {i} delivered the wrong call's sum"
+    assert torch.equal(last, want[-1])
+    # the same eight calls as one CUDA graph, replayed three times: the first call of a replay
+    # delivers the last call of the replay before it
+    side = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        sequence(torch.cuda.current_stream().cuda_stream)
+    for rep in range(3):
+        for t in prev:
+            t.fill_(float("nan"))
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(prev[0], want[-1]), f"replay {rep}: first call"
+        for i in range(1, ncalls):
+            assert torch.equal(prev[i], want[i - 1]), f"replay {rep}: call {i}"
+    assert torch.equal(ex.finish(), want[-1])
     assert _lib.lib.dwconv_b200_device_status() == 0
     ex.close()
 
