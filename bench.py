@@ -310,6 +310,17 @@ class Bench:
         for li in reversed(range(len(bufs))):
             ex[li].finish(bufs[li]["dw"], stream=st)
 
+    def step_sync_kernel(self, bufs, st):
+        """N > 1.  The whole sum inside the kernel that finishes the gradient: after sending its
+        sums it waits for the other ranks' and writes the world sum of THIS step to ``dw``."""
+        for b in bufs:
+            self.forward(b, st)
+        for li in reversed(range(len(bufs))):
+            b = bufs[li]
+            self.exchanges[li].launch_allreduce(b["x"].data_ptr(), b["dy"].data_ptr(), b["w"].data_ptr(),
+                                                b["dx"].data_ptr(), b["dw"].data_ptr(), b["ws"].data_ptr(),
+                                                b["nws"], b["shape"], st)
+
     def step_pipelined(self, bufs, prev, st):
         """N > 1, for comparison: the sum of a step's dW is completed by the NEXT step's
         exchange call (delayed by one step; no finish kernel)."""
@@ -331,13 +342,16 @@ class Bench:
             self.step_sync(bufs, st, True)
         elif mode == "sync_split":
             self.step_sync(bufs, st, False)
+        elif mode == "sync_kernel":
+            self.step_sync_kernel(bufs, st)
         elif mode == "pipelined":
             self.step_pipelined(bufs, self.sets[(i - 1) % self.n_sets], st)
         else:
             raise ValueError(mode)
 
     def launches_per_step(self, mode):
-        per_layer = {"local": 3, "local_unfused": 4, "sync": 4, "sync_split": 5, "pipelined": 4}[mode]
+        per_layer = {"local": 3, "local_unfused": 4, "sync": 4, "sync_split": 5, "sync_kernel": 3,
+                     "pipelined": 4}[mode]
         return per_layer * len(self.layers)
 
     def make_graphs(self, mode, stream):
@@ -438,7 +452,7 @@ def gpu_arm(args, layers):
     calibration = {}
     candidates = [head_mode]
     if world > 1 and not args.unfused:
-        candidates.append("sync_split")
+        candidates.append("sync_kernel")
     best = None
     for mode in candidates:
         for use_graph in ((True, False) if args.launch == "auto" else
@@ -482,11 +496,13 @@ def gpu_arm(args, layers):
                     "against": "NCCL all_reduce(SUM) of every rank's local dwconv_b200_backward_filter"}
         # the other ways to run the step, for the record
         variants = {}
-        for mode in ("local", "sync", "sync_split", "pipelined"):
+        for mode in ("local", "sync", "sync_kernel", "sync_split", "pipelined"):
             variants[mode + "_ms"] = round(wb.time_steps(mode, 200, 10, stream, False, barrier), 5)
         variants["note"] = ("eager launches, 200 steps, max over ranks.  local: no exchange at all; "
                             "sync: fused backward + in-kernel exchange + finish per step (dW of the "
-                            "step complete at its end); sync_split: filter gradient + exchange first, "
+                            "step complete at its end); sync_kernel: fused backward whose second pass "
+                            "also waits for the other ranks' sums (the whole all-reduce in that "
+                            "kernel); sync_split: filter gradient + exchange first, "
                             "backward-input hides the stores' flight, then finish; pipelined: dW "
                             "completed by the next step's exchange (one step late)")
 
@@ -580,8 +596,10 @@ def gpu_arm(args, layers):
         def timed_workload(name, batch, steps):
             lay = [[batch] + list(l[1:]) for l in WORKLOADS[name]]
             w2 = Bench(lay, dev, rank, world, exchange=True, min_sets=2, max_sets=4)
-            mode = "local" if world == 1 else "sync"
-            ms = w2.time_steps(mode, steps, 5, stream, True, barrier)
+            if world == 1:
+                ms = w2.time_steps("local", steps, 5, stream, True, barrier)
+            else:  # the faster of the two synchronous forms
+                ms = min(w2.time_steps(m, steps, 5, stream, True, barrier) for m in ("sync", "sync_kernel"))
             out = {"per_gpu_batch": batch, "ms_per_step": round(ms, 5),
                    "images_per_s": round(batch * world / (ms * 1e-3), 1),
                    "algorithmic_gbps": round(step_bytes(lay) * world / (ms * 1e-3) / 1e9, 1),
@@ -673,7 +691,7 @@ def gpu_arm(args, layers):
         bx, by, bw = (sum(v) for v in zip(*map(layer_bytes, layers)))
         kernel_bytes = {"forward": bx + by + bw, "backward_input": bx + by + bw,
                         "backward_filter": bx + by + bw, "backward_fused": 2 * bx + by + 2 * bw}
-        in_step = (("forward", "backward_fused") if head_mode in ("local", "sync") else
+        in_step = (("forward", "backward_fused") if head_mode in ("local", "sync", "sync_kernel") else
                    ("forward", "backward_input", "backward_filter"))
         dom = max(in_step, key=lambda k: op_ms[k])
         achieved = kernel_bytes[dom] / (op_ms[dom] * 1e-3) / 1e9
@@ -703,6 +721,9 @@ def gpu_arm(args, layers):
                          "local_unfused": "forward, backward-input, backward-filter",
                          "sync": "forward, fused backward whose second pass sends dW to all ranks, "
                                  "exchange_finish (dW of this step complete at its end)",
+                         "sync_kernel": "forward, fused backward whose second pass sends dW to all ranks "
+                                        "and adds the ranks' sums (all-reduce inside the kernel; dW of "
+                                        "this step complete at its end)",
                          "sync_split": "forward, backward-filter whose second pass sends dW to all "
                                        "ranks, backward-input, exchange_finish (dW of this step "
                                        "complete at its end)"}[head_mode],
@@ -750,6 +771,64 @@ def gpu_arm(args, layers):
                          + json.dumps(dw_check))
 
 
+def time_api(layers, reps):
+    """CUDA-event timing of the public Python API (``depthwise_conv2d`` forward, and forward +
+    ``backward``) on arbitrary layers, the way ``oracle/ref_cuda.py --time`` times the reference's
+    CUDA route: rotating buffer sets larger than L2, 3 warm-up calls.  Prints one JSON object."""
+    import torch
+    import dwconv_b200
+    from dwconv_b200 import _lib
+    dts = {"f32": torch.float32, "f16": torch.float16}
+    res = []
+    for layer in layers:
+        if len(layer) == 8:
+            N, C, H, W, k, s, p, dt = layer
+        else:
+            N, C, H, k, s, p, dt = layer
+            W = H
+        ho, wo = out_hw(H, k, s, p), out_hw(W, k, s, p)
+        per_set = 2 * N * C * (H * W + ho * wo) * ESIZE[dt]
+        n_sets = max(2, min(8, int(2 * L2_BYTES // per_set) + 2))
+        sets = []
+        for si in range(n_sets):
+            g = torch.Generator(device="cuda").manual_seed(si)
+            x = torch.randn((N, C, H, W), generator=g, device="cuda").to(dts[dt]).requires_grad_(True)
+            w = (torch.randn((C, 1, k, k), generator=g, device="cuda") / k).to(dts[dt]).requires_grad_(True)
+            dy = torch.randn((N, C, ho, wo), generator=g, device="cuda").to(dts[dt])
+            sets.append((x, w, dy))
+
+        def fwd(i):
+            x, w, dy = sets[i % n_sets]
+            with torch.no_grad():
+                dwconv_b200.depthwise_conv2d(x, w, None, s, p)
+
+        def fwd_bwd(i):
+            x, w, dy = sets[i % n_sets]
+            x.grad = None
+            w.grad = None
+            dwconv_b200.depthwise_conv2d(x, w, None, s, p).backward(dy)
+
+        times = {}
+        for name, fn in (("forward", fwd), ("forward_backward", fwd_bwd)):
+            for i in range(3):
+                fn(i)
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for i in range(reps):
+                fn(i)
+            z.record()
+            torch.cuda.synchronize()
+            times[name] = a.elapsed_time(z) / reps
+        res.append({"layer": list(layer), "forward_ms": round(times["forward"], 5),
+                    "forward_backward_ms": round(times["forward_backward"], 5),
+                    "kernel_family": {1: "direct", 2: "rows"}.get(_lib.lib.dwconv_b200_last_path()),
+                    "buffer_sets": n_sets})
+        del sets
+        torch.cuda.empty_cache()
+    print(json.dumps({"impl": "dwconv_b200 public API (depthwise_conv2d + autograd)", "layers": res}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -767,7 +846,14 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the stack and strong-scaling legs (profiling)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--time-api", metavar="JSON",
+                    help="instead of the benchmark: time the public Python API on a JSON list of "
+                         "[N, C, H, k, stride, pad, dtype] or [N, C, H, W, k, stride, pad, dtype]")
+    ap.add_argument("--reps", type=int, default=50)
     args = ap.parse_args()
+    if args.time_api:
+        time_api(json.loads(args.time_api), args.reps)
+        return
     layers = [list(l) for l in WORKLOADS[args.workload]]
     if args.impl == "reference":
         reference_arm(args, layers)

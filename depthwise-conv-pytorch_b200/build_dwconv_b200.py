@@ -54,15 +54,15 @@ def _recorded_deps(dep_file):
     return deps if all(os.path.exists(d) for d in deps) else None
 
 
-def _compile_one(nvcc, src, verbose):
-    obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
+def _compile_one(nvcc, src, verbose, defines=(), obj_dir=None):
+    obj = os.path.join(obj_dir or OBJ_DIR, os.path.basename(src)[:-3] + ".o")
     dep_file = obj[:-2] + ".d"
     deps = _recorded_deps(dep_file) if os.path.exists(obj) else None
     if deps is not None:
         newest = max(os.path.getmtime(f) for f in [src] + deps)
         if os.path.getmtime(obj) >= newest:
             return obj, ""
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
+    cmd = [nvcc] + NVCC_FLAGS + [f"-D{d}" for d in defines] + (["-Xptxas", "-v"] if verbose else []) + [
         "-I", INCLUDE, "-I", CSRC, "-MD", "-MF", dep_file, "-c", "-o", obj, src]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
@@ -70,36 +70,51 @@ def _compile_one(nvcc, src, verbose):
     return obj, res.stdout + res.stderr
 
 
-def build_library(force=False, verbose=False):
+def build_library(force=False, verbose=False, defines=(), out=None):
     """Build the library if a source is newer than it; returns its path.
 
     Each ``.cu`` is compiled to an object in parallel (they are independent translation
     units), then linked into one shared library with the static CUDA runtime.
+
+    ``defines`` / ``out``: a second library with preprocessor symbols set (for instance
+    ``DWCONV_B200_TUNING``, which compiles the planner's environment-variable overrides in),
+    written to ``out`` with its objects beside it; the shipped library is built without any.
     """
+    if out is not None:
+        return _build(True, verbose, tuple(defines), os.path.abspath(out))
     if not force and not is_stale():
         return LIB_PATH
+    return _build(force, verbose, (), LIB_PATH)
+
+
+def _build(force, verbose, defines, lib_path):
     from concurrent.futures import ThreadPoolExecutor
     nvcc = os.environ.get("NVCC") or os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"),
                                                   "bin", "nvcc")
-    os.makedirs(LIB_DIR, exist_ok=True)
-    os.makedirs(OBJ_DIR, exist_ok=True)
-    if force:
-        for f in glob.glob(os.path.join(OBJ_DIR, "*.o")):
+    obj_dir = OBJ_DIR if lib_path == LIB_PATH else lib_path + ".obj"
+    os.makedirs(os.path.dirname(lib_path), exist_ok=True)
+    os.makedirs(obj_dir, exist_ok=True)
+    if force and lib_path == LIB_PATH:
+        for f in glob.glob(os.path.join(obj_dir, "*.o")):
             os.remove(f)
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
-        results = list(pool.map(lambda src: _compile_one(nvcc, src, verbose), _sources()))
+        results = list(pool.map(lambda src: _compile_one(nvcc, src, verbose, defines, obj_dir),
+                                _sources()))
     if verbose:
         sys.stderr.write("".join(log for _, log in results))
-    tmp = LIB_PATH + ".tmp"
+    tmp = lib_path + ".tmp"
     cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
            "-o", tmp] + [obj for obj, _ in results]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
         raise RuntimeError("nvcc failed linking libdwconv_b200.so")
-    os.replace(tmp, LIB_PATH)
-    return LIB_PATH
+    os.replace(tmp, lib_path)
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    _defs = [a[2:] for a in sys.argv[1:] if a.startswith("-D")]
+    _out = next((a[6:] for a in sys.argv[1:] if a.startswith("--out=")), None)
+    print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
+                        defines=_defs, out=_out))

@@ -106,13 +106,20 @@ int try_rows_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<
 
 template <typename T>
 int forward_t(const void *x, const void *w, void *y, const Shape &s, cudaStream_t st, int forced) {
-  if (forced != DWCONV_B200_PATH_DIRECT) {
+  if (forced == DWCONV_B200_PATH_AUTO || forced == DWCONV_B200_PATH_ROWS) {
     int r = try_rows_forward<T>((const T *)x, (const T *)w, (T *)y, s, st);
     if (r == ROWS_SERVED) {
       t_last_path = DWCONV_B200_PATH_ROWS;
       return launch_status();
     }
     if (forced == DWCONV_B200_PATH_ROWS) return DWCONV_B200_UNSUPPORTED_SHAPE;
+  }
+  if (forced == DWCONV_B200_PATH_AUTO || forced == DWCONV_B200_PATH_TILES) {
+    if (tiles_forward<T>((const T *)x, (const T *)w, (T *)y, s, st) == ROWS_SERVED) {
+      t_last_path = DWCONV_B200_PATH_TILES;
+      return launch_status();
+    }
+    if (forced == DWCONV_B200_PATH_TILES) return DWCONV_B200_UNSUPPORTED_SHAPE;
   }
   const long long total = (long long)s.N * s.C * s.Ho * s.Wo;
   direct_forward_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T *)x, (const T *)w,
@@ -124,13 +131,20 @@ int forward_t(const void *x, const void *w, void *y, const Shape &s, cudaStream_
 template <typename T>
 int backward_input_t(const void *dy, const void *w, void *dx, const Shape &s, cudaStream_t st,
                      int forced) {
-  if (forced != DWCONV_B200_PATH_DIRECT) {
+  if (forced == DWCONV_B200_PATH_AUTO || forced == DWCONV_B200_PATH_ROWS) {
     int r = try_rows_backward_input<T>((const T *)dy, (const T *)w, (T *)dx, s, st);
     if (r == ROWS_SERVED) {
       t_last_path = DWCONV_B200_PATH_ROWS;
       return launch_status();
     }
     if (forced == DWCONV_B200_PATH_ROWS) return DWCONV_B200_UNSUPPORTED_SHAPE;
+  }
+  if (forced == DWCONV_B200_PATH_AUTO || forced == DWCONV_B200_PATH_TILES) {
+    if (tiles_backward_input<T>((const T *)dy, (const T *)w, (T *)dx, s, st) == ROWS_SERVED) {
+      t_last_path = DWCONV_B200_PATH_TILES;
+      return launch_status();
+    }
+    if (forced == DWCONV_B200_PATH_TILES) return DWCONV_B200_UNSUPPORTED_SHAPE;
   }
   const long long total = (long long)s.N * s.C * s.H * s.W;
   direct_backward_input_kernel<T><<<grid_for(total, 256), 256, 0, st>>>(
@@ -159,7 +173,7 @@ int filter_first_pass_t(const void *x, const void *dy, void *ws, size_t ws_bytes
   using A = typename Elem<T>::acc_t;
   if (ws_bytes < filter_workspace_t<T>(s)) return DWCONV_B200_WORKSPACE_TOO_SMALL;
   int S = 0;
-  if (forced != DWCONV_B200_PATH_DIRECT) {
+  if (forced == DWCONV_B200_PATH_AUTO || forced == DWCONV_B200_PATH_ROWS) {
     int r = try_rows_backward_filter<T>((const T *)x, (const T *)dy, (A *)ws, s, st, &S);
     if (r == ROWS_SERVED) {
       t_last_path = DWCONV_B200_PATH_ROWS;
@@ -168,6 +182,17 @@ int filter_first_pass_t(const void *x, const void *dy, void *ws, size_t ws_bytes
     } else {
       if (forced == DWCONV_B200_PATH_ROWS) return DWCONV_B200_UNSUPPORTED_SHAPE;
       S = 0;
+    }
+  }
+  if (S == 0 && (forced == DWCONV_B200_PATH_AUTO || forced == DWCONV_B200_PATH_TILES)) {
+    const int slices = direct_filter_slices(s);  // the same batch split as the kernels below
+    if (tiles_backward_filter<T>((const T *)x, (const T *)dy, (A *)ws, s, slices, st) == ROWS_SERVED) {
+      S = slices;
+      t_last_path = DWCONV_B200_PATH_TILES;
+      int e = launch_status();
+      if (e != DWCONV_B200_OK) return e;
+    } else if (forced == DWCONV_B200_PATH_TILES) {
+      return DWCONV_B200_UNSUPPORTED_SHAPE;
     }
   }
   if (S == 0) {
@@ -217,7 +242,7 @@ int backward_first_pass_t(const void *x, const void *dy, const void *w, void *dx
                           size_t ws_bytes, const Shape &s, cudaStream_t st, int forced, int *slices) {
   using A = typename Elem<T>::acc_t;
   if (ws_bytes < filter_workspace_t<T>(s)) return DWCONV_B200_WORKSPACE_TOO_SMALL;
-  if (forced != DWCONV_B200_PATH_DIRECT) {
+  if (forced == DWCONV_B200_PATH_AUTO || forced == DWCONV_B200_PATH_ROWS) {
     int S = 0;
     int r = try_rows_backward<T>((const T *)x, (const T *)dy, (const T *)w, (T *)dx, (A *)ws, s, st, &S);
     if (r == ROWS_SERVED) {
@@ -292,7 +317,7 @@ int exchange_finish_t(void *dw, dwconv_b200_exchange *ex, cudaStream_t st) {
 template <typename T>
 int backward_filter_exchange_t(const void *x, const void *dy, const void *w, void *dx, void *dw,
                                void *ws, size_t ws_bytes, const Shape &s, dwconv_b200_exchange *ex,
-                               cudaStream_t st, int forced) {
+                               cudaStream_t st, int forced, int same_call) {
   using A = typename Elem<T>::acc_t;
   const int kk = s.kh * s.kw;
   const int blocks = finalize_blocks(s.C, kk);
@@ -307,7 +332,7 @@ int backward_filter_exchange_t(const void *x, const void *dy, const void *w, voi
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t cfg = finalize_config(blocks, st, attr);
   (void)cudaLaunchKernelEx(&cfg, backward_filter_finalize_exchange_kernel<T>, (const A *)ws, (T *)dw,
-                           s.C, kk, S, px, ex->error_flag);
+                           s.C, kk, S, px, ex->error_flag, same_call);
   return launch_status();
 }
 
@@ -342,7 +367,7 @@ const char *dwconv_b200_status_string(int status) {
 int dwconv_b200_last_cuda_error(void) { return t_last_cuda_error; }
 
 int dwconv_b200_set_path(int path) {
-  if (path < DWCONV_B200_PATH_AUTO || path > DWCONV_B200_PATH_ROWS) return -1;
+  if (path < DWCONV_B200_PATH_AUTO || path > DWCONV_B200_PATH_TILES) return -1;
   return g_forced_path.exchange(path);
 }
 
@@ -466,7 +491,8 @@ int dwconv_b200_exchange_finish(void *dw, dwconv_b200_exchange *ex, void *stream
 
 static int exchange_call(const void *x, const void *dy, const void *w, void *dx, void *dw_prev,
                          void *workspace, size_t workspace_bytes, int dtype,
-                         const dwconv_b200_shape *shape, dwconv_b200_exchange *ex, void *stream) {
+                         const dwconv_b200_shape *shape, dwconv_b200_exchange *ex, void *stream,
+                         int same_call) {
   const void *dw = dw_prev != nullptr ? dw_prev : x;  // dw_prev is optional
   int e = check_ptrs(dtype, x, dy, dw);
   if (e) return e;
@@ -482,13 +508,13 @@ static int exchange_call(const void *x, const void *dy, const void *w, void *dx,
   const int forced = g_forced_path.load();
   switch (dtype) {
     case DWCONV_B200_F32:
-      return backward_filter_exchange_t<float>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+      return backward_filter_exchange_t<float>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced, same_call);
     case DWCONV_B200_F16:
-      return backward_filter_exchange_t<__half>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+      return backward_filter_exchange_t<__half>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced, same_call);
     case DWCONV_B200_BF16:
-      return backward_filter_exchange_t<__nv_bfloat16>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+      return backward_filter_exchange_t<__nv_bfloat16>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced, same_call);
     default:
-      return backward_filter_exchange_t<double>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced);
+      return backward_filter_exchange_t<double>(x, dy, w, dx, dw_prev, workspace, workspace_bytes, *shape, ex, st, forced, same_call);
   }
 }
 
@@ -497,7 +523,7 @@ int dwconv_b200_backward_filter_exchange(const void *x, const void *dy, void *dw
                                          const dwconv_b200_shape *shape, dwconv_b200_exchange *ex,
                                          void *stream) {
   return exchange_call(x, dy, nullptr, nullptr, dw_prev, workspace, workspace_bytes, dtype, shape, ex,
-                       stream);
+                       stream, 0);
 }
 
 int dwconv_b200_backward_exchange(const void *x, const void *dy, const void *w, void *dx, void *dw_prev,
@@ -505,7 +531,23 @@ int dwconv_b200_backward_exchange(const void *x, const void *dy, const void *w, 
                                   const dwconv_b200_shape *shape, dwconv_b200_exchange *ex,
                                   void *stream) {
   if (w == nullptr || dx == nullptr) return DWCONV_B200_BAD_ARGUMENT;
-  return exchange_call(x, dy, w, dx, dw_prev, workspace, workspace_bytes, dtype, shape, ex, stream);
+  return exchange_call(x, dy, w, dx, dw_prev, workspace, workspace_bytes, dtype, shape, ex, stream, 0);
+}
+
+int dwconv_b200_backward_filter_allreduce(const void *x, const void *dy, void *dw, void *workspace,
+                                          size_t workspace_bytes, int dtype,
+                                          const dwconv_b200_shape *shape, dwconv_b200_exchange *ex,
+                                          void *stream) {
+  if (dw == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  return exchange_call(x, dy, nullptr, nullptr, dw, workspace, workspace_bytes, dtype, shape, ex, stream, 1);
+}
+
+int dwconv_b200_backward_allreduce(const void *x, const void *dy, const void *w, void *dx, void *dw,
+                                   void *workspace, size_t workspace_bytes, int dtype,
+                                   const dwconv_b200_shape *shape, dwconv_b200_exchange *ex,
+                                   void *stream) {
+  if (w == nullptr || dx == nullptr || dw == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  return exchange_call(x, dy, w, dx, dw, workspace, workspace_bytes, dtype, shape, ex, stream, 1);
 }
 
 int dwconv_b200_copy_async(void *dst, const void *src, size_t bytes, void *stream) {

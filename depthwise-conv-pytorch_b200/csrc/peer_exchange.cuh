@@ -157,16 +157,27 @@ __device__ __forceinline__ bool exchange_receive(const ExchangePeers &px, size_t
   return true;
 }
 
-// dw_prev: where the PREVIOUS call's world sum goes (may be null: not wanted).
+// Two forms, chosen per call:
+//   same_call == 0 (pipelined): dw_out receives the PREVIOUS call's world sum (may be null: not
+//     wanted); this call's sum is completed by the next call or by exchange_finish_kernel, after
+//     whatever the stream runs in between has hidden the stores' flight.
+//   same_call != 0 (all-reduce inside the kernel): after sending, the kernel waits for the other
+//     ranks' words of THIS call and writes this call's world sum to dw_out.  For a step with
+//     nothing left to run behind the gradient: one kernel instead of a send plus a finish, and
+//     the wait starts while the stores are still in flight.
+// Slot safety in both forms and any mix of them: a CTA reads call c-3's words (whose slot call c
+// re-uses) before it sends call c-2, and it sends call c only after it has every rank's call
+// c-2 or c-1 (pipelined: it receives c-1 before sending c; all-reduce: it received c-1 inside
+// call c-1), so every rank is done with the slot by then.
 // (Measured alternative, not kept: staging the sums and sending them from a small kernel on a
 // second stream, to hide the time the peer stores take to be acknowledged, was slower on two
 // GPUs: 80.8 against 78.3 us per step.)
 template <typename T>
 __global__ void __launch_bounds__(FINALIZE_THREADS)
 backward_filter_finalize_exchange_kernel(const typename Elem<T>::acc_t *__restrict__ partial,
-                                         T *__restrict__ dw_prev, const int C, const int kk,
+                                         T *__restrict__ dw_out, const int C, const int kk,
                                          const int S, const ExchangePeers px,
-                                         int *__restrict__ error_flag) {
+                                         int *__restrict__ error_flag, const int same_call) {
   using A = typename Elem<T>::acc_t;
   __shared__ A part_sum[FINALIZE_PARTS][FINALIZE_OUTPUTS];
   const int o = threadIdx.x & (FINALIZE_OUTPUTS - 1);
@@ -188,7 +199,7 @@ backward_filter_finalize_exchange_kernel(const typename Elem<T>::acc_t *__restri
   unsigned *my_calls = reinterpret_cast<unsigned *>(px.buf[px.rank]);
   unsigned long long words[EXCHANGE_MAX_WORLD][ExchangeWords<A>::W];
   unsigned guess = 0;
-  if (part == 0) {
+  if (part == 0 && !same_call) {
     guess = ld_counter(my_calls + b);
     if (live && guess > 0u) exchange_preload<A>(px, header, n, idx, guess, words);
   }
@@ -197,21 +208,30 @@ backward_filter_finalize_exchange_kernel(const typename Elem<T>::acc_t *__restri
   unsigned call = 0;
   if (part == 0) {
     call = ld_counter(my_calls + b) + 1u;  // the same on every rank: all ranks make the same calls
-    if (live && call > 1u && call - 1u != guess) exchange_preload<A>(px, header, n, idx, call - 1u, words);
+    if (!same_call && live && call > 1u && call - 1u != guess)
+      exchange_preload<A>(px, header, n, idx, call - 1u, words);
   }
   const A total = finalize_sum<A>(partial, idx, live, kk, S, part_sum);
   if (part != 0) return;  // the exchange is warp 0's job: lane o owns output idx
 
   bool ok = true;
   if (live) {
-    // receive before sending: a peer that sees this call's words knows that this rank is done
-    // reading the previous call's, which is what makes three slots enough (see the top)
-    if (call > 1u) {
+    if (!same_call) {
+      // receive before sending: a peer that sees this call's words knows that this rank is done
+      // reading the previous call's
+      if (call > 1u) {
+        A sum;
+        ok = exchange_receive<A>(px, header, n, idx, call - 1u, words, deadline, sum);
+        if (ok && dw_out != nullptr) dw_out[idx] = Elem<T>::from_acc(sum);
+      }
+      exchange_send<A>(px, header, n, idx, call, total);
+    } else {
+      exchange_send<A>(px, header, n, idx, call, total);
       A sum;
-      ok = exchange_receive<A>(px, header, n, idx, call - 1u, words, deadline, sum);
-      if (ok && dw_prev != nullptr) dw_prev[idx] = Elem<T>::from_acc(sum);
+      exchange_preload<A>(px, header, n, idx, call, words);
+      ok = exchange_receive<A>(px, header, n, idx, call, words, deadline, sum);
+      if (ok && dw_out != nullptr) dw_out[idx] = Elem<T>::from_acc(sum);
     }
-    exchange_send<A>(px, header, n, idx, call, total);
   }
   ok = __all_sync(0xffffffffu, ok);
   if (o == 0) {

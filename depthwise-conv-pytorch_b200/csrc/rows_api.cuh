@@ -25,6 +25,14 @@ template <typename T>
 int rows_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<T>::acc_t *partial,
                   const Shape &s, cudaStream_t st, int *slices_out);
 
+// Tiles family (tiles.cu): any padding, any map size; 3x3 / 5x5 / 7x7; fp32, fp16, bf16.
+template <typename T> int tiles_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st);
+template <typename T>
+int tiles_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStream_t st);
+template <typename T>
+int tiles_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *partial, const Shape &s,
+                          int slices, cudaStream_t st);
+
 // Reads and clears the flags kernels raise when a bounded wait expires (synchronises the
 // device).  Bit 0: forward/backward-input kernels, bit 1: backward-filter kernels.
 int rows_take_device_error();

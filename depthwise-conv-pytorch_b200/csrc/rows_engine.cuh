@@ -476,6 +476,70 @@ __device__ __forceinline__ TapLayout tap_layout(const T *gw, int first_plane, in
   return l;
 }
 
+// The producer warp of the forward / backward-input kernels: walks this CTA's tiles and brings
+// each tile's rows and taps into the next free stage of the ring.
+template <typename T, int K, int S, int MODE>
+__device__ __forceinline__ void conv_producer(const RowsParams &p, const RowsRing &ring,
+                                              int *__restrict__ error_flag) {
+  constexpr int KK = K * K;
+  const T *__restrict__ gin = static_cast<const T *>(p.in);
+  const T *__restrict__ gw = static_cast<const T *>(p.w);
+  const int lane = threadIdx.x & 31;
+  const size_t plane_in = (size_t)p.Hin * p.Win;
+  int stage = -1, use = 0;
+  for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+    if (++stage == p.NST) {
+      stage = 0;
+      ++use;
+    }
+    if (use > 0 && !mbar_wait_bounded(&ring.empty[stage], (use - 1) & 1)) {
+      *ring.abort_flag = 1;
+      atomicExch(error_flag, 1);
+    }
+    if (*ring.abort_flag) break;
+    const ConvTile t = conv_tile<K, S, MODE>(p, tile);
+    unsigned char *sb = ring.stage(stage);
+    // the tile's rows are one contiguous range of the tensor: one bulk copy, issued first
+    // so that the tap loads below overlap with it
+    uint32_t tx = 0;
+    if (lane == 0) {
+      fence_proxy_async_smem();
+      const int nrows = t.in_hi - t.in_lo;
+      const int elems = (p.NRT == 1) ? t.gcount * (int)plane_in : nrows * p.Win;
+      const T *src0 = gin + (size_t)t.pg * p.G * plane_in + (size_t)t.in_lo * p.Win;
+      tx = stage_range(reinterpret_cast<T *>(sb + p.TAPB + 16), src0, elems, &ring.full[stage]);
+    }
+    // taps of the tile's channels: consecutive channels are one contiguous range of the
+    // filter tensor (two when the group wraps past the last channel), so they are bulk
+    // copies too, issued by lanes 1 and 2
+    const TapLayout tl = tap_layout<T, KK>(gw, t.pg * p.G, t.gcount, p.C);
+    T *staps = reinterpret_cast<T *>(sb);
+    if (tl.direct) {
+      if (lane == 1) {
+        fence_proxy_async_smem();
+        tx = stage_range(staps, gw + (size_t)tl.c_base * KK, tl.nA * KK, &ring.full[stage]);
+      } else if (lane == 2 && tl.nB > 0) {
+        fence_proxy_async_smem();
+        tx = stage_range(staps + tl.offB16, gw, tl.nB * KK, &ring.full[stage]);
+      }
+    } else {
+      // more planes in the tile than channels in the tensor: gather with plain loads
+      for (int idx = lane; idx < t.gcount * KK; idx += 32) {
+        const int g = idx / KK;
+        staps[idx] = gw[(size_t)((tl.c_base + g) % p.C) * KK + (idx - g * KK)];
+      }
+    }
+    tx = warp_sum(tx);
+    __syncwarp();
+    if (lane == 0) {
+      if (tx)
+        mbar_arrive_expect_tx(&ring.full[stage], tx);
+      else
+        mbar_arrive(&ring.full[stage]);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // forward / backward-input
 // ---------------------------------------------------------------------------------------
@@ -499,59 +563,7 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
   const size_t plane_out = (size_t)p.Hout * p.Wout;
 
   if (warp == ROWS_CWARPS) {
-    // ------------------------------- producer warp -------------------------------
-    int stage = -1, use = 0;
-    for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
-      if (++stage == p.NST) {
-        stage = 0;
-        ++use;
-      }
-      if (use > 0 && !mbar_wait_bounded(&ring.empty[stage], (use - 1) & 1)) {
-        *ring.abort_flag = 1;
-        atomicExch(error_flag, 1);
-      }
-      if (*ring.abort_flag) break;
-      const ConvTile t = conv_tile<K, S, MODE>(p, tile);
-      unsigned char *sb = ring.stage(stage);
-      // the tile's rows are one contiguous range of the tensor: one bulk copy, issued first
-      // so that the tap loads below overlap with it
-      uint32_t tx = 0;
-      if (lane == 0) {
-        fence_proxy_async_smem();
-        const int nrows = t.in_hi - t.in_lo;
-        const int elems = (p.NRT == 1) ? t.gcount * (int)plane_in : nrows * p.Win;
-        const T *src0 = gin + (size_t)t.pg * p.G * plane_in + (size_t)t.in_lo * p.Win;
-        tx = stage_range(reinterpret_cast<T *>(sb + p.TAPB + 16), src0, elems, &ring.full[stage]);
-      }
-      // taps of the tile's channels: consecutive channels are one contiguous range of the
-      // filter tensor (two when the group wraps past the last channel), so they are bulk
-      // copies too, issued by lanes 1 and 2
-      const TapLayout tl = tap_layout<T, KK>(gw, t.pg * p.G, t.gcount, p.C);
-      T *staps = reinterpret_cast<T *>(sb);
-      if (tl.direct) {
-        if (lane == 1) {
-          fence_proxy_async_smem();
-          tx = stage_range(staps, gw + (size_t)tl.c_base * KK, tl.nA * KK, &ring.full[stage]);
-        } else if (lane == 2 && tl.nB > 0) {
-          fence_proxy_async_smem();
-          tx = stage_range(staps + tl.offB16, gw, tl.nB * KK, &ring.full[stage]);
-        }
-      } else {
-        // more planes in the tile than channels in the tensor: gather with plain loads
-        for (int idx = lane; idx < t.gcount * KK; idx += 32) {
-          const int g = idx / KK;
-          staps[idx] = gw[(size_t)((tl.c_base + g) % p.C) * KK + (idx - g * KK)];
-        }
-      }
-      tx = warp_sum(tx);
-      __syncwarp();
-      if (lane == 0) {
-        if (tx)
-          mbar_arrive_expect_tx(&ring.full[stage], tx);
-        else
-          mbar_arrive(&ring.full[stage]);
-      }
-    }
+    conv_producer<T, K, S, MODE>(p, ring, error_flag);
     return;
   }
 

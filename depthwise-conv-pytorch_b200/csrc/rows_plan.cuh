@@ -209,13 +209,21 @@ inline TilePlan plan_search(PlanInput in, const int *u_options, int n_options) {
   return best;
 }
 
-// Planning walks a few hundred candidates; results are remembered per problem so that a
-// repeated launch costs one table lookup.
-// Tuning aid: DWCONV_B200_FORCE_PLAN="fwd=U,G,NRT,TH,NRB,NST;bwd=...;flt=..." (read once per
-// process) replaces the planner's choice for forward (and stride-1 backward-input, which is the
-// same kernel), stride-2 backward-input, or backward-filter.  A tiling that does not fit is refused.
+// Tuning aids, compiled only into a library built with -DDWCONV_B200_TUNING (never the shipped
+// one): environment variables that override the planner and the variant selection, for sweeps.
+//   DWCONV_B200_FORCE_PLAN="fwd=U,G,NRT,TH,NRB,NST;bwd=...;flt=..."  one tiling (refused if it
+//       does not fit) for forward / stride-1 backward-input, stride-2 backward-input, backward-filter
+//   DWCONV_B200_FORCE_U="fwd=U;bwd=U;flt=U"   one chunk height
+//   DWCONV_B200_<NAME>=int                     switches read with tuning_int("<NAME>", default)
+#ifdef DWCONV_B200_TUNING
+inline int tuning_int(const char *name, int dflt) {
+  char key[96];
+  std::snprintf(key, sizeof(key), "DWCONV_B200_%s", name);
+  const char *v = std::getenv(key);
+  return v ? std::atoi(v) : dflt;
+}
 inline bool forced_plan(const PlanInput &in, TilePlan &out) {
-  static const char *env = std::getenv("DWCONV_B200_FORCE_PLAN");
+  const char *env = std::getenv("DWCONV_B200_FORCE_PLAN");
   if (env == nullptr) return false;
   const char *key = in.filter ? "flt=" : (in.mode == MODE_BWD ? "bwd=" : "fwd=");
   const char *at = std::strstr(env, key);
@@ -234,16 +242,20 @@ inline bool forced_plan(const PlanInput &in, TilePlan &out) {
   out = c;
   return true;
 }
-
-// Tuning aid: DWCONV_B200_FORCE_U="fwd=U;bwd=U;flt=U" restricts the planner to one chunk height.
 inline int forced_u(const PlanInput &in) {
-  static const char *env = std::getenv("DWCONV_B200_FORCE_U");
+  const char *env = std::getenv("DWCONV_B200_FORCE_U");
   if (env == nullptr) return 0;
   const char *at = std::strstr(env, in.filter ? "flt=" : (in.mode == MODE_BWD ? "bwd=" : "fwd="));
   return at ? std::atoi(at + 4) : 0;
 }
+#else
+inline int tuning_int(const char *, int dflt) { return dflt; }
+#endif
 
+// Planning walks a few hundred candidates; results are remembered per problem so that a
+// repeated launch costs one table lookup.
 inline TilePlan plan_best(const PlanInput &in, const int *u_options, int n_options) {
+#ifdef DWCONV_B200_TUNING
   {
     TilePlan forced{};
     if (forced_plan(in, forced)) {
@@ -254,6 +266,7 @@ inline TilePlan plan_best(const PlanInput &in, const int *u_options, int n_optio
     for (int i = 0; fu > 0 && i < n_options; ++i)
       if (u_options[i] == fu) return plan_search(in, &u_options[i], 1);
   }
+#endif
   struct Entry {
     int key[16];
     TilePlan plan;

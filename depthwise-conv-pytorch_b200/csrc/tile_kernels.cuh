@@ -1,0 +1,235 @@
+// "Tiles" kernel family: the general fast path for what the rows family declines.
+//
+// Serves 3x3 / 5x5 / 7x7 filters with ANY padding (top / left given, bottom / right implied by
+// the output extent), any map size (odd widths, maps wider than 128 columns), fp32 / fp16 /
+// bf16: forward, backward-input and backward-filter at stride 1 or 2.
+// It covers the rest of the domain of the reference's large-map kernel
+// (torch_dwconv/dwconv_kernel.cu:69-181: any map size, any padding below k), whose own tests
+// use exactly such shapes (padding 0; 63x65 and 33x35 maps).
+//
+// A CTA takes a tile of TW x 32 (or 32 x 64) outputs of one plane.  All threads copy the input
+// tile with its halo from global to shared memory with coalesced scalar loads (any alignment;
+// elements outside the map become zero, which is the padding), converting to fp32 on the way.
+// A thread then owns ONE output column and a strip of R = 8 output rows: it walks the strip's
+// input rows once, reads the K values of a row under its column from shared memory (consecutive
+// threads read consecutive words: no bank conflicts; stride 2 keeps even and odd columns in
+// separate halves of a row for the same reason), and adds that row's contribution to every
+// output row it touches.  Per accumulator the taps arrive ky-major / kx-minor with one fused
+// multiply-add each: the reference's order (dwconv_kernel.cu:164-172), so fp32 results are
+// bit-identical to it and to the other families.  No bulk copies, no pipeline: latency is
+// hidden by several resident CTAs per SM.
+//
+// Backward-input at stride 2 is the reference's own formulation (torch_dwconv/dwconv.py:57-64,
+// dwconv_kernel.cu:107-114): dy is staged with a zero between neighbouring elements (up-sampling
+// by the stride happens while copying into shared memory) and correlated at stride 1 with the
+// flipped filter; the inserted zeros add nothing, so the sum is the same as the polyphase form's.
+#pragma once
+
+#include "common.cuh"
+
+namespace dwb {
+
+constexpr int TILE_THREADS = 256;
+constexpr int TILE_R = 8;  // output rows per thread
+
+struct TileParams {
+  int NC, C;
+  int Hin, Win, Hout, Wout;
+  int pt, pl;    // rows / columns of zero padding above / left of the input
+  int flip;      // apply the filter flipped in both axes (backward-input)
+  int tiles_x, tiles_y;
+  long long ntiles;
+};
+
+// Position of input-tile column x inside a shared-memory row: stride 2 separates even and odd
+// columns so that threads c, c+1, ... (which read columns 2c + kx) hit consecutive words.
+template <int S, int HALF> __device__ __forceinline__ int tile_col(int x) {
+  return S == 1 ? x : (x & 1) * HALF + (x >> 1);
+}
+
+template <typename T, int K, int S, int TW>
+struct TileGeo {
+  static constexpr int TH = TILE_THREADS / TW * TILE_R;     // output rows per tile
+  static constexpr int IH = (TH - 1) * S + K;               // input rows per tile
+  static constexpr int IW = (TW - 1) * S + K;               // input columns per tile
+  static constexpr int HALF = (IW + 1) / 2;
+  static constexpr int PITCH = S == 1 ? IW : 2 * HALF;
+  static constexpr int IR = (TILE_R - 1) * S + K;           // input rows under one thread's strip
+};
+
+// Copies the input tile whose first element is (gy0, gx0) of `plane` into shared memory.
+// UP > 1: (gy, gx) address the map up-sampled by UP with zeros in between ((Hin-1)*UP+1 rows);
+// only coordinates that are multiples of UP hold data.
+template <typename T, int S, int IH, int IW, int HALF, int PITCH, int UP = 1>
+__device__ __forceinline__ void tile_stage(float *sm, const T *__restrict__ plane, int Hin, int Win,
+                                           int gy0, int gx0) {
+  constexpr int TOTAL = IH * IW;
+  constexpr int UNROLL = 4;
+  for (int base = threadIdx.x; base < TOTAL; base += TILE_THREADS * UNROLL) {
+    float v[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int idx = base + u * TILE_THREADS;
+      const int iy = idx / IW, ix = idx - iy * IW;
+      const int gy = gy0 + iy, gx = gx0 + ix;
+      v[u] = 0.f;
+      if (UP == 1) {
+        if (idx < TOTAL && (unsigned)gy < (unsigned)Hin && (unsigned)gx < (unsigned)Win)
+          v[u] = Elem<T>::ld(plane + (size_t)gy * Win + gx);
+      } else {
+        const int sy = gy / UP, sx = gx / UP;  // gy, gx >= 0 is checked below
+        if (idx < TOTAL && gy >= 0 && gx >= 0 && sy * UP == gy && sx * UP == gx && sy < Hin && sx < Win)
+          v[u] = Elem<T>::ld(plane + (size_t)sy * Win + sx);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int idx = base + u * TILE_THREADS;
+      const int iy = idx / IW, ix = idx - iy * IW;
+      if (idx < TOTAL) sm[iy * PITCH + tile_col<S, HALF>(ix)] = v[u];
+    }
+  }
+}
+
+// out[oy][ox] = sum over (ky, kx) of in[oy*S - pt + ky][ox*S - pl + kx] * tap[ky][kx], `in` being
+// the map up-sampled by UP.
+template <typename T, int K, int S, int TW, int UP = 1>
+__global__ void __launch_bounds__(TILE_THREADS)
+tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restrict__ out,
+                 const TileParams p) {
+  using G = TileGeo<T, K, S, TW>;
+  constexpr int KK = K * K;
+  __shared__ float sm[G::IH * G::PITCH];
+  const int tc = threadIdx.x % TW;   // output column inside the tile
+  const int tr = threadIdx.x / TW;   // strip of TILE_R output rows
+  const size_t plane_in = (size_t)p.Hin * p.Win, plane_out = (size_t)p.Hout * p.Wout;
+  const int per_plane = p.tiles_x * p.tiles_y;
+  for (long long tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+    const int plane = (int)(tile / per_plane);
+    const int rest = (int)(tile - (long long)plane * per_plane);
+    const int ty = rest / p.tiles_x, tx = rest - ty * p.tiles_x;
+    const int y0 = ty * G::TH, x0 = tx * TW;  // first output of the tile
+    __syncthreads();                         // the previous tile's readers are done
+    tile_stage<T, S, G::IH, G::IW, G::HALF, G::PITCH, UP>(sm, in + (size_t)plane * plane_in, p.Hin,
+                                                          p.Win, y0 * S - p.pt, x0 * S - p.pl);
+    float tap[K][K];
+    {
+      const T *tp = w + (size_t)(plane % p.C) * KK;
+#pragma unroll
+      for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+        for (int kx = 0; kx < K; ++kx)
+          tap[ky][kx] = Elem<T>::ld(tp + (p.flip ? KK - 1 - (ky * K + kx) : ky * K + kx));
+    }
+    __syncthreads();
+    float acc[TILE_R];
+#pragma unroll
+    for (int o = 0; o < TILE_R; ++o) acc[o] = 0.f;
+    const float *row = sm + (tr * TILE_R * S) * G::PITCH;
+#pragma unroll
+    for (int ir = 0; ir < G::IR; ++ir) {
+      float v[K];
+#pragma unroll
+      for (int kx = 0; kx < K; ++kx) v[kx] = row[ir * G::PITCH + tile_col<S, G::HALF>(tc * S + kx)];
+#pragma unroll
+      for (int o = 0; o < TILE_R; ++o) {
+        const int ky = ir - o * S;
+        if (ky >= 0 && ky < K) {
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) acc[o] = fmaf(v[kx], tap[ky][kx], acc[o]);
+        }
+      }
+    }
+    const int ox = x0 + tc;
+    if (ox < p.Wout) {
+      T *op = out + (size_t)plane * plane_out + (size_t)(y0 + tr * TILE_R) * p.Wout + ox;
+#pragma unroll
+      for (int o = 0; o < TILE_R; ++o)
+        if (y0 + tr * TILE_R + o < p.Hout) op[(size_t)o * p.Wout] = Elem<T>::from_acc(acc[o]);
+    }
+  }
+}
+
+// Backward-filter, first pass.  Block (c, slice) owns the images [slice*N/SL, (slice+1)*N/SL) of
+// channel c and walks their tiles: the x tile (with halo) and the dy tile are staged in shared
+// memory; a thread owns one dy column and a strip of dy rows, keeps K*K accumulators, walks the
+// strip's x rows once and adds dy[o] * x-row values to the tap row each (x row, dy row) pair
+// belongs to.  At the end the block adds its threads' accumulators in a fixed order (warp
+// shuffle, then the warps in order) and writes partial[(c*SL + slice)*K*K + tap].
+struct TileFilterParams {
+  int N, C, H, W, Ho, Wo;
+  int pt, pl;
+  int SL;
+  int tiles_x, tiles_y;
+};
+
+template <typename T, int K, int S, int TW>
+__global__ void __launch_bounds__(TILE_THREADS)
+tile_filter_kernel(const T *__restrict__ x, const T *__restrict__ dy, float *__restrict__ partial,
+                   const TileFilterParams p) {
+  using G = TileGeo<T, K, S, TW>;
+  constexpr int KK = K * K;
+  __shared__ float sx[G::IH * G::PITCH];
+  __shared__ float sdy[G::TH * TW];
+  __shared__ float red[TILE_THREADS / 32][KK];
+  pdl_launch_dependents();  // the second pass may take its place on the SMs early
+  const int c = blockIdx.x / p.SL;
+  const int slice = blockIdx.x - c * p.SL;
+  const int n0 = (int)((long long)slice * p.N / p.SL);
+  const int n1 = (int)((long long)(slice + 1) * p.N / p.SL);
+  const int tc = threadIdx.x % TW, tr = threadIdx.x / TW;
+  const size_t plane_x = (size_t)p.H * p.W, plane_dy = (size_t)p.Ho * p.Wo;
+  float acc[K][K];
+#pragma unroll
+  for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+    for (int kx = 0; kx < K; ++kx) acc[ky][kx] = 0.f;
+
+  for (int n = n0; n < n1; ++n) {
+    const T *xp = x + ((size_t)n * p.C + c) * plane_x;
+    const T *gp = dy + ((size_t)n * p.C + c) * plane_dy;
+    for (int ty = 0; ty < p.tiles_y; ++ty)
+      for (int tx = 0; tx < p.tiles_x; ++tx) {
+        const int y0 = ty * G::TH, x0 = tx * TW;
+        __syncthreads();
+        tile_stage<T, S, G::IH, G::IW, G::HALF, G::PITCH>(sx, xp, p.H, p.W, y0 * S - p.pt, x0 * S - p.pl);
+        tile_stage<T, 1, G::TH, TW, 0, TW>(sdy, gp, p.Ho, p.Wo, y0, x0);
+        __syncthreads();
+        float g[TILE_R];
+#pragma unroll
+        for (int o = 0; o < TILE_R; ++o) g[o] = sdy[(tr * TILE_R + o) * TW + tc];
+        const float *row = sx + (tr * TILE_R * S) * G::PITCH;
+#pragma unroll
+        for (int ir = 0; ir < G::IR; ++ir) {
+          float v[K];
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) v[kx] = row[ir * G::PITCH + tile_col<S, G::HALF>(tc * S + kx)];
+#pragma unroll
+          for (int o = 0; o < TILE_R; ++o) {
+            const int ky = ir - o * S;
+            if (ky >= 0 && ky < K) {
+#pragma unroll
+              for (int kx = 0; kx < K; ++kx) acc[ky][kx] = fmaf(g[o], v[kx], acc[ky][kx]);
+            }
+          }
+        }
+      }
+  }
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+  for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+    for (int kx = 0; kx < K; ++kx) {
+      const float v = warp_sum(acc[ky][kx]);
+      if (lane == 0) red[wid][ky * K + kx] = v;
+    }
+  __syncthreads();
+  if (threadIdx.x < KK) {
+    float s = 0.f;
+#pragma unroll
+    for (int q = 0; q < TILE_THREADS / 32; ++q) s += red[q][threadIdx.x];
+    partial[((size_t)c * p.SL + slice) * KK + threadIdx.x] = s;
+  }
+}
+
+}  // namespace dwb

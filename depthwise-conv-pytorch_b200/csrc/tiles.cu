@@ -1,0 +1,150 @@
+// Tiles family: variant selection and launches (kernels: tile_kernels.cuh).
+#include "tile_kernels.cuh"
+#include "rows_api.cuh"
+
+namespace dwb {
+
+namespace {
+
+template <typename T> struct TilesDtype { static constexpr bool ok = false; };
+template <> struct TilesDtype<float> { static constexpr bool ok = true; };
+template <> struct TilesDtype<__half> { static constexpr bool ok = true; };
+template <> struct TilesDtype<__nv_bfloat16> { static constexpr bool ok = true; };
+
+inline bool tiles_filter_ok(const Shape &s) {
+  return s.kh == s.kw && (s.kh == 3 || s.kh == 5 || s.kh == 7) && s.sh == s.sw &&
+         (s.sh == 1 || s.sh == 2);
+}
+// Tiny maps would leave most of a tile empty: they stay on the one-thread-per-output kernels.
+inline bool tiles_worth_it(int Hout, int Wout) { return Wout >= 16 && Hout >= 8; }
+
+// 64-column tiles unless 32-column tiles waste fewer columns (narrow or just-over-64 maps).
+inline int pick_tw(int Wout) {
+  const int w64 = ceil_div(Wout, 64) * 64, w32 = ceil_div(Wout, 32) * 32;
+  return w32 < w64 ? 32 : 64;
+}
+
+template <typename T, int K, int S, int TW, int UP = 1>
+void launch_conv(const T *in, const T *w, T *out, TileParams p, cudaStream_t st) {
+  constexpr int TH = TileGeo<T, K, S, TW>::TH;
+  p.tiles_x = ceil_div(p.Wout, TW);
+  p.tiles_y = ceil_div(p.Hout, TH);
+  p.ntiles = (long long)p.NC * p.tiles_x * p.tiles_y;
+  const long long cap = 148ll * 16;  // grid-stride beyond this
+  const int grid = (int)(p.ntiles < cap ? p.ntiles : cap);
+  tile_conv_kernel<T, K, S, TW, UP><<<grid, TILE_THREADS, 0, st>>>(in, w, out, p);
+}
+
+template <typename T, int K, int S, int UP = 1>
+void launch_conv_tw(const T *in, const T *w, T *out, const TileParams &p, cudaStream_t st) {
+  if (pick_tw(p.Wout) == 32)
+    launch_conv<T, K, S, 32, UP>(in, w, out, p, st);
+  else
+    launch_conv<T, K, S, 64, UP>(in, w, out, p, st);
+}
+
+template <typename T>
+int conv_dispatch(const T *in, const T *w, T *out, const TileParams &p, int K, int S, cudaStream_t st) {
+  switch (K * 10 + S) {
+    case 31: launch_conv_tw<T, 3, 1>(in, w, out, p, st); return ROWS_SERVED;
+    case 51: launch_conv_tw<T, 5, 1>(in, w, out, p, st); return ROWS_SERVED;
+    case 71: launch_conv_tw<T, 7, 1>(in, w, out, p, st); return ROWS_SERVED;
+    case 32: launch_conv_tw<T, 3, 2>(in, w, out, p, st); return ROWS_SERVED;
+    case 52: launch_conv_tw<T, 5, 2>(in, w, out, p, st); return ROWS_SERVED;
+    case 72: launch_conv_tw<T, 7, 2>(in, w, out, p, st); return ROWS_SERVED;
+    default: return ROWS_DECLINED;
+  }
+}
+
+template <typename T, int K, int S, int TW>
+void launch_filter(const T *x, const T *dy, float *partial, TileFilterParams p, cudaStream_t st) {
+  constexpr int TH = TileGeo<T, K, S, TW>::TH;
+  p.tiles_x = ceil_div(p.Wo, TW);
+  p.tiles_y = ceil_div(p.Ho, TH);
+  tile_filter_kernel<T, K, S, TW><<<p.C * p.SL, TILE_THREADS, 0, st>>>(x, dy, partial, p);
+}
+
+template <typename T, int K, int S>
+void launch_filter_tw(const T *x, const T *dy, float *partial, const TileFilterParams &p, cudaStream_t st) {
+  if (pick_tw(p.Wo) == 32)
+    launch_filter<T, K, S, 32>(x, dy, partial, p, st);
+  else
+    launch_filter<T, K, S, 64>(x, dy, partial, p, st);
+}
+
+}  // namespace
+
+template <typename T>
+int tiles_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st) {
+  if constexpr (!TilesDtype<T>::ok) {
+    return ROWS_DECLINED;
+  } else {
+    if (!tiles_filter_ok(s) || !tiles_worth_it(s.Ho, s.Wo)) return ROWS_DECLINED;
+    TileParams p{};
+    p.NC = s.N * s.C; p.C = s.C;
+    p.Hin = s.H; p.Win = s.W; p.Hout = s.Ho; p.Wout = s.Wo;
+    p.pt = s.ph; p.pl = s.pw; p.flip = 0;
+    return conv_dispatch<T>(x, w, y, p, s.kh, s.sh, st);
+  }
+}
+
+// The transposed operation is the stride-1 correlation of dy, up-sampled by the forward stride
+// and padded by k-1-p, with the flipped filter (torch_dwconv/dwconv.py:39-44,57-64).
+template <typename T>
+int tiles_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStream_t st) {
+  if constexpr (!TilesDtype<T>::ok) {
+    return ROWS_DECLINED;
+  } else {
+    if (!tiles_filter_ok(s) || s.ph > s.kh - 1 || s.pw > s.kw - 1 || !tiles_worth_it(s.H, s.W))
+      return ROWS_DECLINED;
+    TileParams p{};
+    p.NC = s.N * s.C; p.C = s.C;
+    p.Hin = s.Ho; p.Win = s.Wo; p.Hout = s.H; p.Wout = s.W;
+    p.pt = s.kh - 1 - s.ph; p.pl = s.kw - 1 - s.pw; p.flip = 1;
+    if (s.sh == 1) return conv_dispatch<T>(dy, w, dx, p, s.kh, 1, st);
+    switch (s.kh) {
+      case 3: launch_conv_tw<T, 3, 1, 2>(dy, w, dx, p, st); return ROWS_SERVED;
+      case 5: launch_conv_tw<T, 5, 1, 2>(dy, w, dx, p, st); return ROWS_SERVED;
+      case 7: launch_conv_tw<T, 7, 1, 2>(dy, w, dx, p, st); return ROWS_SERVED;
+      default: return ROWS_DECLINED;
+    }
+  }
+}
+
+// First pass of the filter gradient with `slices` batch slices per channel (the caller sized
+// the workspace for them): partial[C][slices][K*K].
+template <typename T>
+int tiles_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *partial, const Shape &s,
+                          int slices, cudaStream_t st) {
+  if constexpr (!TilesDtype<T>::ok) {
+    return ROWS_DECLINED;
+  } else {
+    if (!tiles_filter_ok(s) || !tiles_worth_it(s.Ho, s.Wo)) return ROWS_DECLINED;
+    TileFilterParams p{};
+    p.N = s.N; p.C = s.C; p.H = s.H; p.W = s.W; p.Ho = s.Ho; p.Wo = s.Wo;
+    p.pt = s.ph; p.pl = s.pw; p.SL = slices;
+    switch (s.kh * 10 + s.sh) {
+      case 31: launch_filter_tw<T, 3, 1>(x, dy, partial, p, st); break;
+      case 51: launch_filter_tw<T, 5, 1>(x, dy, partial, p, st); break;
+      case 71: launch_filter_tw<T, 7, 1>(x, dy, partial, p, st); break;
+      case 32: launch_filter_tw<T, 3, 2>(x, dy, partial, p, st); break;
+      case 52: launch_filter_tw<T, 5, 2>(x, dy, partial, p, st); break;
+      case 72: launch_filter_tw<T, 7, 2>(x, dy, partial, p, st); break;
+      default: return ROWS_DECLINED;
+    }
+    return ROWS_SERVED;
+  }
+}
+
+#define DWB_TILES_INSTANTIATE(T)                                                              \
+  template int tiles_forward<T>(const T *, const T *, T *, const Shape &, cudaStream_t);        \
+  template int tiles_backward_input<T>(const T *, const T *, T *, const Shape &, cudaStream_t); \
+  template int tiles_backward_filter<T>(const T *, const T *, typename Elem<T>::acc_t *,        \
+                                        const Shape &, int, cudaStream_t);
+DWB_TILES_INSTANTIATE(float)
+DWB_TILES_INSTANTIATE(__half)
+DWB_TILES_INSTANTIATE(__nv_bfloat16)
+DWB_TILES_INSTANTIATE(double)
+#undef DWB_TILES_INSTANTIATE
+
+}  // namespace dwb

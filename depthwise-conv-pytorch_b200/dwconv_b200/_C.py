@@ -42,14 +42,47 @@ def _check_filter(input, kernel):
 
 
 def _stream(t):
-    return torch.cuda.current_stream(t.device).cuda_stream
+    """Raw handle of the current stream of ``t``'s device (no Stream object is built)."""
+    return torch._C._cuda_getCurrentRawStream(t.device.index)
+
+
+class _on_device:
+    """``with _on_device(t):`` makes ``t``'s device current for the library call; when it
+    already is (the usual case) nothing is switched."""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, t):
+        self.idx = t.device.index
+
+    def __enter__(self):
+        self.prev = torch.cuda._exchange_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev != self.idx:
+            torch.cuda._maybe_exchange_device(self.prev)
+        return False
+
+
+def out_size(n_in, up, pad0, pad1, k, down):
+    """``dwconv_b200_out_size`` restated in Python (the hot path calls it per tensor):
+    (in*up + pad0 + pad1 - k + down) / down, torch_dwconv/dwconv_kernel.cu:612-615."""
+    if down <= 0:
+        return 0
+    num = n_in * up + pad0 + pad1 - k + down
+    return num // down if num >= 0 else 0
 
 
 def use_dwconv2d_small(input, kernel, up_h, up_w, down_h, down_w, pad_h, pad_w):
-    """torch_dwconv/dwconv.cpp:61 -- host-only shape test, works for any device."""
-    return bool(_lib.lib.dwconv_b200_use_dwconv2d_small(
-        input.shape[2], input.shape[3], kernel.shape[2], kernel.shape[3],
-        up_h, up_w, down_h, down_w, pad_h, pad_w))
+    """torch_dwconv/dwconv.cpp:61 -- host-only shape test, works for any device; the same
+    predicate as ``dwconv_b200_use_dwconv2d_small`` (dwconv_kernel.cu:652-662), evaluated here
+    to spare a library call per forward."""
+    in_h, in_w, kh, kw = input.shape[2], input.shape[3], kernel.shape[2], kernel.shape[3]
+    return (down_h == 1 and down_w == 1 and in_h <= 32 and in_w <= 32
+            and in_h == out_size(in_h, up_h, pad_h, pad_h, kh, down_h)
+            and in_w == out_size(in_w, up_w, pad_w, pad_w, kw, down_w)
+            and 0 <= pad_h < kh and 0 <= pad_w < kw
+            and kh * kw <= (in_h + 1) // 2 * in_w)
 
 
 def dwconv2d(input, kernel, up_h, up_w, down_h, down_w, pad_h0, pad_h1, pad_w0, pad_w1, forward):
@@ -62,12 +95,12 @@ def dwconv2d(input, kernel, up_h, up_w, down_h, down_w, pad_h0, pad_h1, pad_w0, 
     kernel = kernel.contiguous()
     N, C, H, W = input.shape
     kh, kw = kernel.shape[2], kernel.shape[3]
-    oh = _lib.lib.dwconv_b200_out_size(H, up_h, pad_h0, pad_h1, kh, down_h)
-    ow = _lib.lib.dwconv_b200_out_size(W, up_w, pad_w0, pad_w1, kw, down_w)
+    oh = out_size(H, up_h, pad_h0, pad_h1, kh, down_h)
+    ow = out_size(W, up_w, pad_w0, pad_w1, kw, down_w)
     if oh <= 0 or ow <= 0:
         raise RuntimeError(f"dwconv_b200.dwconv2d: empty output ({oh} x {ow})")
     out = torch.empty((N, C, oh, ow), dtype=input.dtype, device=input.device)
-    with torch.cuda.device(input.device):
+    with _on_device(input):
         st = _lib.lib.dwconv_b200_dwconv2d(
             input.data_ptr(), kernel.data_ptr(), out.data_ptr(), code, N, C, H, W, kh, kw,
             up_h, up_w, down_h, down_w, pad_h0, pad_h1, pad_w0, pad_w1, 1 if forward else 0,
@@ -103,7 +136,7 @@ def dwconv2d_backward_kernel(input, out_grad, kernel, up_h, up_w, down_h, down_w
         raise RuntimeError("dwconv_b200.dwconv2d_backward_kernel: invalid geometry")
     dkernel = torch.empty((C, 1, kh, kw), dtype=input.dtype, device=input.device)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=input.device)
-    with torch.cuda.device(input.device):
+    with _on_device(input):
         st = _lib.lib.dwconv_b200_dwconv2d_backward_kernel(
             input.data_ptr(), out_grad.data_ptr(), dkernel.data_ptr(), ws.data_ptr(), nbytes, code,
             N, C, H, W, oh, ow, kh, kw, up_h, up_w, down_h, down_w, pad_h, pad_w, _stream(input))

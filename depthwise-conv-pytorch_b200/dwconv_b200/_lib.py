@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__
 _BUILD_HINT = "python depthwise-conv-pytorch_b200/build_dwconv_b200.py"
 
 F32, F16, F64, BF16 = 0, 1, 2, 3
-PATH_AUTO, PATH_DIRECT, PATH_ROWS = 0, 1, 2
+PATH_AUTO, PATH_DIRECT, PATH_ROWS, PATH_TILES = 0, 1, 2, 3
 OK = 0
 
 
@@ -58,6 +58,8 @@ def _load():
         "dwconv_b200_exchange_finish": (ci, [vp, vp, vp]),
         "dwconv_b200_backward_filter_exchange": (ci, [vp, vp, vp, vp, sz, ci, sp, vp, vp]),
         "dwconv_b200_backward_exchange": (ci, [vp, vp, vp, vp, vp, vp, sz, ci, sp, vp, vp]),
+        "dwconv_b200_backward_filter_allreduce": (ci, [vp, vp, vp, vp, sz, ci, sp, vp, vp]),
+        "dwconv_b200_backward_allreduce": (ci, [vp, vp, vp, vp, vp, vp, sz, ci, sp, vp, vp]),
     }
     for name, (res, args) in sig.items():
         try:
@@ -78,6 +80,7 @@ EXPORTS = (
     "dwconv_b200_forward", "dwconv_b200_backward_input",
     "dwconv_b200_backward_filter_workspace_bytes", "dwconv_b200_backward_filter",
     "dwconv_b200_backward", "dwconv_b200_backward_accumulate", "dwconv_b200_backward_exchange",
+    "dwconv_b200_backward_filter_allreduce", "dwconv_b200_backward_allreduce",
     "dwconv_b200_use_dwconv2d_small", "dwconv_b200_dwconv2d", "dwconv_b200_dwconv2d_small",
     "dwconv_b200_dwconv2d_backward_kernel", "dwconv_b200_static_scratch_bytes",
     "dwconv_b200_backward_filter_static",

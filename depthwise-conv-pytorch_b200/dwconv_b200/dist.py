@@ -183,9 +183,7 @@ class PeerFilterExchange:
                 dist.barrier(group=group)  # nobody sends before every rank has mapped its peers
         self._ws = None
 
-    def start(self, x, dy, stride=1, padding=0, dw_prev=None):
-        """Local gradient of (x, dy), sent to all ranks; ``dw_prev`` (optional) receives the
-        previous call's world sum."""
+    def _prepare(self, x, dy, stride, padding):
         _lib = self._lib
         if (x.dim() != 4 or dy.dim() != 4 or tuple(dy.shape[:2]) != tuple(x.shape[:2])
                 or x.shape[1] != self.C or x.dtype != self.dtype or dy.dtype != self.dtype
@@ -200,6 +198,12 @@ class PeerFilterExchange:
         nws = int(_lib.lib.dwconv_b200_backward_filter_workspace_bytes(self.code, shape))
         if self._ws is None or self._ws.numel() < nws:
             self._ws = torch.empty(nws, dtype=torch.uint8, device=self.device)
+        return shape, nws
+
+    def start(self, x, dy, stride=1, padding=0, dw_prev=None):
+        """Local gradient of (x, dy), sent to all ranks; ``dw_prev`` (optional) receives the
+        previous call's world sum."""
+        shape, nws = self._prepare(x, dy, stride, padding)
         with torch.cuda.device(self.device):
             self.launch(x.data_ptr(), dy.data_ptr(), dw_prev.data_ptr() if dw_prev is not None else None,
                         self._ws.data_ptr(), nws, shape,
@@ -232,6 +236,31 @@ class PeerFilterExchange:
         self._lib.check(self._lib.lib.dwconv_b200_backward_exchange(
             x_ptr, dy_ptr, w_ptr, dx_ptr, dw_prev_ptr, ws_ptr, ws_bytes, self.code, shape, self._ex,
             stream), "backward_exchange")
+
+    def launch_allreduce(self, x_ptr, dy_ptr, w_ptr, dx_ptr, dw_ptr, ws_ptr, ws_bytes, shape, stream):
+        """The whole sum inside the kernel that finishes the gradient: ``dw`` receives THIS
+        call's world sum (the kernel waits for the other ranks' values after sending its own).
+        With ``w_ptr`` / ``dx_ptr`` the first pass is the fused backward's and ``dx`` is written
+        too; with both ``None`` only the filter gradient is computed."""
+        L = self._lib.lib
+        if dx_ptr is None:
+            st = L.dwconv_b200_backward_filter_allreduce(x_ptr, dy_ptr, dw_ptr, ws_ptr, ws_bytes,
+                                                         self.code, shape, self._ex, stream)
+        else:
+            st = L.dwconv_b200_backward_allreduce(x_ptr, dy_ptr, w_ptr, dx_ptr, dw_ptr, ws_ptr,
+                                                  ws_bytes, self.code, shape, self._ex, stream)
+        self._lib.check(st, "backward_allreduce")
+
+    def allreduce_backward_filter(self, x, dy, stride=1, padding=0, dw=None):
+        """Tensor form of ``launch_allreduce`` for the filter gradient alone."""
+        shape, nws = self._prepare(x, dy, stride, padding)
+        if dw is None:
+            dw = torch.empty((self.C, 1, self.kh, self.kw), dtype=self.dtype, device=self.device)
+        with torch.cuda.device(self.device):
+            self.launch_allreduce(x.data_ptr(), dy.data_ptr(), None, None, dw.data_ptr(),
+                                  self._ws.data_ptr(), nws, shape,
+                                  torch.cuda.current_stream(self.device).cuda_stream)
+        return dw
 
     def close(self):
         """Collective: every rank calls it, after its last ``finish``."""

@@ -29,13 +29,27 @@ def use_dwconv2d_small(input, weight, up, stride, padding):
 def _forward_shape(input, kernel, stride, pad):
     N, C, H, W = input.shape
     kh, kw = kernel.shape[2], kernel.shape[3]
-    oh = _lib.lib.dwconv_b200_out_size(H, 1, pad[0], pad[0], kh, stride[0])
-    ow = _lib.lib.dwconv_b200_out_size(W, 1, pad[1], pad[1], kw, stride[1])
+    oh = _C.out_size(H, 1, pad[0], pad[0], kh, stride[0])
+    ow = _C.out_size(W, 1, pad[1], pad[1], kw, stride[1])
     if oh <= 0 or ow <= 0:
         raise RuntimeError(
             f"depthwise_conv2d: filter {kh}x{kw} does not fit the padded input "
             f"{H + 2 * pad[0]}x{W + 2 * pad[1]}")
     return _lib.Shape(N, C, H, W, kh, kw, stride[0], stride[1], pad[0], pad[1], oh, ow)
+
+
+_WS_BYTES = {}
+
+
+def _workspace_bytes(code, s):
+    """``dwconv_b200_backward_filter_workspace_bytes``, remembered per geometry."""
+    key = (code, s.N, s.C, s.H, s.W, s.kh, s.kw, s.sh, s.sw, s.ph, s.pw, s.Ho, s.Wo)
+    n = _WS_BYTES.get(key)
+    if n is None:
+        if len(_WS_BYTES) > 4096:
+            _WS_BYTES.clear()
+        n = _WS_BYTES[key] = int(_lib.lib.dwconv_b200_backward_filter_workspace_bytes(code, s))
+    return n
 
 
 class DepthwiseConv2dFunction(Function):
@@ -58,7 +72,7 @@ class DepthwiseConv2dFunction(Function):
         shape = _forward_shape(input, kernel, stride, pad)
         out = torch.empty((shape.N, shape.C, shape.Ho, shape.Wo), dtype=input.dtype,
                           device=input.device)
-        with torch.cuda.device(input.device):
+        with _C._on_device(input):
             st = _lib.lib.dwconv_b200_forward(input.data_ptr(), kernel.data_ptr(), out.data_ptr(),
                                               code, shape, _C._stream(input))
         _lib.check(st, "forward")
@@ -84,11 +98,11 @@ class DepthwiseConv2dFunction(Function):
                                f"{(shape.N, shape.C, shape.Ho, shape.Wo)}")
         grad_output = grad_output.contiguous()
         grad_input = grad_kernel = None
-        with torch.cuda.device(input.device):
+        with _C._on_device(input):
             stream = _C._stream(input)
             want_dx, want_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
             if want_dw:
-                nbytes = _lib.lib.dwconv_b200_backward_filter_workspace_bytes(code, shape)
+                nbytes = _workspace_bytes(code, shape)
                 ws = torch.empty(nbytes, dtype=torch.uint8, device=input.device)
                 grad_kernel = torch.empty_like(kernel)
             if want_dx:

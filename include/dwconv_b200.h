@@ -68,7 +68,8 @@ typedef enum dwconv_b200_status {
 typedef enum dwconv_b200_path {
   DWCONV_B200_PATH_AUTO = 0,    /* choose per shape (default) */
   DWCONV_B200_PATH_DIRECT = 1,  /* one thread per output, any shape / dtype */
-  DWCONV_B200_PATH_ROWS = 2     /* bulk-copy staged row tiles, lane-per-column warps */
+  DWCONV_B200_PATH_ROWS = 2,    /* bulk-copy staged row tiles, lane-per-column warps */
+  DWCONV_B200_PATH_TILES = 3    /* shared-memory tiles, any padding and map size (3x3/5x5/7x7) */
 } dwconv_b200_path;
 
 /* Geometry of one depthwise convolution in forward terms.
@@ -205,6 +206,15 @@ DWCONV_B200_API int dwconv_b200_copy_async(void *dst, const void *src, size_t by
  *                     nothing is written on the first call).
  *   backward_exchange the same with the fused backward's first pass
  *                     (dwconv_b200_backward): dx is written too.
+ *   backward_filter_allreduce / backward_allreduce
+ *                     the same first passes, but the second pass, after
+ *                     sending, waits for the other ranks' words of THIS call
+ *                     and writes this call's world sum to dw: the whole
+ *                     all-reduce inside the kernel that finishes the gradient.
+ *                     For a step with nothing left to run behind the gradient
+ *                     (the pipelined form plus exchange_finish costs a second
+ *                     kernel and starts waiting later).  May be mixed freely
+ *                     with the pipelined calls on one object.
  *   exchange_finish   dw = the world sum of the latest call.  Waits for the
  *                     peers' words if they are still in flight.  A step that
  *                     needs its own sum before it ends calls this after the
@@ -238,6 +248,14 @@ DWCONV_B200_API int dwconv_b200_backward_exchange(const void *x, const void *dy,
                                                   void *dw_prev, void *workspace, size_t workspace_bytes,
                                                   int dtype, const dwconv_b200_shape *shape,
                                                   dwconv_b200_exchange *ex, void *stream);
+DWCONV_B200_API int dwconv_b200_backward_filter_allreduce(const void *x, const void *dy, void *dw,
+                                                          void *workspace, size_t workspace_bytes,
+                                                          int dtype, const dwconv_b200_shape *shape,
+                                                          dwconv_b200_exchange *ex, void *stream);
+DWCONV_B200_API int dwconv_b200_backward_allreduce(const void *x, const void *dy, const void *w, void *dx,
+                                                   void *dw, void *workspace, size_t workspace_bytes,
+                                                   int dtype, const dwconv_b200_shape *shape,
+                                                   dwconv_b200_exchange *ex, void *stream);
 
 /* ------------------------------------------------------------------------
  * Operator-form entry points: one per function of the reference's pybind

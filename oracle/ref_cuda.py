@@ -74,19 +74,24 @@ def time_layers(ref, layers, reps):
     import torch
     dts = {"f32": torch.float32, "f16": torch.float16}
     res = []
-    for (N, C, H, k, s, p, dt) in layers:
-        ho = (H + 2 * p - k) // s + 1
-        per_set = 2 * N * C * (H * H + ho * ho) * (2 if dt == "f16" else 4)
+    for layer in layers:
+        if len(layer) == 8:   # rectangular map: [N, C, H, W, k, stride, pad, dtype]
+            N, C, H, W, k, s, p, dt = layer
+        else:                 # square map: [N, C, H, k, stride, pad, dtype]
+            N, C, H, k, s, p, dt = layer
+            W = H
+        ho, wo = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+        per_set = 2 * N * C * (H * W + ho * wo) * (2 if dt == "f16" else 4)
         n_sets = max(2, min(8, int(2 * 126e6 // per_set) + 2))
         sets = []
         for si in range(n_sets):
             g = torch.Generator(device="cuda").manual_seed(si)
-            x = torch.randn((N, C, H, H), generator=g, device="cuda").to(dts[dt]).requires_grad_(True)
+            x = torch.randn((N, C, H, W), generator=g, device="cuda").to(dts[dt]).requires_grad_(True)
             w = (torch.randn((C, 1, k, k), generator=g, device="cuda") / k).to(dts[dt]).requires_grad_(True)
-            dy = torch.randn((N, C, ho, ho), generator=g, device="cuda").to(dts[dt])
+            dy = torch.randn((N, C, ho, wo), generator=g, device="cuda").to(dts[dt])
             sets.append((x, w, dy))
         if not served_by_reference_kernels(ref, sets[0][0], sets[0][1], s, p):
-            res.append({"layer": [N, C, H, k, s, p, dt], "served": False})
+            res.append({"layer": list(layer), "served": False})
             continue
 
         def fwd(i):
@@ -112,7 +117,7 @@ def time_layers(ref, layers, reps):
             z.record()
             torch.cuda.synchronize()
             times[name] = a.elapsed_time(z) / reps
-        res.append({"layer": [N, C, H, k, s, p, dt], "served": True,
+        res.append({"layer": list(layer), "served": True,
                     "forward_ms": round(times["forward"], 5),
                     "forward_backward_ms": round(times["forward_backward"], 5),
                     "buffer_sets": n_sets})
@@ -126,7 +131,8 @@ def main():
     ap.add_argument("--cases")
     ap.add_argument("--out")
     ap.add_argument("--time", action="store_true")
-    ap.add_argument("--layers", help="JSON list of [N, C, H, k, stride, pad, dtype]")
+    ap.add_argument("--layers", help="JSON list of [N, C, H, k, stride, pad, dtype] or "
+                                     "[N, C, H, W, k, stride, pad, dtype]")
     ap.add_argument("--reps", type=int, default=50)
     a = ap.parse_args()
     ref = load_reference()

@@ -69,6 +69,15 @@ def _worker(rank, world, port, q, scenario="sharding"):
                 assert torch.equal(both[0], both[1]), "ranks disagree on the exchanged dW"
                 err = (got.double().cpu() - truth).abs().max().item()
                 assert err <= rel * truth.abs().max().item(), err
+            # the whole sum inside the finishing kernel (it waits for the peer's values itself),
+            # interleaved with the pipelined form on the same object
+            dys0 = shard_batch(dy, world, rank).cuda()
+            for rep in range(3):
+                got2 = ex.allreduce_backward_filter(xs.detach(), dys0, s, p)
+                torch.cuda.synchronize()
+                assert torch.equal(got2, got), "all-reduce form differs from start + finish"
+                if rep == 1:
+                    assert torch.equal(ex.backward_filter(xs.detach(), dys0, s, p), got)
             # pipelined form: the second start() delivers the first call's sum
             dys = shard_batch(dy, world, rank).cuda()
             first = torch.full_like(got, float("nan"))

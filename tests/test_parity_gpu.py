@@ -12,7 +12,8 @@ from gpu_util import (c_backward, c_backward_filter, c_backward_input, c_forward
 
 pytestmark = pytest.mark.gpu
 
-PATHS = {"auto": _lib.PATH_AUTO, "direct": _lib.PATH_DIRECT, "rows": _lib.PATH_ROWS}
+PATHS = {"auto": _lib.PATH_AUTO, "direct": _lib.PATH_DIRECT, "rows": _lib.PATH_ROWS,
+         "tiles": _lib.PATH_TILES}
 
 
 def _check_three_ops(x, w, dy, stride, padding, dt, path, what, exact=True):
@@ -41,12 +42,14 @@ def _check_three_ops(x, w, dy, stride, padding, dt, path, what, exact=True):
     assert _lib.lib.dwconv_b200_device_status() == 0, f"{what}: a bounded wait expired in a kernel"
     res = {}
     for key, (st, t, used) in out.items():
-        if path == "rows" and st == 6:
+        if path in ("rows", "tiles") and st == 6:
             res[key] = None  # the forced family does not serve this shape; that is a status, not UB
             continue
         assert st == 0, f"{what}/{key}: status {st} ({_lib.status_string(st)})"
         if path == "rows":
             assert used == _lib.PATH_ROWS
+        if path == "tiles":
+            assert used == _lib.PATH_TILES
         if path == "direct":
             assert used == _lib.PATH_DIRECT
         assert not torch.isnan(t).any(), f"{what}/{key}: output not fully written"
@@ -69,7 +72,7 @@ def _check_three_ops(x, w, dy, stride, padding, dt, path, what, exact=True):
     return res
 
 
-@pytest.mark.parametrize("path", ["auto", "direct", "rows"])
+@pytest.mark.parametrize("path", ["auto", "direct", "rows", "tiles"])
 @pytest.mark.parametrize("name", case_names())
 def test_golden_cases(name, path):
     g = golden()
@@ -115,6 +118,8 @@ def test_reference_forward_cases(case):
     C, H, W, k, s, p = case
     x, w, dy = seeded((32, C, H, W), (k, k), s, p, torch.float32, seed=sum(case))
     custom = dwconv_b200.depthwise_conv2d(x, w, stride=s, padding=p)
+    # every one of them runs on a staged-tile kernel, none on the one-thread-per-output family
+    assert last_path() in (_lib.PATH_ROWS, _lib.PATH_TILES)
     native = F.conv2d(x, w, stride=s, padding=p, groups=C)
     assert (native - custom).abs().max().item() <= 1e-5 * k * k
     assert torch.equal(custom.cpu(), oracle.forward_seq(x, w, s, p))
@@ -172,7 +177,7 @@ for _dt in ("f32", "f16"):
             SWEEP.append((_dt, _H, _W, _k, _s, _p))
 
 
-@pytest.mark.parametrize("path", ["auto", "rows"])
+@pytest.mark.parametrize("path", ["auto", "rows", "tiles"])
 @pytest.mark.parametrize("cfg", SWEEP, ids=lambda c: "-".join(map(str, c)))
 def test_shape_sweep(cfg, path):
     """Map sizes either side of every tiling boundary x filter / stride / padding classes,
@@ -341,6 +346,10 @@ def test_exchange_entry_point_with_one_rank_equals_plain(shape, k, s, p, dtype):
     for _ in range(4):
         got = ex.backward_filter(x, dy, s, p)
         assert torch.equal(got, want)
+    # the all-reduce form gives this call's sum at once, and mixes with the other form
+    for _ in range(3):
+        assert torch.equal(ex.allreduce_backward_filter(x, dy, s, p), want)
+    assert torch.equal(ex.backward_filter(x, dy, s, p), want)
     # pipelined form: a later start() delivers the earlier call's result
     earlier = torch.full_like(want, float("nan"))
     ex.start(x, dy, s, p)
@@ -351,6 +360,34 @@ def test_exchange_entry_point_with_one_rank_equals_plain(shape, k, s, p, dtype):
     assert st2 == 0 and torch.equal(later, want2)
     assert _lib.lib.dwconv_b200_device_status() == 0
     ex.close()
+
+
+TILES_CASES = [
+    # (N, C, H, W, k, stride, padding): no padding, odd widths, maps wider than 128 columns,
+    # paddings other than k/2 (smaller, larger, different per axis), tiles that end mid-map
+    (2, 3, 64, 64, 3, 1, 0), (2, 3, 64, 64, 5, 2, 0), (2, 3, 64, 64, 5, 1, 0), (2, 3, 64, 64, 3, 2, 0),
+    (1, 2, 63, 65, 5, 1, 2), (1, 2, 63, 65, 3, 2, 1), (1, 2, 63, 65, 3, 1, 1), (1, 2, 63, 65, 5, 2, 2),
+    (1, 2, 224, 224, 3, 1, 1), (1, 2, 224, 224, 3, 2, 1), (1, 3, 150, 130, 7, 1, 3),
+    (1, 3, 130, 150, 7, 2, 3), (2, 2, 40, 200, 5, 1, 1), (1, 2, 50, 70, 5, 1, (0, 2)),
+    (1, 2, 40, 40, 3, 1, 2), (1, 2, 33, 35, 5, 2, (4, 1)), (2, 2, 40, 300, 7, 2, 0),
+    (1, 1, 97, 33, 3, 1, 0), (1, 2, 129, 129, 7, 1, 6),
+]
+
+
+@pytest.mark.parametrize("dtn", ["f32", "f16"])
+@pytest.mark.parametrize("cfg", TILES_CASES, ids=lambda c: "x".join(map(str, c)))
+def test_tiles_family(cfg, dtn):
+    """The shared-memory tile kernels on the geometries the rows family declines, forced and
+    as the automatic choice: bit-identical to the sequential-order oracle."""
+    N, C, H, W, k, s, p = cfg
+    dt = NP_DT[dtn]
+    x, w, dy = seeded((N, C, H, W), (k, k), s, p, dt, seed=H + W + k)
+    res = _check_three_ops(x, w, dy, s, p, dt, "tiles", f"tiles{cfg}")
+    assert res["y"] is not None and res["dx"] is not None and res["dw"] is not None
+    _check_three_ops(x, w, dy, s, p, dt, "auto", f"tiles{cfg}[auto]")
+    with forced_path(_lib.PATH_AUTO):
+        st, _ = c_forward(x, w, s, p)
+        assert st == 0 and last_path() in (_lib.PATH_ROWS, _lib.PATH_TILES)
 
 
 FUSED_CASES = [
@@ -503,7 +540,7 @@ def test_bfloat16_against_oracle(shape, k, s, p):
     xf, wf, dyf = x.float().cpu(), w.float().cpu(), dy.float().cpu()
     H, W = shape[2:]
     st, y = c_forward(x, w, s, p)
-    assert st == 0 and last_path() == _lib.PATH_DIRECT
+    assert st == 0 and last_path() in (_lib.PATH_DIRECT, _lib.PATH_TILES)  # never the rows family
     st, dx = c_backward_input(dy, w, (H, W), s, p)
     assert st == 0
     st, dw = c_backward_filter(x, dy, k, s, p)
