@@ -105,9 +105,19 @@ int try_rows_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<
 }
 
 template <typename T>
-int forward_t(const void *x, const void *w, void *y, const Shape &s, cudaStream_t st, int forced) {
+int try_rows_forward_epilogue(const T *x, const T *w, T *y, const Shape &s, const EpilogueArgs &ep,
+                              cudaStream_t st) {
+  if constexpr (kRowsCompiled<T>) return rows_forward_epilogue<T>(x, w, y, s, ep, st);
+  return ROWS_DECLINED;
+}
+
+template <typename T>
+int forward_t(const void *x, const void *w, void *y, const Shape &s, cudaStream_t st, int forced,
+              const EpilogueArgs &ep) {
   if (forced == DWCONV_B200_PATH_AUTO || forced == DWCONV_B200_PATH_ROWS) {
-    int r = try_rows_forward<T>((const T *)x, (const T *)w, (T *)y, s, st);
+    // large filters have no epilogue variant in the rows family: they go on to the general kernels
+    int r = ep.on ? try_rows_forward_epilogue<T>((const T *)x, (const T *)w, (T *)y, s, ep, st)
+                  : try_rows_forward<T>((const T *)x, (const T *)w, (T *)y, s, st);
     if (r == ROWS_SERVED) {
       t_last_path = DWCONV_B200_PATH_ROWS;
       return launch_status();
@@ -115,7 +125,7 @@ int forward_t(const void *x, const void *w, void *y, const Shape &s, cudaStream_
     if (forced == DWCONV_B200_PATH_ROWS) return DWCONV_B200_UNSUPPORTED_SHAPE;
   }
   if (forced == DWCONV_B200_PATH_AUTO || forced == DWCONV_B200_PATH_TILES) {
-    if (tiles_forward<T>((const T *)x, (const T *)w, (T *)y, s, st) == ROWS_SERVED) {
+    if (tiles_forward<T>((const T *)x, (const T *)w, (T *)y, s, ep, st) == ROWS_SERVED) {
       t_last_path = DWCONV_B200_PATH_TILES;
       return launch_status();
     }
@@ -123,7 +133,7 @@ int forward_t(const void *x, const void *w, void *y, const Shape &s, cudaStream_
   }
   const long long total = (long long)s.N * s.C * s.Ho * s.Wo;
   direct_forward_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T *)x, (const T *)w,
-                                                                 (T *)y, s, total);
+                                                                 (T *)y, s, total, ep);
   t_last_path = DWCONV_B200_PATH_DIRECT;
   return launch_status();
 }
@@ -162,6 +172,8 @@ size_t filter_workspace_t(const Shape &s) {
   if (rs > slices) slices = rs;
   const size_t fs = (size_t)try_rows_backward_slices<T>(s);  // the fused backward shares the workspace
   if (fs > slices) slices = fs;
+  const size_t ns = (size_t)nhwc_filter_slices(s);  // and so do the channels-last kernels
+  if (ns > slices) slices = ns;
   size_t b = (size_t)s.C * slices * kk * sizeof(A);
   return b < 16 ? 16 : ((b + 15) / 16) * 16;
 }
@@ -567,8 +579,8 @@ int dwconv_b200_out_size(int in, int up, int pad0, int pad1, int k, int down) {
   return (int)(num / down);
 }
 
-int dwconv_b200_forward(const void *x, const void *w, void *y, int dtype,
-                        const dwconv_b200_shape *shape, void *stream) {
+static int forward_call(const void *x, const void *w, void *y, int dtype,
+                        const dwconv_b200_shape *shape, const EpilogueArgs &ep, void *stream) {
   int e = check_ptrs(dtype, x, w, y);
   if (e) return e;
   e = check_shape(shape);
@@ -576,11 +588,35 @@ int dwconv_b200_forward(const void *x, const void *w, void *y, int dtype,
   cudaStream_t st = (cudaStream_t)stream;
   const int forced = g_forced_path.load();
   switch (dtype) {
-    case DWCONV_B200_F32: return forward_t<float>(x, w, y, *shape, st, forced);
-    case DWCONV_B200_F16: return forward_t<__half>(x, w, y, *shape, st, forced);
-    case DWCONV_B200_BF16: return forward_t<__nv_bfloat16>(x, w, y, *shape, st, forced);
-    default: return forward_t<double>(x, w, y, *shape, st, forced);
+    case DWCONV_B200_F32: return forward_t<float>(x, w, y, *shape, st, forced, ep);
+    case DWCONV_B200_F16: return forward_t<__half>(x, w, y, *shape, st, forced, ep);
+    case DWCONV_B200_BF16: return forward_t<__nv_bfloat16>(x, w, y, *shape, st, forced, ep);
+    default: return forward_t<double>(x, w, y, *shape, st, forced, ep);
   }
+}
+
+int dwconv_b200_forward(const void *x, const void *w, void *y, int dtype,
+                        const dwconv_b200_shape *shape, void *stream) {
+  return forward_call(x, w, y, dtype, shape, EpilogueArgs{nullptr, nullptr, 0, 0}, stream);
+}
+
+int dwconv_b200_forward_epilogue(const void *x, const void *w, void *y, int dtype,
+                                 const dwconv_b200_shape *shape, const dwconv_b200_epilogue *epilogue,
+                                 void *stream) {
+  EpilogueArgs ep{nullptr, nullptr, 0, 0};
+  if (epilogue != nullptr) {
+    if (epilogue->activation < DWCONV_B200_ACT_NONE || epilogue->activation > DWCONV_B200_ACT_HARDSWISH)
+      return DWCONV_B200_BAD_ARGUMENT;
+    const size_t es = elem_size(dtype);
+    if (es != 0 && ((epilogue->scale != nullptr && !aligned_to(epilogue->scale, es)) ||
+                    (epilogue->bias != nullptr && !aligned_to(epilogue->bias, es))))
+      return DWCONV_B200_MISALIGNED;
+    ep.scale = epilogue->scale;
+    ep.bias = epilogue->bias;
+    ep.act = epilogue->activation;
+    ep.on = (ep.scale != nullptr || ep.bias != nullptr || ep.act != DWCONV_B200_ACT_NONE) ? 1 : 0;
+  }
+  return forward_call(x, w, y, dtype, shape, ep, stream);
 }
 
 int dwconv_b200_backward_input(const void *dy, const void *w, void *dx, int dtype,
@@ -672,6 +708,87 @@ int dwconv_b200_backward_accumulate(const void *x, const void *dy, const void *w
                                     const dwconv_b200_shape *shape, void *stream) {
   return backward_call(x, dy, w, dx, dw_acc, workspace, workspace_bytes, dtype, shape, stream, true,
                        accumulate ? 1 : 0);
+}
+
+}  // extern "C"
+
+// ---- channels-last (NHWC) operators ----
+namespace {
+
+template <typename T>
+int nhwc_call_t(int op, const void *a, const void *b, void *c, void *ws, size_t ws_bytes, const Shape &s,
+                const EpilogueArgs &ep, cudaStream_t st) {
+  using A = typename Elem<T>::acc_t;
+  int r = ROWS_DECLINED;
+  if (op == 0) {
+    r = nhwc_forward<T>((const T *)a, (const T *)b, (T *)c, s, ep, st);
+  } else if (op == 1) {
+    r = nhwc_backward_input<T>((const T *)a, (const T *)b, (T *)c, s, st);
+  } else {
+    if (ws_bytes < filter_workspace_t<T>(s)) return DWCONV_B200_WORKSPACE_TOO_SMALL;
+    int S = 0;
+    r = nhwc_backward_filter<T>((const T *)a, (const T *)b, (A *)ws, s, st, &S);
+    if (r == ROWS_SERVED) {
+      int e = launch_status();
+      if (e != DWCONV_B200_OK) return e;
+      const int kk = s.kh * s.kw;
+      cudaLaunchAttribute attr[1];
+      cudaLaunchConfig_t cfg = finalize_config(finalize_blocks(s.C, kk), st, attr);
+      (void)cudaLaunchKernelEx(&cfg, backward_filter_finalize_kernel<T>, (const A *)ws, (T *)c, s.C, kk, S);
+    }
+  }
+  if (r != ROWS_SERVED) return DWCONV_B200_UNSUPPORTED_SHAPE;
+  return launch_status();
+}
+
+int nhwc_call(int op, const void *a, const void *b, void *c, void *ws, size_t ws_bytes, int dtype,
+              const dwconv_b200_shape *shape, const EpilogueArgs &ep, void *stream) {
+  int e = check_ptrs(dtype, a, b, c);
+  if (e) return e;
+  e = check_shape(shape);
+  if (e) return e;
+  if (op == 2) {
+    if (ws == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+    if (!aligned_to(ws, 16)) return DWCONV_B200_MISALIGNED;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case DWCONV_B200_F32: return nhwc_call_t<float>(op, a, b, c, ws, ws_bytes, *shape, ep, st);
+    case DWCONV_B200_F16: return nhwc_call_t<__half>(op, a, b, c, ws, ws_bytes, *shape, ep, st);
+    case DWCONV_B200_BF16: return nhwc_call_t<__nv_bfloat16>(op, a, b, c, ws, ws_bytes, *shape, ep, st);
+    default: return DWCONV_B200_UNSUPPORTED_SHAPE;  // fp64: make the maps contiguous NCHW
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int dwconv_b200_forward_nhwc(const void *x, const void *w, void *y, int dtype,
+                             const dwconv_b200_shape *shape, const dwconv_b200_epilogue *epilogue,
+                             void *stream) {
+  EpilogueArgs ep{nullptr, nullptr, 0, 0};
+  if (epilogue != nullptr) {
+    if (epilogue->activation < DWCONV_B200_ACT_NONE || epilogue->activation > DWCONV_B200_ACT_HARDSWISH)
+      return DWCONV_B200_BAD_ARGUMENT;
+    ep.scale = epilogue->scale;
+    ep.bias = epilogue->bias;
+    ep.act = epilogue->activation;
+    ep.on = (ep.scale != nullptr || ep.bias != nullptr || ep.act != DWCONV_B200_ACT_NONE) ? 1 : 0;
+  }
+  return nhwc_call(0, x, w, y, nullptr, 0, dtype, shape, ep, stream);
+}
+
+int dwconv_b200_backward_input_nhwc(const void *dy, const void *w, void *dx, int dtype,
+                                    const dwconv_b200_shape *shape, void *stream) {
+  return nhwc_call(1, dy, w, dx, nullptr, 0, dtype, shape, EpilogueArgs{nullptr, nullptr, 0, 0}, stream);
+}
+
+int dwconv_b200_backward_filter_nhwc(const void *x, const void *dy, void *dw, void *workspace,
+                                     size_t workspace_bytes, int dtype,
+                                     const dwconv_b200_shape *shape, void *stream) {
+  return nhwc_call(2, x, dy, dw, workspace, workspace_bytes, dtype, shape,
+                   EpilogueArgs{nullptr, nullptr, 0, 0}, stream);
 }
 
 int dwconv_b200_use_dwconv2d_small(int in_h, int in_w, int kh, int kw, int up_h, int up_w,

@@ -43,6 +43,40 @@ template <> struct Elem<double> {
 __device__ __forceinline__ float fma_acc(float a, float b, float c) { return fmaf(a, b, c); }
 __device__ __forceinline__ double fma_acc(double a, double b, double c) { return fma(a, b, c); }
 
+// Optional epilogue of the forward operator, applied to the accumulator before the one rounding
+// to the storage type: v = act(acc * scale[c] + bias[c]).  The reference has no such thing (it
+// rejects a bias outright, torch_dwconv/dwconv.py:108-109); the blocks that use depthwise
+// convolutions follow them with exactly this (folded batch-norm scale and shift, activation),
+// which otherwise costs another read and write of the output map.
+struct EpilogueArgs {
+  const void *scale;  // [C] in the tensors' element type, or null (1)
+  const void *bias;   // [C] or null (0)
+  int act;            // dwconv_b200_activation
+  int on;             // 0: plain forward
+};
+template <typename A> __device__ __forceinline__ A apply_activation(A v, int act) {
+  switch (act) {
+    case DWCONV_B200_ACT_RELU: return v > A(0) ? v : A(0);
+    case DWCONV_B200_ACT_RELU6: return v < A(0) ? A(0) : (v > A(6) ? A(6) : v);
+    case DWCONV_B200_ACT_SILU: return v / (A(1) + exp(-v));
+    case DWCONV_B200_ACT_HARDSWISH: {
+      const A t = v + A(3);
+      return v * (t < A(0) ? A(0) : (t > A(6) ? A(6) : t)) / A(6);
+    }
+    default: return v;
+  }
+}
+template <typename A> __device__ __forceinline__ A apply_epilogue(A acc, A sc, A bi, int act) {
+  return apply_activation<A>(fma_acc(acc, sc, bi), act);
+}
+// scale and bias of channel c as accumulator values
+template <typename T>
+__device__ __forceinline__ void epilogue_coeffs(const EpilogueArgs &ep, int c,
+                                                typename Elem<T>::acc_t &sc, typename Elem<T>::acc_t &bi) {
+  sc = ep.scale ? Elem<T>::ld(static_cast<const T *>(ep.scale) + c) : typename Elem<T>::acc_t(1);
+  bi = ep.bias ? Elem<T>::ld(static_cast<const T *>(ep.bias) + c) : typename Elem<T>::acc_t(0);
+}
+
 // Programmatic dependent launch.  A kernel launched with the programmatic-serialization
 // attribute may become resident while the kernel before it in the stream is still running (as soon
 // as every CTA of that kernel has called pdl_launch_dependents() or exited); it must call

@@ -13,7 +13,7 @@ namespace dwb {
 template <typename T>
 __global__ void __launch_bounds__(256)
 direct_forward_kernel(const T *__restrict__ x, const T *__restrict__ w, T *__restrict__ y,
-                      const Shape s, const long long total) {
+                      const Shape s, const long long total, const EpilogueArgs ep) {
   using A = typename Elem<T>::acc_t;
   const long long step = (long long)gridDim.x * blockDim.x;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
@@ -36,6 +36,11 @@ direct_forward_kernel(const T *__restrict__ x, const T *__restrict__ w, T *__res
         if (yok & (ix >= 0) & (ix < s.W)) v = Elem<T>::ld(xp + (long long)iy * s.W + ix);
         acc = fma_acc(v, Elem<T>::ld(wp + ky * s.kw + kx), acc);
       }
+    }
+    if (ep.on) {
+      A sc, bi;
+      epilogue_coeffs<T>(ep, c, sc, bi);
+      acc = apply_epilogue<A>(acc, sc, bi, ep.act);
     }
     y[idx] = Elem<T>::from_acc(acc);
   }

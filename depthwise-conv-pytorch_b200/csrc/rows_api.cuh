@@ -10,6 +10,10 @@ namespace dwb {
 enum { ROWS_DECLINED = 0, ROWS_SERVED = 1 };
 
 template <typename T> int rows_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st);
+// The forward with a fused epilogue (rows_conv_epi.cu); 3x3 / 5x5 / 7x7 only.
+template <typename T>
+int rows_forward_epilogue(const T *x, const T *w, T *y, const Shape &s, const EpilogueArgs &ep,
+                          cudaStream_t st);
 template <typename T>
 int rows_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStream_t st);
 // Batch/row slices per channel the first pass would use (0: declines); sizes the workspace.
@@ -26,12 +30,24 @@ int rows_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<T>::
                   const Shape &s, cudaStream_t st, int *slices_out);
 
 // Tiles family (tiles.cu): any padding, any map size; 3x3 / 5x5 / 7x7; fp32, fp16, bf16.
-template <typename T> int tiles_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st);
+template <typename T>
+int tiles_forward(const T *x, const T *w, T *y, const Shape &s, const EpilogueArgs &ep, cudaStream_t st);
 template <typename T>
 int tiles_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStream_t st);
 template <typename T>
 int tiles_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *partial, const Shape &s,
                           int slices, cudaStream_t st);
+
+// Channels-last (NHWC) operators (nhwc.cu): 3x3 / 5x5 / 7x7, stride 1 or 2, any padding; fp32,
+// fp16, bf16.
+int nhwc_filter_slices(const Shape &s);
+template <typename T>
+int nhwc_forward(const T *x, const T *w, T *y, const Shape &s, const EpilogueArgs &ep, cudaStream_t st);
+template <typename T>
+int nhwc_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStream_t st);
+template <typename T>
+int nhwc_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *partial, const Shape &s,
+                         cudaStream_t st, int *slices_out);
 
 // Reads and clears the flags kernels raise when a bounded wait expires (synchronises the
 // device).  Bit 0: forward/backward-input kernels, bit 1: backward-filter kernels.

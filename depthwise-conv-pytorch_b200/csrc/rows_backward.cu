@@ -65,6 +65,10 @@ template <typename T, int K, int S>
 bool plan_backward_ks(const Shape &s, bool a16, BackwardPlan &f) {
   constexpr int MODE = (S == 1) ? MODE_FWD : MODE_BWD;
   if (!pick_v(S, s.W, s.Wo, a16, f.VI, f.VO)) return false;
+  // Where the one-CTA-per-SM fused kernel measured slower than the two operators run one after
+  // the other (32x32 maps, four columns per lane: 5x5 fp32 65 against 51 us, 7x7 fp32 108
+  // against 104 us), the caller falls back to them.
+  if (S == 1 && f.VO == 4 && (K == 5 || (K == 7 && sizeof(T) == 4))) return false;
   const int lanes_in = ceil_div(s.Wo, f.VI);
   const int lanes = max(lanes_in, ceil_div(s.W, f.VO));
   RowsBackwardParams &p = f.p;
@@ -164,7 +168,10 @@ int launch_backward_u(const BackwardPlan &f, cudaStream_t st) {
 template <typename T, int K, int S>
 int launch_backward(const BackwardPlan &f, cudaStream_t st) {
   if (S == 1) {
-    if (f.VI == 4) return launch_backward_u<T, K, 1, 4, 4, 0>(f, st);
+    // (the variants the planner never picks, see plan_backward_ks, are not compiled)
+    if constexpr (!(K == 5 || (K == 7 && sizeof(T) == 4))) {
+      if (f.VI == 4) return launch_backward_u<T, K, 1, 4, 4, 0>(f, st);
+    }
     if (f.VI == 2) return launch_backward_u<T, K, 1, 2, 2, 0>(f, st);
     return launch_backward_u<T, K, 1, 1, 1, 0>(f, st);
   }

@@ -1,183 +1,10 @@
-// Rows family, forward and backward-input: variant selection and launches.
-#include "rows_plan.cuh"
+// Rows family, forward and backward-input: the plain operators.
+#include "rows_conv_impl.cuh"
 
 namespace dwb {
 
 template <typename T> int rows_bigk_conv(const RowsParams &p, int K, cudaStream_t st);  // rows_bigk.cu
 int rows_bigk_take_error();
-
-namespace {
-
-__device__ int g_conv_error_flag;
-
-// When set (rows_debug_conv_plan), the selected variant and tiling are written here and
-// nothing is launched.
-thread_local int *t_plan_out = nullptr;
-
-template <typename T> struct RowsDtype { static constexpr bool ok = false; };
-template <> struct RowsDtype<float> { static constexpr bool ok = true; };
-template <> struct RowsDtype<__half> { static constexpr bool ok = true; };
-
-constexpr int conv_minb(int K) { return K <= 5 ? 2 : 1; }  // 49 tap registers: one CTA per SM
-
-// Rows-per-chunk choices compiled for each (K, S, MODE); the planner picks per shape.
-template <int K, int S, int MODE> struct ConvU;
-template <> struct ConvU<3, 1, MODE_FWD> { static constexpr int n = 3; static constexpr int v[4] = {4, 7, 8, 8}; };  // 14 measured slower than 7 on 14-row maps
-template <> struct ConvU<5, 1, MODE_FWD> { static constexpr int n = 2; static constexpr int v[4] = {4, 7, 7, 7}; };
-template <> struct ConvU<7, 1, MODE_FWD> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };  // 4 measured the same (no spill, 33.1 vs 32.7 us on 32x32 maps)
-template <> struct ConvU<3, 2, MODE_FWD> { static constexpr int n = 3; static constexpr int v[4] = {2, 4, 7, 7}; };
-template <> struct ConvU<5, 2, MODE_FWD> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };  // 4 measured slower (and spills at VI = 4)
-template <> struct ConvU<7, 2, MODE_FWD> { static constexpr int n = 1; static constexpr int v[4] = {2, 2, 2, 2}; };
-template <> struct ConvU<3, 2, MODE_BWD> { static constexpr int n = 3; static constexpr int v[4] = {4, 8, 14, 14}; };
-template <> struct ConvU<5, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[4] = {4, 14, 14, 14}; };
-template <> struct ConvU<7, 2, MODE_BWD> { static constexpr int n = 2; static constexpr int v[4] = {2, 4, 4, 4}; };
-
-// Options above this height spill registers for the given vector width (ptxas -v) and measured
-// slower; the tables are ascending, so a cap keeps a prefix.
-constexpr int conv_u_cap(int K, int S, int mode, int VI) {
-  if (VI == 4 && K == 3 && S == 1) return 8;
-  if (VI == 4 && K == 5 && S == 1) return 4;
-  return 1 << 20;
-}
-template <int K, int S, int MODE, int VI> constexpr int conv_u_count() {
-  int n = 0;
-  for (int i = 0; i < ConvU<K, S, MODE>::n; ++i)
-    if (ConvU<K, S, MODE>::v[i] <= conv_u_cap(K, S, MODE, VI)) ++n;
-  return n;
-}
-
-int *conv_flag_address() {
-  static std::atomic<int *> cached[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  int *p = cached[dev].load(std::memory_order_acquire);
-  if (p == nullptr) {
-    if (cudaGetSymbolAddress((void **)&p, g_conv_error_flag) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return nullptr;
-    }
-    cached[dev].store(p, std::memory_order_release);
-  }
-  return p;
-}
-
-template <typename T, int K, int S, int MODE, int VI, int VO, int U, bool MASK, bool EXACT>
-int launch_variant(const RowsParams &p, cudaStream_t st) {
-  constexpr int MINB = conv_minb(K);
-  auto kernel = rows_conv_kernel<T, K, S, MODE, VI, VO, U, MASK, EXACT, MINB>;
-  static std::atomic<unsigned long long> smem_done{0};
-  if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
-  int *flag = conv_flag_address();
-  if (flag == nullptr) return ROWS_DECLINED;
-  const int grid = (int)min((long long)sm_count() * MINB, (long long)p.ntiles);
-  launch_dependent(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, p, flag);
-  return ROWS_SERVED;
-}
-
-// Dispatch on the planner's runtime choices (U among the compiled options, mask, exact).
-template <typename T, int K, int S, int MODE, int VI, int VO, int I>
-int launch_u(const RowsParams &p, int U, bool mask, bool exact, cudaStream_t st) {
-  constexpr int UI = ConvU<K, S, MODE>::v[I];
-  constexpr int N = conv_u_count<K, S, MODE, VI>();
-  if (U == UI || I + 1 >= N) {
-    if (mask)
-      return exact ? launch_variant<T, K, S, MODE, VI, VO, UI, true, true>(p, st)
-                   : launch_variant<T, K, S, MODE, VI, VO, UI, true, false>(p, st);
-    return exact ? launch_variant<T, K, S, MODE, VI, VO, UI, false, true>(p, st)
-                 : launch_variant<T, K, S, MODE, VI, VO, UI, false, false>(p, st);
-  }
-  if constexpr (I + 1 < N)
-    return launch_u<T, K, S, MODE, VI, VO, I + 1>(p, U, mask, exact, st);
-  else
-    return ROWS_DECLINED;
-}
-
-template <typename T, int K, int S, int MODE, int VI, int VO>
-int launch_conv(RowsParams p, cudaStream_t st) {
-  using Geo = RowsGeo<K, S, MODE, VI, VO, ConvU<K, S, MODE>::v[0]>;  // column geometry: U-independent
-  const int lanes_in = ceil_div(p.Win, VI);
-  const int lanes = max(lanes_in, ceil_div(p.Wout, VO));
-  p.LW = pick_lw(lanes);
-  if (p.LW == 0) return ROWS_DECLINED;
-  PlanInput in{K, S, MODE, p.Hin, p.Win, p.Hout, p.Wout, (int)sizeof(T),
-               ROWS_CWARPS * (32 / p.LW), p.NC, 0, sm_count() * conv_minb(K), false};
-  const TilePlan t = plan_best(in, ConvU<K, S, MODE>::v, conv_u_count<K, S, MODE, VI>());
-  if (!t.ok) return ROWS_DECLINED;
-  p.G = t.G; p.NRT = t.NRT; p.TH = t.TH; p.NRB = t.NRB; p.RBH = t.RBH;
-  p.inv_NRB = magic_of(p.NRB);
-  p.NST = t.NST;
-  p.TAPB = t.TAPB;
-  const long long ntiles = (long long)ceil_div(p.NC, p.G) * p.NRT;
-  if (ntiles > (1ll << 30)) return ROWS_DECLINED;
-  p.ntiles = (int)ntiles;
-  // halo columns reach this many lanes to either side; spare (zero) lanes at the end of each
-  // segment make explicit masking unnecessary
-  constexpr int halo_lanes = (-Geo::fdiv(Geo::CMIN, VI) > Geo::fdiv(Geo::CMAX, VI))
-                                 ? -Geo::fdiv(Geo::CMIN, VI)
-                                 : Geo::fdiv(Geo::CMAX, VI);
-  const bool mask = (p.LW - lanes_in) < halo_lanes;
-  if (t_plan_out != nullptr) {
-    const int v[24] = {VI, VO, t.U, mask ? 1 : 0, p.LW, p.G, p.NRT, p.TH, p.NRB, p.RBH, p.NST,
-                       t.exact ? 1 : 0, 0, p.TAPB, 0, 0, p.ntiles, 0, MODE, 0, 0, 0, 0, 0};
-    for (int i = 0; i < 24; ++i) t_plan_out[i] = v[i];
-    return ROWS_SERVED;
-  }
-  return launch_u<T, K, S, MODE, VI, VO, 0>(p, t.U, mask, t.exact, st);
-}
-
-// Picks the widest per-lane vector the widths and pointers allow.
-template <typename T, int K, int S, int MODE>
-int select_conv(const RowsParams &p, cudaStream_t st) {
-  const bool a16 = ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(p.out)) & 15) == 0;
-  if (S == 1) {
-    if (a16 && p.Win % 4 == 0 && p.Wout % 4 == 0 && p.Win <= 128 && p.Wout <= 128 && p.Win > 16)
-      return launch_conv<T, K, 1, MODE_FWD, 4, 4>(p, st);
-    if (a16 && p.Win % 2 == 0 && p.Wout % 2 == 0 && p.Win <= 64 && p.Wout <= 64 && p.Win > 8)
-      return launch_conv<T, K, 1, MODE_FWD, 2, 2>(p, st);
-    if (p.Win <= 32 && p.Wout <= 32) return launch_conv<T, K, 1, MODE_FWD, 1, 1>(p, st);
-    return ROWS_DECLINED;
-  }
-  if (MODE == MODE_FWD) {
-    if (a16 && p.Win % 4 == 0 && p.Wout % 2 == 0 && p.Win <= 128 && p.Wout <= 64 && p.Win > 16)
-      return launch_conv<T, K, 2, MODE_FWD, 4, 2>(p, st);
-    if (a16 && p.Win % 2 == 0 && p.Win <= 64 && p.Wout <= 32)
-      return launch_conv<T, K, 2, MODE_FWD, 2, 1>(p, st);
-    return ROWS_DECLINED;
-  }
-  if (a16 && p.Win % 2 == 0 && p.Wout % 4 == 0 && p.Win <= 64 && p.Wout <= 128 && p.Wout > 16)
-    return launch_conv<T, K, 2, MODE_BWD, 2, 4>(p, st);
-  if (a16 && p.Wout % 2 == 0 && p.Win <= 32 && p.Wout <= 64)
-    return launch_conv<T, K, 2, MODE_BWD, 1, 2>(p, st);
-  return ROWS_DECLINED;
-}
-
-template <typename T, int MODE>
-int select_k(const RowsParams &p, int K, int S, cudaStream_t st) {
-  switch (K * 10 + S) {
-    case 31: return select_conv<T, 3, 1, MODE_FWD>(p, st);
-    case 51: return select_conv<T, 5, 1, MODE_FWD>(p, st);
-    case 71: return select_conv<T, 7, 1, MODE_FWD>(p, st);
-    case 32: return select_conv<T, 3, 2, MODE>(p, st);
-    case 52: return select_conv<T, 5, 2, MODE>(p, st);
-    case 72: return select_conv<T, 7, 2, MODE>(p, st);
-    default: return ROWS_DECLINED;
-  }
-}
-
-// The family covers square odd filters, equal strides 1 or 2, padding k/2, and the output
-// extent that padding implies: 3/5/7 here, 9..31 at stride 1 in rows_bigk.cu.
-inline bool conv_shape_ok(const Shape &s, bool big) {
-  if (s.kh != s.kw) return false;
-  if (!big && s.kh != 3 && s.kh != 5 && s.kh != 7) return false;
-  if (big && (s.kh < 9 || s.kh > 31 || (s.kh & 1) == 0 || s.sh != 1)) return false;
-  if (s.sh != s.sw || (s.sh != 1 && s.sh != 2)) return false;
-  if (s.ph != s.kh / 2 || s.pw != s.kw / 2) return false;
-  if (s.Ho != (s.H + 2 * s.ph - s.kh) / s.sh + 1 || s.Wo != (s.W + 2 * s.pw - s.kw) / s.sw + 1)
-    return false;
-  return true;
-}
-
-}  // namespace
 
 template <typename T>
 int rows_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st) {
@@ -192,7 +19,7 @@ int rows_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st) 
     p.Hin = s.H; p.Win = s.W; p.Hout = s.Ho; p.Wout = s.Wo;
     p.flip = 0;
     if (big) return t_plan_out ? ROWS_DECLINED : rows_bigk_conv<T>(p, s.kh, st);
-    return select_k<T, MODE_FWD>(p, s.kh, s.sh, st);
+    return select_k<T, MODE_FWD, false>(p, s.kh, s.sh, st);
   }
 }
 
@@ -210,7 +37,7 @@ int rows_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStre
     p.flip = 1;
     if (big) return t_plan_out ? ROWS_DECLINED : rows_bigk_conv<T>(p, s.kh, st);
     // stride 1: the transposed operation is the same correlation with the flipped filter
-    return select_k<T, MODE_BWD>(p, s.kh, s.sh, st);
+    return select_k<T, MODE_BWD, false>(p, s.kh, s.sh, st);
   }
 }
 
@@ -231,17 +58,10 @@ int rows_debug_conv_plan(int op, int esize, const Shape &s, int a16, int *out) {
   return r == ROWS_SERVED ? 1 : 0;
 }
 
+int rows_conv_epi_take_error();  // rows_conv_epi.cu
+
 int rows_conv_take_error() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_conv_error_flag, sizeof(int)) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return 0;
-  }
-  if (v) {
-    const int zero = 0;
-    (void)cudaMemcpyToSymbol(g_conv_error_flag, &zero, sizeof(int));
-  }
-  return v | rows_bigk_take_error();
+  return conv_take_error_here() | rows_conv_epi_take_error() | rows_bigk_take_error();
 }
 
 template int rows_forward<float>(const float *, const float *, float *, const Shape &, cudaStream_t);

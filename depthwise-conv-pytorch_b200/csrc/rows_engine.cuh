@@ -214,6 +214,7 @@ struct RowsParams {
              // bytes follow, then the tile's rows
   int ntiles;
   int flip;  // apply the filter flipped in both axes (backward-input)
+  EpilogueArgs ep;  // forward with a fused epilogue (kernels compiled with EPI) only
 };
 
 // V elements from shared memory (32-bit shared address) into fp32 registers.
@@ -544,7 +545,9 @@ __device__ __forceinline__ void conv_producer(const RowsParams &p, const RowsRin
 // forward / backward-input
 // ---------------------------------------------------------------------------------------
 // EXACT: every task of every tile has exactly RBH rows, so no per-row test guards the stores.
-template <typename T, int K, int S, int MODE, int VI, int VO, int U, bool MASK, bool EXACT, int MINB>
+// EPI: the forward with a fused epilogue (scale, bias, activation on the accumulator).
+template <typename T, int K, int S, int MODE, int VI, int VO, int U, bool MASK, bool EXACT, int MINB,
+          bool EPI = false>
 __global__ void __launch_bounds__(ROWS_THREADS, MINB)
 rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
   using Geo = RowsGeo<K, S, MODE, VI, VO, U>;
@@ -642,6 +645,8 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
       T *orow = gout + (size_t)plane * plane_out + (size_t)r_begin * p.Wout + j * VO;
       const bool st_ok = active && out_alive;
       int rows_left = st_ok ? (r_end - r_begin) : 0;
+      float ep_scale = 1.f, ep_bias = 0.f;
+      if constexpr (EPI) epilogue_coeffs<T>(p.ep, plane % p.C, ep_scale, ep_bias);
 
       float rows[Geo::KR][Geo::NIN];
       {
@@ -680,6 +685,10 @@ rows_conv_kernel(const RowsParams p, int *__restrict__ error_flag) {
                 acc[e] = fmaf(rows[ri][Geo::rel(e, tx) - Geo::CMIN], tap, acc[e]);
               }
             }
+          }
+          if constexpr (EPI) {
+#pragma unroll
+            for (int e = 0; e < VO; ++e) acc[e] = apply_epilogue<float>(acc[e], ep_scale, ep_bias, p.ep.act);
           }
           if (EXACT ? st_ok : (u < rows_left)) GmemSt<T, VO>::st(orow, acc);
           orow += p.Wout;

@@ -39,6 +39,7 @@ struct TileParams {
   int flip;      // apply the filter flipped in both axes (backward-input)
   int tiles_x, tiles_y;
   long long ntiles;
+  EpilogueArgs ep;  // forward with a fused epilogue (ep.on)
 };
 
 // Position of input-tile column x inside a shared-memory row: stride 2 separates even and odd
@@ -139,6 +140,12 @@ tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restric
           for (int kx = 0; kx < K; ++kx) acc[o] = fmaf(v[kx], tap[ky][kx], acc[o]);
         }
       }
+    }
+    if (p.ep.on) {
+      float sc, bi;
+      epilogue_coeffs<T>(p.ep, plane % p.C, sc, bi);
+#pragma unroll
+      for (int o = 0; o < TILE_R; ++o) acc[o] = apply_epilogue<float>(acc[o], sc, bi, p.ep.act);
     }
     const int ox = x0 + tc;
     if (ox < p.Wout) {

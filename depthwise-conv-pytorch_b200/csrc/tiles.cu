@@ -75,7 +75,7 @@ void launch_filter_tw(const T *x, const T *dy, float *partial, const TileFilterP
 }  // namespace
 
 template <typename T>
-int tiles_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st) {
+int tiles_forward(const T *x, const T *w, T *y, const Shape &s, const EpilogueArgs &ep, cudaStream_t st) {
   if constexpr (!TilesDtype<T>::ok) {
     return ROWS_DECLINED;
   } else {
@@ -84,6 +84,7 @@ int tiles_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st)
     p.NC = s.N * s.C; p.C = s.C;
     p.Hin = s.H; p.Win = s.W; p.Hout = s.Ho; p.Wout = s.Wo;
     p.pt = s.ph; p.pl = s.pw; p.flip = 0;
+    p.ep = ep;
     return conv_dispatch<T>(x, w, y, p, s.kh, s.sh, st);
   }
 }
@@ -137,7 +138,8 @@ int tiles_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *part
 }
 
 #define DWB_TILES_INSTANTIATE(T)                                                              \
-  template int tiles_forward<T>(const T *, const T *, T *, const Shape &, cudaStream_t);        \
+  template int tiles_forward<T>(const T *, const T *, T *, const Shape &, const EpilogueArgs &, \
+                                cudaStream_t);                                                  \
   template int tiles_backward_input<T>(const T *, const T *, T *, const Shape &, cudaStream_t); \
   template int tiles_backward_filter<T>(const T *, const T *, typename Elem<T>::acc_t *,        \
                                         const Shape &, int, cudaStream_t);

@@ -14,6 +14,14 @@ PATH_AUTO, PATH_DIRECT, PATH_ROWS, PATH_TILES = 0, 1, 2, 3
 OK = 0
 
 
+ACT_NONE, ACT_RELU, ACT_RELU6, ACT_SILU, ACT_HARDSWISH = 0, 1, 2, 3, 4
+
+
+class Epilogue(ctypes.Structure):
+    """Mirror of ``dwconv_b200_epilogue``."""
+    _fields_ = [("scale", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("activation", ctypes.c_int)]
+
+
 class Shape(ctypes.Structure):
     """Mirror of ``dwconv_b200_shape``."""
     _fields_ = [(n, ctypes.c_int) for n in
@@ -39,7 +47,11 @@ def _load():
         "dwconv_b200_debug_plan": (ci, [ci, ci, sp, ci, ctypes.POINTER(ci)]),
         "dwconv_b200_out_size": (ci, [ci] * 6),
         "dwconv_b200_forward": (ci, [vp, vp, vp, ci, sp, vp]),
+        "dwconv_b200_forward_epilogue": (ci, [vp, vp, vp, ci, sp, ctypes.POINTER(Epilogue), vp]),
         "dwconv_b200_backward_input": (ci, [vp, vp, vp, ci, sp, vp]),
+        "dwconv_b200_forward_nhwc": (ci, [vp, vp, vp, ci, sp, ctypes.POINTER(Epilogue), vp]),
+        "dwconv_b200_backward_input_nhwc": (ci, [vp, vp, vp, ci, sp, vp]),
+        "dwconv_b200_backward_filter_nhwc": (ci, [vp, vp, vp, vp, sz, ci, sp, vp]),
         "dwconv_b200_backward_filter_workspace_bytes": (sz, [ci, sp]),
         "dwconv_b200_backward_filter": (ci, [vp, vp, vp, vp, sz, ci, sp, vp]),
         "dwconv_b200_backward": (ci, [vp, vp, vp, vp, vp, vp, sz, ci, sp, vp]),
@@ -77,8 +89,9 @@ EXPORTS = (
     "dwconv_b200_version", "dwconv_b200_status_string", "dwconv_b200_last_cuda_error",
     "dwconv_b200_set_path", "dwconv_b200_last_path", "dwconv_b200_device_status",
     "dwconv_b200_debug_plan", "dwconv_b200_out_size",
-    "dwconv_b200_forward", "dwconv_b200_backward_input",
+    "dwconv_b200_forward", "dwconv_b200_forward_epilogue", "dwconv_b200_backward_input",
     "dwconv_b200_backward_filter_workspace_bytes", "dwconv_b200_backward_filter",
+    "dwconv_b200_forward_nhwc", "dwconv_b200_backward_input_nhwc", "dwconv_b200_backward_filter_nhwc",
     "dwconv_b200_backward", "dwconv_b200_backward_accumulate", "dwconv_b200_backward_exchange",
     "dwconv_b200_backward_filter_allreduce", "dwconv_b200_backward_allreduce",
     "dwconv_b200_use_dwconv2d_small", "dwconv_b200_dwconv2d", "dwconv_b200_dwconv2d_small",

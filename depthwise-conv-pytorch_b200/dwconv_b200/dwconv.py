@@ -26,6 +26,21 @@ def use_dwconv2d_small(input, weight, up, stride, padding):
                                  padding[0], padding[1])
 
 
+def _is_channels_last(t):
+    """A 4-d tensor laid out [n][h][w][c] (and not at the same time plain contiguous, which
+    happens when C or H*W is 1)."""
+    return (t.dim() == 4 and not t.is_contiguous()
+            and t.is_contiguous(memory_format=torch.channels_last))
+
+
+def _nhwc_served(code, kernel, stride):
+    """What the channels-last kernels cover: square 3x3 / 5x5 / 7x7, equal strides 1 or 2,
+    fp32 / fp16 / bf16 (other geometries are made contiguous NCHW, as the reference does)."""
+    kh, kw = kernel.shape[2], kernel.shape[3]
+    return (kh == kw and kh in (3, 5, 7) and stride[0] == stride[1] and stride[0] in (1, 2)
+            and code in (_lib.F32, _lib.F16, _lib.BF16))
+
+
 def _forward_shape(input, kernel, stride, pad):
     N, C, H, W = input.shape
     kh, kw = kernel.shape[2], kernel.shape[3]
@@ -67,15 +82,26 @@ class DepthwiseConv2dFunction(Function):
         stride = tuple(int(v) for v in stride)
         pad = tuple(int(v) for v in pad)
         _C._check_filter(input, kernel)
-        input = input.contiguous()
+        # channels-last maps are read and written in place (no NCHW copy); the result follows
+        # the input's layout, as PyTorch's own convolution does
+        nhwc = _is_channels_last(input) and _nhwc_served(code, kernel, stride)
+        if not nhwc:
+            input = input.contiguous()
         kernel = kernel.contiguous()
         shape = _forward_shape(input, kernel, stride, pad)
         out = torch.empty((shape.N, shape.C, shape.Ho, shape.Wo), dtype=input.dtype,
-                          device=input.device)
+                          device=input.device,
+                          memory_format=torch.channels_last if nhwc else torch.contiguous_format)
         with _C._on_device(input):
-            st = _lib.lib.dwconv_b200_forward(input.data_ptr(), kernel.data_ptr(), out.data_ptr(),
-                                              code, shape, _C._stream(input))
+            if nhwc:
+                st = _lib.lib.dwconv_b200_forward_nhwc(input.data_ptr(), kernel.data_ptr(),
+                                                       out.data_ptr(), code, shape, None,
+                                                       _C._stream(input))
+            else:
+                st = _lib.lib.dwconv_b200_forward(input.data_ptr(), kernel.data_ptr(), out.data_ptr(),
+                                                  code, shape, _C._stream(input))
         _lib.check(st, "forward")
+        ctx.nhwc = nhwc
         ctx.save_for_backward(input, kernel)
         ctx.shape = shape
         ctx.code = code
@@ -96,6 +122,8 @@ class DepthwiseConv2dFunction(Function):
             raise RuntimeError(f"depthwise_conv2d backward: grad_output has shape "
                                f"{tuple(grad_output.shape)}, expected "
                                f"{(shape.N, shape.C, shape.Ho, shape.Wo)}")
+        if ctx.nhwc:
+            return DepthwiseConv2dFunction._backward_nhwc(ctx, grad_output, input, kernel)
         grad_output = grad_output.contiguous()
         grad_input = grad_kernel = None
         with _C._on_device(input):
@@ -129,7 +157,134 @@ class DepthwiseConv2dFunction(Function):
         return grad_input, grad_kernel, None, None, None
 
 
+    @staticmethod
+    def _backward_nhwc(ctx, grad_output, input, kernel):
+        """Both gradients for a channels-last forward: dy is taken channels-last (a copy only
+        if autograd hands it over in another layout), dx is channels-last like the input."""
+        shape, code = ctx.shape, ctx.code
+        grad_output = grad_output.contiguous(memory_format=torch.channels_last)
+        grad_input = grad_kernel = None
+        with _C._on_device(input):
+            stream = _C._stream(input)
+            if ctx.needs_input_grad[0]:
+                grad_input = torch.empty_like(input, memory_format=torch.channels_last)
+                st = _lib.lib.dwconv_b200_backward_input_nhwc(
+                    grad_output.data_ptr(), kernel.data_ptr(), grad_input.data_ptr(), code, shape,
+                    stream)
+                _lib.check(st, "backward_input_nhwc")
+            if ctx.needs_input_grad[1]:
+                nbytes = _workspace_bytes(code, shape)
+                ws = torch.empty(nbytes, dtype=torch.uint8, device=input.device)
+                grad_kernel = torch.empty_like(kernel)
+                st = _lib.lib.dwconv_b200_backward_filter_nhwc(
+                    input.data_ptr(), grad_output.data_ptr(), grad_kernel.data_ptr(), ws.data_ptr(),
+                    nbytes, code, shape, stream)
+                _lib.check(st, "backward_filter_nhwc")
+            if _lib.CHECK_STATUS:
+                _lib.check_device_status("backward")
+        return grad_input, grad_kernel, None, None, None
+
+
 depthwise_conv2d_fn = DepthwiseConv2dFunction.apply
+
+_ACTIVATIONS = {None: _lib.ACT_NONE, "none": _lib.ACT_NONE, "relu": _lib.ACT_RELU,
+                "relu6": _lib.ACT_RELU6, "silu": _lib.ACT_SILU, "swish": _lib.ACT_SILU,
+                "hardswish": _lib.ACT_HARDSWISH}
+
+
+class DepthwiseConv2dEpilogueFunction(Function):
+    """``act(conv(input, kernel) * scale[c] + bias[c])`` in one kernel (new surface: the
+    reference rejects a bias, torch_dwconv/dwconv.py:108-109).
+
+    Gradients flow to ``input`` and ``kernel`` for the activations whose derivative can be read
+    off the output (none, ReLU, ReLU6): ``grad_output`` is masked and scaled with elementwise
+    torch operations and handed to the fused backward.  ``scale`` and ``bias`` are constants
+    (a folded batch-norm): they get no gradient.  SiLU and hard-swish are forward-only.
+    """
+
+    @staticmethod
+    def forward(ctx, input, kernel, scale, bias, act, stride, pad):
+        _C._check_cuda(input, "input")
+        _C._check_cuda(kernel, "kernel")
+        code = _C._dtype_code(input, kernel)
+        _C._check_filter(input, kernel)
+        C = input.shape[1]
+        for t, name in ((scale, "scale"), (bias, "bias")):
+            if t is not None:
+                _C._dtype_code(input, t)
+                if t.numel() != C:
+                    raise RuntimeError(f"depthwise_conv2d_epilogue: {name} must have {C} elements, "
+                                       f"got {tuple(t.shape)}")
+        input = input.contiguous()
+        kernel = kernel.contiguous()
+        scale_c = scale.contiguous() if scale is not None else None
+        bias_c = bias.contiguous() if bias is not None else None
+        shape = _forward_shape(input, kernel, stride, pad)
+        out = torch.empty((shape.N, shape.C, shape.Ho, shape.Wo), dtype=input.dtype,
+                          device=input.device)
+        ep = _lib.Epilogue(scale_c.data_ptr() if scale_c is not None else None,
+                           bias_c.data_ptr() if bias_c is not None else None, act)
+        with _C._on_device(input):
+            st = _lib.lib.dwconv_b200_forward_epilogue(input.data_ptr(), kernel.data_ptr(),
+                                                       out.data_ptr(), code, shape, ep,
+                                                       _C._stream(input))
+        _lib.check(st, "forward_epilogue")
+        ctx.save_for_backward(input, kernel, scale_c, out)
+        ctx.shape, ctx.code, ctx.act = shape, code, act
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, kernel, scale, out = ctx.saved_tensors
+        if ctx.act not in (_lib.ACT_NONE, _lib.ACT_RELU, _lib.ACT_RELU6):
+            raise RuntimeError("depthwise_conv2d_epilogue: this activation is forward-only "
+                               "(its derivative is not a function of the output)")
+        g = grad_output
+        if scale is not None:
+            g = g * scale.view(1, -1, 1, 1)
+        if ctx.act == _lib.ACT_RELU:
+            g = torch.where(out > 0, g, torch.zeros((), dtype=g.dtype, device=g.device))
+        elif ctx.act == _lib.ACT_RELU6:
+            g = torch.where((out > 0) & (out < 6), g, torch.zeros((), dtype=g.dtype, device=g.device))
+        g = g.contiguous()
+        shape, code = ctx.shape, ctx.code
+        grad_input = grad_kernel = None
+        with _C._on_device(input):
+            stream = _C._stream(input)
+            nbytes = _workspace_bytes(code, shape)
+            ws = torch.empty(nbytes, dtype=torch.uint8, device=input.device)
+            grad_input = torch.empty_like(input)
+            grad_kernel = torch.empty_like(kernel)
+            st = _lib.lib.dwconv_b200_backward(
+                input.data_ptr(), g.data_ptr(), kernel.data_ptr(), grad_input.data_ptr(),
+                grad_kernel.data_ptr(), ws.data_ptr(), nbytes, code, shape, stream)
+            _lib.check(st, "backward")
+        return grad_input, grad_kernel, None, None, None, None, None
+
+
+def depthwise_conv2d_epilogue(input, weight, scale=None, bias=None, activation=None, stride=1,
+                              padding=0):
+    """Depthwise convolution followed, inside the same kernel, by a per-channel scale and
+    shift and an activation: ``act(conv(input, weight) * scale[c] + bias[c])``.
+
+    ``scale`` / ``bias``: 1-d tensors of C elements (or ``None``), same dtype and device as the
+    input.  ``activation``: ``None``, ``'relu'``, ``'relu6'``, ``'silu'`` (= ``'swish'``) or
+    ``'hardswish'``.  Opt-in: ``depthwise_conv2d`` keeps the reference's behaviour of rejecting
+    a bias.
+    """
+    stride = make_tuple(stride, 2)
+    padding = make_tuple(padding, 2)
+    check_options(input.shape[1], weight.shape[0], 1, None, None)
+    if activation not in _ACTIVATIONS:
+        raise ValueError(f"unknown activation {activation!r}; expected one of "
+                         f"{sorted(k for k in _ACTIVATIONS if k)}")
+    for t, name in ((scale, "scale"), (bias, "bias")):
+        if t is not None and t.requires_grad:
+            raise RuntimeError(f"depthwise_conv2d_epilogue: {name} is a constant of the fused "
+                               "epilogue and gets no gradient; detach it")
+    return DepthwiseConv2dEpilogueFunction.apply(
+        input, weight, scale, bias, _ACTIVATIONS[activation],
+        tuple(int(v) for v in stride), tuple(int(v) for v in padding))
 
 
 def make_tuple(value, n_value):

@@ -145,6 +145,60 @@ DWCONV_B200_API int dwconv_b200_backward_filter(const void *x, const void *dy, v
                                 size_t workspace_bytes, int dtype,
                                 const dwconv_b200_shape *shape, void *stream);
 
+/* ------------------------------------------------------------------------
+ * Forward with a fused epilogue (opt-in; no counterpart in the reference, which
+ * rejects a bias outright, torch_dwconv/dwconv.py:108-109).
+ *   y = act(conv(x, w) * scale[c] + bias[c])
+ * applied to the accumulator (fp32; fp64 for f64 data) before the one rounding to
+ * the storage type.  `scale` and `bias` are [C] arrays of the tensors' element
+ * type on the device, each may be NULL (1 resp. 0).  This is what follows a
+ * depthwise convolution in the blocks that use one (folded batch-norm scale and
+ * shift, then ReLU6 / SiLU / hard-swish); done separately it costs another read
+ * and write of the output map.  Every shape and dtype dwconv_b200_forward
+ * serves is served.  A NULL `epilogue`, or one with no scale, no bias and no
+ * activation, is the plain forward.
+ * ---------------------------------------------------------------------- */
+typedef enum dwconv_b200_activation {
+  DWCONV_B200_ACT_NONE = 0,
+  DWCONV_B200_ACT_RELU = 1,
+  DWCONV_B200_ACT_RELU6 = 2,
+  DWCONV_B200_ACT_SILU = 3,      /* v * sigmoid(v) */
+  DWCONV_B200_ACT_HARDSWISH = 4  /* v * relu6(v + 3) / 6 */
+} dwconv_b200_activation;
+
+typedef struct dwconv_b200_epilogue {
+  const void *scale; /* [C] or NULL */
+  const void *bias;  /* [C] or NULL */
+  int activation;    /* dwconv_b200_activation */
+} dwconv_b200_epilogue;
+
+DWCONV_B200_API int dwconv_b200_forward_epilogue(const void *x, const void *w, void *y, int dtype,
+                                                 const dwconv_b200_shape *shape,
+                                                 const dwconv_b200_epilogue *epilogue, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Channels-last (NHWC) operators: activations laid out x[n][h][w][c]
+ * (torch.channels_last), filters [C,1,kh,kw] as everywhere.  The reference makes
+ * every operand contiguous NCHW first (torch_dwconv/dwconv_kernel.cu:741-742,
+ * 855-856,1023-1024), which costs a channels-last caller an extra read and write
+ * of each map; these read and write NHWC in place.  `shape` has the same meaning
+ * as for the NCHW entry points.  Served: square 3x3 / 5x5 / 7x7 filters, equal
+ * strides 1 or 2, any padding, f32 / f16 / bf16; anything else returns
+ * DWCONV_B200_UNSUPPORTED_SHAPE (make the maps contiguous NCHW and use the
+ * entry points above).  Same summation order as the NCHW kernels: the same
+ * values give the same bits.  forward_nhwc takes the optional epilogue of
+ * dwconv_b200_forward_epilogue (NULL: none); backward_filter_nhwc takes the
+ * workspace of dwconv_b200_backward_filter (same size query).
+ * ---------------------------------------------------------------------- */
+DWCONV_B200_API int dwconv_b200_forward_nhwc(const void *x, const void *w, void *y, int dtype,
+                                             const dwconv_b200_shape *shape,
+                                             const dwconv_b200_epilogue *epilogue, void *stream);
+DWCONV_B200_API int dwconv_b200_backward_input_nhwc(const void *dy, const void *w, void *dx, int dtype,
+                                                    const dwconv_b200_shape *shape, void *stream);
+DWCONV_B200_API int dwconv_b200_backward_filter_nhwc(const void *x, const void *dy, void *dw,
+                                                     void *workspace, size_t workspace_bytes, int dtype,
+                                                     const dwconv_b200_shape *shape, void *stream);
+
 /* Both gradients from ONE pass over dy: dx as dwconv_b200_backward_input (bit for bit),
  * dw as dwconv_b200_backward_filter (same two-pass reduction; the partial sums are
  * accumulated in another order, so dw agrees to rounding, not bit for bit).  For the

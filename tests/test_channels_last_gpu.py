@@ -1,0 +1,85 @@
+"""Channels-last (NHWC) maps: read and written in place by their own kernels, against the
+oracle and against the NCHW path on the same values."""
+import pytest
+import torch
+
+import oracle
+from conftest import NP_DT, assert_dw_close
+from dwconv_b200 import _lib
+from gpu_util import CODE, make_shape, seeded
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # (N, C, H, W, k, stride, padding): channel counts around the 32-channel blocks, odd maps,
+    # paddings other than k/2, tiles that end mid-map
+    (2, 32, 14, 14, 3, 1, 1), (3, 40, 28, 28, 3, 2, 1), (2, 7, 33, 35, 5, 1, 2), (1, 96, 56, 56, 5, 2, 2),
+    (2, 65, 17, 19, 7, 1, 3), (1, 33, 30, 41, 7, 2, 3), (2, 16, 20, 20, 3, 1, 0), (1, 48, 21, 21, 5, 2, 0),
+    (1, 3, 64, 64, 3, 1, (2, 0)), (4, 160, 7, 7, 3, 1, 1),
+]
+
+
+@pytest.mark.parametrize("dtn", ["f32", "f16"])
+@pytest.mark.parametrize("cfg", CASES, ids=lambda c: "x".join(map(str, c)))
+def test_channels_last_through_the_c_abi(cfg, dtn):
+    N, C, H, W, k, s, p = cfg
+    dt = NP_DT[dtn]
+    x, w, dy = seeded((N, C, H, W), (k, k), s, p, dt, seed=C + H + k)
+    sh = make_shape((N, C, H, W), (k, k), s, p)
+    xl = x.contiguous(memory_format=torch.channels_last)
+    dyl = dy.contiguous(memory_format=torch.channels_last)
+    L, st0 = _lib.lib, torch.cuda.current_stream().cuda_stream
+    y = torch.full_like(dyl, float("nan"))
+    dx = torch.full_like(xl, float("nan"))
+    assert L.dwconv_b200_forward_nhwc(xl.data_ptr(), w.data_ptr(), y.data_ptr(), CODE[dt], sh, None, st0) == 0
+    assert L.dwconv_b200_backward_input_nhwc(dyl.data_ptr(), w.data_ptr(), dx.data_ptr(), CODE[dt], sh, st0) == 0
+    nbytes = L.dwconv_b200_backward_filter_workspace_bytes(CODE[dt], sh)
+    ws = torch.full((nbytes + 256,), 0xA5, dtype=torch.uint8, device="cuda")
+    dw = torch.full_like(w, float("nan"))
+    assert L.dwconv_b200_backward_filter_nhwc(xl.data_ptr(), dyl.data_ptr(), dw.data_ptr(), ws.data_ptr(),
+                                              nbytes, CODE[dt], sh, st0) == 0
+    torch.cuda.synchronize()
+    assert bool((ws[nbytes:] == 0xA5).all()), "wrote past the workspace"
+    assert y.is_contiguous(memory_format=torch.channels_last)
+    assert not torch.isnan(y).any() and not torch.isnan(dx).any() and not torch.isnan(dw).any()
+    assert torch.equal(y.cpu(), oracle.forward_seq(x, w, s, p))
+    assert torch.equal(dx.cpu(), oracle.backward_input_seq(dy, w, (H, W), s, p))
+    assert_dw_close(dw, oracle.backward_filter(x, dy, (k, k), s, p), dt, "NHWC dW")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16], ids=["f32", "f16", "bf16"])
+def test_channels_last_through_autograd(dtype):
+    """``depthwise_conv2d`` on a channels-last tensor: output and input gradient come back
+    channels-last, with the values of the NCHW path."""
+    import dwconv_b200
+    for (N, C, H, W, k, s, p) in [(2, 40, 28, 28, 3, 1, 1), (2, 24, 30, 30, 5, 2, 2)]:
+        x, w, dy = seeded((N, C, H, W), (k, k), s, p, dtype, seed=3)
+        xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        ya = dwconv_b200.depthwise_conv2d(xa, wa, stride=s, padding=p)
+        ya.backward(dy)
+        xb = x.contiguous(memory_format=torch.channels_last).requires_grad_(True)
+        wb = w.clone().requires_grad_(True)
+        yb = dwconv_b200.depthwise_conv2d(xb, wb, stride=s, padding=p)
+        assert yb.is_contiguous(memory_format=torch.channels_last) and not yb.is_contiguous()
+        yb.backward(dy.contiguous(memory_format=torch.channels_last))
+        assert xb.grad.is_contiguous(memory_format=torch.channels_last)
+        assert torch.equal(yb, ya)
+        assert torch.equal(xb.grad, xa.grad)
+        scale = wa.grad.double().abs().max().item()
+        tol = 1e-4 if dtype == torch.float32 else 2e-2
+        assert (wb.grad.double() - wa.grad.double()).abs().max().item() <= tol * scale
+    assert _lib.lib.dwconv_b200_device_status() == 0
+
+
+def test_channels_last_outside_the_nhwc_kernels_is_copied():
+    """A geometry the channels-last kernels do not cover (rectangular filter) still works: the
+    map is made contiguous first, as the reference does for every input."""
+    import dwconv_b200
+    x, w, _ = seeded((2, 8, 12, 12), (3, 5), 1, (1, 2), torch.float32, seed=8)
+    xl = x.contiguous(memory_format=torch.channels_last)
+    y = dwconv_b200.depthwise_conv2d(xl, w, stride=1, padding=(1, 2))
+    assert y.is_contiguous()
+    assert torch.equal(y.cpu(), oracle.forward_seq(x, w, 1, (1, 2)))
+    s = make_shape((2, 8, 12, 12), (3, 5), 1, (1, 2))
+    assert _lib.lib.dwconv_b200_forward_nhwc(xl.data_ptr(), w.data_ptr(), y.data_ptr(), _lib.F32, s, None,
+                                             None) == 6
