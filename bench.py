@@ -457,7 +457,8 @@ def gpu_arm(args, layers):
     for mode in candidates:
         for use_graph in ((True, False) if args.launch == "auto" else
                           ((True,) if args.launch == "graph" else (False,))):
-            ms = wb.time_steps(mode, 120, 10, stream, use_graph, barrier)
+            ms = wb.time_steps(mode, args.calibration_steps, min(10, args.calibration_steps), stream,
+                               use_graph, barrier)
             calibration[f"{mode}_{'graph' if use_graph else 'eager'}_ms"] = round(ms, 5)
             if best is None or ms < best[0]:
                 best = (ms, mode, use_graph)
@@ -846,6 +847,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the stack and strong-scaling legs (profiling)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--calibration-steps", type=int, default=120,
+                    help="steps timed per launch mode before the headline (a profiler run wants few)")
     ap.add_argument("--time-api", metavar="JSON",
                     help="instead of the benchmark: time the public Python API on a JSON list of "
                          "[N, C, H, k, stride, pad, dtype] or [N, C, H, W, k, stride, pad, dtype]")

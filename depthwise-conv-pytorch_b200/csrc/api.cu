@@ -9,6 +9,7 @@
 #include "common.cuh"
 #include "direct_kernels.cuh"
 #include "peer_exchange.cuh"
+#include "api_checks.cuh"
 #include "rows_api.cuh"
 
 using namespace dwb;
@@ -22,32 +23,6 @@ std::atomic<int> g_forced_path{DWCONV_B200_PATH_AUTO};
 thread_local int t_last_path = DWCONV_B200_PATH_AUTO;
 thread_local int t_last_cuda_error = 0;
 
-inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
-
-inline size_t elem_size(int dtype) {
-  switch (dtype) {
-    case DWCONV_B200_F32: return 4;
-    case DWCONV_B200_F16: return 2;
-    case DWCONV_B200_BF16: return 2;
-    case DWCONV_B200_F64: return 8;
-    default: return 0;
-  }
-}
-
-int check_shape(const Shape *s) {
-  if (s == nullptr) return DWCONV_B200_BAD_ARGUMENT;
-  if (s->N <= 0 || s->C <= 0 || s->H <= 0 || s->W <= 0 || s->kh <= 0 || s->kw <= 0 ||
-      s->sh <= 0 || s->sw <= 0 || s->ph < 0 || s->pw < 0 || s->Ho <= 0 || s->Wo <= 0)
-    return DWCONV_B200_BAD_ARGUMENT;
-  // Index arithmetic inside one plane is 32-bit; whole-tensor offsets are 64-bit.
-  const long long lim = 1ll << 30;
-  if ((long long)s->H * s->W >= lim || (long long)s->Ho * s->Wo >= lim ||
-      (long long)s->kh * s->kw >= (1ll << 20) || (long long)s->N * s->C >= (1ll << 31) - 1 ||
-      (long long)s->Ho * s->sh + s->kh >= lim || (long long)s->Wo * s->sw + s->kw >= lim)
-    return DWCONV_B200_TOO_LARGE;
-  return DWCONV_B200_OK;
-}
-
 int launch_status() {
   cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) {
@@ -57,6 +32,17 @@ int launch_status() {
   }
   return DWCONV_B200_OK;
 }
+
+}  // namespace
+
+namespace dwb {
+// For the entry points that live in other translation units (static_scratch.cu): the same
+// per-thread records dwconv_b200_last_cuda_error / dwconv_b200_last_path report.
+int api_launch_status() { return launch_status(); }
+void api_note_path(int path) { t_last_path = path; }
+}  // namespace dwb
+
+namespace {
 
 inline int grid_for(long long total, int block) {
   long long g = ceil_div_ll(total, block);

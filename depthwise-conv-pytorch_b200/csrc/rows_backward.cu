@@ -1,5 +1,6 @@
 // Rows family, fused backward (dx and the partial sums of dW in one pass over dy): variant
 // selection and launch.
+#include "lanerow_backward.cuh"
 #include "rows_backward.cuh"
 #include "rows_plan.cuh"
 
@@ -183,6 +184,52 @@ template <typename T> struct RowsDtype { static constexpr bool ok = false; };
 template <> struct RowsDtype<float> { static constexpr bool ok = true; };
 template <> struct RowsDtype<__half> { static constexpr bool ok = true; };
 
+// ---- small maps: a lane owns a row (lanerow_backward.cuh) ----
+// fp32, stride 1, 3x3 / 5x5, maps 7 or 14 columns wide and at most 32 rows high.
+inline bool lanerow_shape_ok(const Shape &s) {
+  return s.kh == s.kw && (s.kh == 3 || s.kh == 5) && s.sh == 1 && s.sw == 1 && s.ph == s.kh / 2 &&
+         s.pw == s.kw / 2 && (s.W == 7 || s.W == 14) && s.H <= 32 && s.Ho == s.H && s.Wo == s.W;
+}
+
+inline bool plan_lanerow(const Shape &s, LaneRowParams &p) {
+  if (!lanerow_shape_ok(s)) return false;
+  const int lanes = ROWS_CWARPS * 32;
+  int G = lanes / s.H;
+  if (G > s.C) G = s.C;
+  if (G < 1) return false;
+  const int plane_bytes = s.H * s.W * 4;
+  auto region = [&](int g) { return round_up(g * plane_bytes + 16, 16); };
+  auto stage_need = [&](int g) { return LANEROW_ZERO_BYTES + 3 * region(g); };
+  while (G > 1 && stage_need(G) > ROWS_RING_BYTES / 2) --G;
+  if (stage_need(G) > ROWS_RING_BYTES / 2) return false;
+  p.NST = stage_need(G) <= ROWS_RING_BYTES / 3 ? 3 : 2;
+  p.N = s.N; p.C = s.C; p.H = s.H; p.G = G;
+  p.DYOFF = LANEROW_ZERO_BYTES;
+  p.XOFF = p.DYOFF + region(G);
+  p.OUTOFF = p.XOFF + region(G);
+  p.NCG = ceil_div(s.C, G);
+  const int slots = sm_count() * 2;
+  int SL = slots / p.NCG;
+  if (SL < 1 || (long long)SL * p.NCG * 100 < 85ll * slots) SL = ceil_div(2 * slots, p.NCG);
+  if (SL > s.N) SL = s.N;
+  if (SL < 1) SL = 1;
+  p.SL = SL;
+  return true;
+}
+
+template <int K, int W>
+int launch_lanerow(const LaneRowParams &p, cudaStream_t st) {
+  auto kernel = lanerow_backward_kernel<K, W, 2>;
+  static std::atomic<unsigned long long> smem_done{0};
+  if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
+  int *flag = backward_flag_address();
+  if (flag == nullptr) return ROWS_DECLINED;
+  const long long items = (long long)p.NCG * p.SL;
+  const int grid = (int)min((long long)sm_count() * 2, items);
+  launch_dependent(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, p, flag);
+  return ROWS_SERVED;
+}
+
 }  // namespace
 
 template <typename T> int rows_backward_slices(const Shape &s) {
@@ -194,6 +241,8 @@ template <typename T> int rows_backward_slices(const Shape &s) {
     int best = 0;
     for (int a16 = 0; a16 < 2; ++a16)
       if (plan_backward<T>(s, a16 != 0, f) && f.p.SL > best) best = f.p.SL;
+    LaneRowParams lp{};
+    if (sizeof(T) == 4 && plan_lanerow(s, lp) && lp.SL > best) best = lp.SL;
     return best;
   }
 }
@@ -206,6 +255,20 @@ int rows_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<T>::
   } else {
     const bool a16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
                        reinterpret_cast<uintptr_t>(dx)) & 15) == 0;
+    if constexpr (sizeof(T) == 4) {
+      LaneRowParams lp{};
+      if (a16 && tuning_int("LANEROW", 1) != 0 && plan_lanerow(s, lp)) {
+        lp.x = x; lp.dy = dy; lp.w = w; lp.dx = dx; lp.partial = partial;
+        *slices_out = lp.SL;
+        switch (s.kh * 100 + s.W) {
+          case 307: return launch_lanerow<3, 7>(lp, st);
+          case 314: return launch_lanerow<3, 14>(lp, st);
+          case 507: return launch_lanerow<5, 7>(lp, st);
+          case 514: return launch_lanerow<5, 14>(lp, st);
+          default: break;
+        }
+      }
+    }
     BackwardPlan f{};
     if (!plan_backward<T>(s, a16, f)) return ROWS_DECLINED;
     f.p.x = x; f.p.dy = dy; f.p.w = w; f.p.dx = dx; f.p.partial = partial;

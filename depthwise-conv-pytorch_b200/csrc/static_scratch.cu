@@ -2,7 +2,7 @@
 // library's device image.  Declaration and contract: include/dwconv_b200.h.
 #include <mutex>
 
-#include "common.cuh"
+#include "api_checks.cuh"
 #include "direct_kernels.cuh"
 
 using namespace dwb;
@@ -57,17 +57,12 @@ int run(const void *x, const void *dy, void *dw, const Shape &s, cudaStream_t st
   if (e != DWCONV_B200_OK) return e;
   direct_backward_filter_partial_kernel<T><<<s.C * S, 256, 0, st>>>((const T *)x, (const T *)dy,
                                                                     (A *)scratch, s, S);
-  if (cudaPeekAtLastError() != cudaSuccess) {
-    (void)cudaGetLastError();
-    return DWCONV_B200_CUDA_ERROR;
-  }
+  e = api_launch_status();
+  if (e != DWCONV_B200_OK) return e;
   backward_filter_finalize_kernel<T><<<finalize_blocks(s.C, kk), FINALIZE_THREADS, 0, st>>>(
       (const A *)scratch, (T *)dw, s.C, kk, S);
-  if (cudaPeekAtLastError() != cudaSuccess) {
-    (void)cudaGetLastError();
-    return DWCONV_B200_CUDA_ERROR;
-  }
-  return DWCONV_B200_OK;
+  api_note_path(DWCONV_B200_PATH_DIRECT);
+  return api_launch_status();
 }
 
 }  // namespace
@@ -78,20 +73,12 @@ size_t dwconv_b200_static_scratch_bytes(void) { return DWCONV_B200_STATIC_SCRATC
 
 int dwconv_b200_backward_filter_static(const void *x, const void *dy, void *dw, int dtype,
                                        const dwconv_b200_shape *s, void *stream) {
-  if (x == nullptr || dy == nullptr || dw == nullptr || s == nullptr)
-    return DWCONV_B200_BAD_ARGUMENT;
-  if (s->N <= 0 || s->C <= 0 || s->H <= 0 || s->W <= 0 || s->kh <= 0 || s->kw <= 0 ||
-      s->sh <= 0 || s->sw <= 0 || s->ph < 0 || s->pw < 0 || s->Ho <= 0 || s->Wo <= 0)
-    return DWCONV_B200_BAD_ARGUMENT;
-  const long long lim = 1ll << 30;
-  if ((long long)s->H * s->W >= lim || (long long)s->Ho * s->Wo >= lim ||
-      (long long)s->kh * s->kw >= (1ll << 20) || (long long)s->N * s->C >= (1ll << 31) - 1)
-    return DWCONV_B200_TOO_LARGE;
-  const size_t es = dtype == DWCONV_B200_F32 ? 4 : (dtype == DWCONV_B200_F16 || dtype == DWCONV_B200_BF16) ? 2
-                    : dtype == DWCONV_B200_F64 ? 8 : 0;
+  if (x == nullptr || dy == nullptr || dw == nullptr) return DWCONV_B200_BAD_ARGUMENT;
+  int e = check_shape(s);
+  if (e) return e;
+  const size_t es = elem_size(dtype);
   if (es == 0) return DWCONV_B200_UNSUPPORTED_DTYPE;
-  if (((uintptr_t)x % es) || ((uintptr_t)dy % es) || ((uintptr_t)dw % es))
-    return DWCONV_B200_MISALIGNED;
+  if (!aligned_to(x, es) || !aligned_to(dy, es) || !aligned_to(dw, es)) return DWCONV_B200_MISALIGNED;
   cudaStream_t st = (cudaStream_t)stream;
   switch (dtype) {
     case DWCONV_B200_F32: return run<float>(x, dy, dw, *s, st);

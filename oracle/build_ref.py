@@ -12,7 +12,9 @@ vendored beside it, and that copy collides with the toolkit's CUB that the ATen
 headers pull in.  The two files (and the package's two ``.py`` files) are
 therefore staged in a temporary directory WITHOUT the vendored ``cub/`` folder,
 so the include resolves to the toolkit's CUB.  Nothing is copied into the
-tracked tree; the only outputs are ``oracle/_ref/torch_dwconv/{_C.so,*.py}``.
+tracked tree; the only outputs are ``oracle/_ref/torch_dwconv/{_C.so,*.py}`` and a copy of
+the reference's two test files in ``oracle/_ref/test/`` (git-ignored like the rest of
+``oracle/_ref``; ``tests/test_reference_suite_gpu.py`` runs them unchanged).
 
 Usage:  python oracle/build_ref.py [/path/to/reference]
         (default: the directory named by the environment variable DWCONV_REFERENCE_DIR,
@@ -39,6 +41,15 @@ def build_ref(ref_root=None, verbose=False):
     if not os.path.isdir(src):
         return None
     so = os.path.join(OUT, "_C.so")
+    # the reference's own test files, to be run unchanged against this library and against the
+    # reference build (they import ``torch_dwconv``; which package that is, the runner decides)
+    tdir = os.path.join(os.path.dirname(OUT), "test")
+    tsrc = os.path.join(os.path.dirname(src), "test")
+    if os.path.isdir(tsrc):
+        os.makedirs(tdir, exist_ok=True)
+        for f in ("test_forward.py", "test_grad.py"):
+            if os.path.exists(os.path.join(tsrc, f)):
+                shutil.copy(os.path.join(tsrc, f), tdir)
     newest = max(os.path.getmtime(os.path.join(src, f))
                  for f in ("dwconv.cpp", "dwconv_kernel.cu", "dwconv.py"))
     if os.path.exists(so) and os.path.getmtime(so) >= newest:

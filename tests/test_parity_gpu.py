@@ -399,6 +399,10 @@ FUSED_CASES = [
     ((3, 9, 14, 14), 5, 1), ((2, 4, 30, 30), 5, 1), ((1, 3, 62, 62), 5, 1),
     ((2, 6, 56, 56), 5, 2), ((3, 7, 14, 14), 5, 2),
     ((2, 5, 28, 28), 7, 1), ((1, 3, 56, 56), 7, 1), ((2, 4, 30, 30), 7, 1), ((2, 3, 28, 28), 7, 2),
+    # maps 7 and 14 columns wide (fp32: the lane-per-row kernel): rectangular planes, channel
+    # groups with a ragged last group, batches smaller than the slice count, many planes
+    ((2, 40, 7, 7), 5, 1), ((3, 33, 28, 14), 3, 1), ((1, 5, 32, 14), 5, 1), ((2, 3, 9, 7), 3, 1),
+    ((1, 70, 14, 14), 3, 1), ((9, 20, 5, 14), 5, 1), ((17, 64, 7, 7), 3, 1), ((40, 18, 14, 14), 5, 1),
 ]
 
 
