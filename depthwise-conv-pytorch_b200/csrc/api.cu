@@ -85,8 +85,8 @@ template <typename T> int try_rows_backward_slices(const Shape &s) {
 }
 template <typename T>
 int try_rows_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<T>::acc_t *partial,
-                      const Shape &s, cudaStream_t st, int *slices_out) {
-  if constexpr (kRowsCompiled<T>) return rows_backward<T>(x, dy, w, dx, partial, s, st, slices_out);
+                      const Shape &s, cudaStream_t st, int *slices_out, T *dw_direct) {
+  if constexpr (kRowsCompiled<T>) return rows_backward<T>(x, dy, w, dx, partial, s, st, slices_out, dw_direct);
   return ROWS_DECLINED;
 }
 
@@ -235,17 +235,21 @@ int backward_filter_t(const void *x, const void *dy, void *dw, void *ws, size_t 
 // First pass of the fused backward: dx, and the partial sums of dW into ws.  One kernel when
 // the rows family serves the shape (dy is read once); otherwise backward-input followed by the
 // filter gradient's own first pass.
+// dw_direct (optional): where the kernel may write the finished filter gradient itself; *slices
+// is then 0 and no second pass is due.
 template <typename T>
 int backward_first_pass_t(const void *x, const void *dy, const void *w, void *dx, void *ws,
-                          size_t ws_bytes, const Shape &s, cudaStream_t st, int forced, int *slices) {
+                          size_t ws_bytes, const Shape &s, cudaStream_t st, int forced, int *slices,
+                          void *dw_direct = nullptr) {
   using A = typename Elem<T>::acc_t;
   if (ws_bytes < filter_workspace_t<T>(s)) return DWCONV_B200_WORKSPACE_TOO_SMALL;
   if (forced == DWCONV_B200_PATH_AUTO || forced == DWCONV_B200_PATH_ROWS) {
     int S = 0;
-    int r = try_rows_backward<T>((const T *)x, (const T *)dy, (const T *)w, (T *)dx, (A *)ws, s, st, &S);
-    if (r == ROWS_SERVED) {
+    int r = try_rows_backward<T>((const T *)x, (const T *)dy, (const T *)w, (T *)dx, (A *)ws, s, st, &S,
+                                 (T *)dw_direct);
+    if (r != ROWS_DECLINED) {
       t_last_path = DWCONV_B200_PATH_ROWS;
-      *slices = S;
+      *slices = (r == ROWS_SERVED_DW) ? 0 : S;
       return launch_status();
     }
   }
@@ -261,9 +265,11 @@ int backward_t(const void *x, const void *dy, const void *w, void *dx, void *dw,
                int accumulate) {
   using A = typename Elem<T>::acc_t;
   int S = 0;
-  int e = dx != nullptr ? backward_first_pass_t<T>(x, dy, w, dx, ws, ws_bytes, s, st, forced, &S)
+  int e = dx != nullptr ? backward_first_pass_t<T>(x, dy, w, dx, ws, ws_bytes, s, st, forced, &S,
+                                                   dw_is_acc ? nullptr : dw)
                         : filter_first_pass_t<T>(x, dy, ws, ws_bytes, s, st, forced, &S);
   if (e != DWCONV_B200_OK) return e;
+  if (S == 0) return DWCONV_B200_OK;  // the first pass finished dW itself
   const int kk = s.kh * s.kw;
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t cfg = finalize_config(finalize_blocks(s.C, kk), st, attr);

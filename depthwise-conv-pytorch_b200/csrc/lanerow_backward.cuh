@@ -1,4 +1,5 @@
-// Fused backward for SMALL maps (7 or 14 columns wide), stride 1, padding k/2: "a lane owns a row".
+// Fused backward for SMALL maps (7, 14 or 28 columns wide), stride 1, padding k/2, fp32 and fp16:
+// "a lane owns a row".
 //
 // rows_backward_kernel gives a lane a few columns of a row and fetches the halo columns from
 // its neighbours by shuffle; on maps this narrow the shuffles, the per-row address selects and
@@ -25,11 +26,11 @@
 // other kernels' and the reference's (torch_dwconv/dwconv_kernel.cu:164-172).
 #pragma once
 
-#include "rows_engine.cuh"
+#include "rows_backward.cuh"
 
 namespace dwb {
 
-constexpr int LANEROW_ZERO_BYTES = 64;  // >= one row of zeros (W <= 16 fp32 columns)
+constexpr int LANEROW_ZERO_BYTES = 128;  // >= one row of zeros (W <= 32 fp32 columns)
 
 struct LaneRowParams {
   const void *x;
@@ -44,6 +45,8 @@ struct LaneRowParams {
   int SL;          // work items (slices of the image list) per channel group
   int DYOFF, XOFF, OUTOFF;  // byte offsets inside a stage (16-byte aligned); the stage starts
                             // with LANEROW_ZERO_BYTES zero bytes
+  void *dw_direct;  // not null: one item per CTA, SL CTAs per cluster, dW written here (see
+                    // cluster_finalize in rows_backward.cuh); `partial` is then unused
 };
 
 __device__ __forceinline__ void bulk_store_s2g(void *dst, const void *src, uint32_t bytes) {
@@ -76,34 +79,93 @@ __device__ __forceinline__ void store_range(T *dst, const T *src16, int n) {
   for (int i = 0; i < tail; ++i) dst[head + interior + i] = src[head + interior + i];
 }
 
-// W floats from shared memory (8-byte aligned when W is even).
-template <int W> __device__ __forceinline__ void lds_row(uint32_t a, float (&v)[W]) {
-  if constexpr (W % 2 == 0) {
+// A row of W elements of T between shared memory and fp32 registers.  Rows start on a multiple
+// of their own length in bytes behind a 16-byte aligned base, so they are 8-byte aligned when that
+// length is a multiple of 8, else 4-byte aligned (W even) or element aligned.
+template <typename T, int W> struct RowIO;
+template <int W> struct RowIO<float, W> {
+  static __device__ __forceinline__ void ld(uint32_t a, float (&v)[W]) {
+    if constexpr (W % 2 == 0) {
 #pragma unroll
-    for (int i = 0; i < W / 2; ++i)
-      asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v[2 * i]), "=f"(v[2 * i + 1]) : "r"(a + 8u * i));
-  } else {
+      for (int i = 0; i < W / 2; ++i)
+        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v[2 * i]), "=f"(v[2 * i + 1]) : "r"(a + 8u * i));
+    } else {
 #pragma unroll
-    for (int i = 0; i < W; ++i) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[i]) : "r"(a + 4u * i));
+      for (int i = 0; i < W; ++i) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[i]) : "r"(a + 4u * i));
+    }
   }
-}
-template <int W> __device__ __forceinline__ void sts_row(uint32_t a, const float (&v)[W]) {
-  if constexpr (W % 2 == 0) {
+  static __device__ __forceinline__ void st(uint32_t a, const float (&v)[W]) {
+    if constexpr (W % 2 == 0) {
 #pragma unroll
-    for (int i = 0; i < W / 2; ++i)
-      asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(a + 8u * i), "f"(v[2 * i]), "f"(v[2 * i + 1]) : "memory");
-  } else {
+      for (int i = 0; i < W / 2; ++i)
+        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(a + 8u * i), "f"(v[2 * i]), "f"(v[2 * i + 1]) : "memory");
+    } else {
 #pragma unroll
-    for (int i = 0; i < W; ++i) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a + 4u * i), "f"(v[i]) : "memory");
+      for (int i = 0; i < W; ++i) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a + 4u * i), "f"(v[i]) : "memory");
+    }
   }
-}
+};
+template <int W> struct RowIO<__half, W> {
+  static __device__ __forceinline__ float2 unpack(uint32_t r) {
+    return __half22float2(*reinterpret_cast<const __half2 *>(&r));
+  }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __half2 h = __halves2half2(__float2half_rn(a), __float2half_rn(b));
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+  static __device__ __forceinline__ void ld(uint32_t a, float (&v)[W]) {
+    if constexpr (W % 4 == 0) {  // rows of a multiple of 8 bytes
+#pragma unroll
+      for (int i = 0; i < W / 4; ++i) {
+        uint32_t r0, r1;
+        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(a + 8u * i));
+        const float2 x = unpack(r0), y = unpack(r1);
+        v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = y.x; v[4 * i + 3] = y.y;
+      }
+    } else if constexpr (W % 2 == 0) {
+#pragma unroll
+      for (int i = 0; i < W / 2; ++i) {
+        uint32_t r0;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(r0) : "r"(a + 4u * i));
+        const float2 x = unpack(r0);
+        v[2 * i] = x.x; v[2 * i + 1] = x.y;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < W; ++i) {
+        unsigned short h;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(a + 2u * i));
+        v[i] = __half2float(__ushort_as_half(h));
+      }
+    }
+  }
+  static __device__ __forceinline__ void st(uint32_t a, const float (&v)[W]) {
+    if constexpr (W % 4 == 0) {
+#pragma unroll
+      for (int i = 0; i < W / 4; ++i)
+        asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(a + 8u * i), "r"(pack(v[4 * i], v[4 * i + 1])),
+                     "r"(pack(v[4 * i + 2], v[4 * i + 3]))
+                     : "memory");
+    } else if constexpr (W % 2 == 0) {
+#pragma unroll
+      for (int i = 0; i < W / 2; ++i)
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(a + 4u * i), "r"(pack(v[2 * i], v[2 * i + 1])) : "memory");
+    } else {
+#pragma unroll
+      for (int i = 0; i < W; ++i)
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(a + 2u * i), "h"(__half_as_ushort(__float2half_rn(v[i])))
+                     : "memory");
+    }
+  }
+};
 
-template <int K, int W, int MINB>
+template <typename T, int K, int W, int MINB>
 __global__ void __launch_bounds__(ROWS_THREADS, MINB)
 lanerow_backward_kernel(const LaneRowParams p, int *__restrict__ error_flag) {
   constexpr int KK = K * K;
   constexpr int P = K / 2;
-  constexpr uint32_t ROWB = W * 4;
+  constexpr int ES = (int)sizeof(T);
+  constexpr uint32_t ROWB = W * ES;
   static_assert(ROWB <= LANEROW_ZERO_BYTES, "a row of zeros must fit the zero block");
   extern __shared__ __align__(128) unsigned char rows_smem[];
   pdl_launch_dependents();  // the second pass may take its place on the SMs early
@@ -115,10 +177,10 @@ lanerow_backward_kernel(const LaneRowParams p, int *__restrict__ error_flag) {
   __syncthreads();
   pdl_wait();  // everything earlier in the stream has completed; global memory may be touched
 
-  const float *__restrict__ gx = static_cast<const float *>(p.x);
-  const float *__restrict__ gdy = static_cast<const float *>(p.dy);
-  const float *__restrict__ gw = static_cast<const float *>(p.w);
-  float *__restrict__ gdx = static_cast<float *>(p.dx);
+  const T *__restrict__ gx = static_cast<const T *>(p.x);
+  const T *__restrict__ gdy = static_cast<const T *>(p.dy);
+  const T *__restrict__ gw = static_cast<const T *>(p.w);
+  T *__restrict__ gdx = static_cast<T *>(p.dx);
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int plane_elems = p.H * W;
@@ -153,11 +215,11 @@ lanerow_backward_kernel(const LaneRowParams p, int *__restrict__ error_flag) {
         uint32_t tx = 0;
         if (lane == 0) {
           fence_proxy_async_smem();
-          tx = stage_range(reinterpret_cast<float *>(sb + p.DYOFF), gdy + pl0 * plane_elems,
+          tx = stage_range(reinterpret_cast<T *>(sb + p.DYOFF), gdy + pl0 * plane_elems,
                            gcount * plane_elems, &ring.full[stage]);
         } else if (lane == 1) {
           fence_proxy_async_smem();
-          tx = stage_range(reinterpret_cast<float *>(sb + p.XOFF), gx + pl0 * plane_elems,
+          tx = stage_range(reinterpret_cast<T *>(sb + p.XOFF), gx + pl0 * plane_elems,
                            gcount * plane_elems, &ring.full[stage]);
         }
         tx = warp_sum(tx);
@@ -170,6 +232,7 @@ lanerow_backward_kernel(const LaneRowParams p, int *__restrict__ error_flag) {
         }
       }
     }
+    if (p.dw_direct != nullptr) cluster_finalize<T>(nullptr, 0, static_cast<T *>(nullptr), 0, false);
     return;
   }
 
@@ -193,11 +256,11 @@ lanerow_backward_kernel(const LaneRowParams p, int *__restrict__ error_flag) {
     // the channel's taps, flipped in both axes, for the whole item
     float taps[K][K];
     {
-      const float *tp = gw + (size_t)(c0 + (active ? g : 0)) * KK;
+      const T *tp = gw + (size_t)(c0 + (active ? g : 0)) * KK;
 #pragma unroll
       for (int ty = 0; ty < K; ++ty)
 #pragma unroll
-        for (int tx = 0; tx < K; ++tx) taps[ty][tx] = active ? __ldg(tp + (KK - 1 - (ty * K + tx))) : 0.f;
+        for (int tx = 0; tx < K; ++tx) taps[ty][tx] = active ? Elem<T>::ld(tp + (KK - 1 - (ty * K + tx))) : 0.f;
     }
     float dwacc[K][K];
 #pragma unroll
@@ -222,16 +285,16 @@ lanerow_backward_kernel(const LaneRowParams p, int *__restrict__ error_flag) {
         const int dphase = slot_phase(gdy + pl0 * plane_elems);
         const int xphase = slot_phase(gx + pl0 * plane_elems);
         const int ophase = slot_phase(gdx + pl0 * plane_elems);
-        const uint32_t dybase = smem_u32(sb + p.DYOFF) + (uint32_t)((dphase + g * plane_elems) * 4);
+        const uint32_t dybase = smem_u32(sb + p.DYOFF) + (uint32_t)((dphase + g * plane_elems) * ES);
         float xr[W], acc[W];
-        lds_row<W>(active ? smem_u32(sb + p.XOFF) + (uint32_t)((xphase + g * plane_elems + r * W) * 4) : zaddr, xr);
+        RowIO<T, W>::ld(active ? smem_u32(sb + p.XOFF) + (uint32_t)((xphase + g * plane_elems + r * W) * ES) : zaddr, xr);
 #pragma unroll
         for (int c = 0; c < W; ++c) acc[c] = 0.f;
 #pragma unroll
         for (int ty = 0; ty < K; ++ty) {
           const int rr = r - P + ty;  // dy row under tap row ty
           float d[W];
-          lds_row<W>((active && (unsigned)rr < (unsigned)p.H) ? dybase + (uint32_t)rr * ROWB : zaddr, d);
+          RowIO<T, W>::ld((active && (unsigned)rr < (unsigned)p.H) ? dybase + (uint32_t)rr * ROWB : zaddr, d);
 #pragma unroll
           for (int tx = 0; tx < K; ++tx) {
 #pragma unroll
@@ -244,7 +307,7 @@ lanerow_backward_kernel(const LaneRowParams p, int *__restrict__ error_flag) {
           }
         }
         if (active)
-          sts_row<W>(smem_u32(sb + p.OUTOFF) + (uint32_t)((ophase + g * plane_elems + r * W) * 4), acc);
+          RowIO<T, W>::st(smem_u32(sb + p.OUTOFF) + (uint32_t)((ophase + g * plane_elems + r * W) * ES), acc);
         fence_proxy_async_smem();  // the rows just written are read by the bulk store below
         __syncwarp();
         if (lane == 0) mbar_arrive(&ring.empty[stage]);  // dy and x of this stage are consumed
@@ -262,12 +325,15 @@ lanerow_backward_kernel(const LaneRowParams p, int *__restrict__ error_flag) {
       if (elected && !aborted) {
         unsigned char *sb = ring.stage(stage);
         const size_t pl0 = (size_t)n * p.C + c0;
-        store_range(gdx + pl0 * plane_elems, reinterpret_cast<const float *>(sb + p.OUTOFF),
+        store_range(gdx + pl0 * plane_elems, reinterpret_cast<const T *>(sb + p.OUTOFF),
                     gcount * plane_elems);
       }
     }
 
-    // item done: per channel, the rows' sums are added in row order, one tap row at a time
+    // item done: per channel, the rows' sums are added in row order, one tap row at a time.
+    // Direct mode: the sums stay in shared memory (the dy area of the first stage: this CTA's
+    // only item is done, and the bulk stores still in flight read the staging areas only).
+    float *fin = reinterpret_cast<float *>(ring.stage(0) + p.DYOFF);
 #pragma unroll
     for (int ty = 0; ty < K; ++ty) {
       consumer_sync();  // the previous tap row's readers are done with `red`
@@ -280,8 +346,16 @@ lanerow_backward_kernel(const LaneRowParams p, int *__restrict__ error_flag) {
         float s = 0.f;
         for (int rr = 0; rr < p.H; ++rr) s += red[(gg * p.H + rr) * K + tx];
         // window position (ty, tx) is the gradient of tap (K-1-ty, K-1-tx)
-        p.partial[((size_t)(c0 + gg) * p.SL + slice) * KK + (KK - 1 - (ty * K + tx))] = s;
+        const int tap = KK - 1 - (ty * K + tx);
+        if (p.dw_direct != nullptr)
+          fin[gg * KK + tap] = s;
+        else
+          p.partial[((size_t)(c0 + gg) * p.SL + slice) * KK + tap] = s;
       }
+    }
+    if (p.dw_direct != nullptr) {
+      consumer_sync();  // fin is complete
+      cluster_finalize<T>(fin, gcount * KK, static_cast<T *>(p.dw_direct) + (size_t)c0 * KK, p.SL, true);
     }
   }
   if (elected) bulk_wait_all();  // every dx tile has left shared memory and reached global memory

@@ -7,7 +7,8 @@
 
 namespace dwb {
 
-enum { ROWS_DECLINED = 0, ROWS_SERVED = 1 };
+// ROWS_SERVED_DW: served, and the kernel finished the filter gradient itself (no second pass).
+enum { ROWS_DECLINED = 0, ROWS_SERVED = 1, ROWS_SERVED_DW = 2 };
 
 template <typename T> int rows_forward(const T *x, const T *w, T *y, const Shape &s, cudaStream_t st);
 // The forward with a fused epilogue (rows_conv_epi.cu); 3x3 / 5x5 / 7x7 only.
@@ -23,11 +24,12 @@ int rows_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *parti
                          cudaStream_t st, int *slices_out);
 
 // Fused backward: dx and the first pass of dW (partial sums, as rows_backward_filter) from one
-// read of dy.
+// read of dy.  With `dw_direct` the kernel may finish dW itself (thread-block clusters over the
+// slices, small problems) and then returns ROWS_SERVED_DW.
 template <typename T> int rows_backward_slices(const Shape &s);
 template <typename T>
 int rows_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<T>::acc_t *partial,
-                  const Shape &s, cudaStream_t st, int *slices_out);
+                  const Shape &s, cudaStream_t st, int *slices_out, T *dw_direct);
 
 // Tiles family (tiles.cu): any padding, any map size; 3x3 / 5x5 / 7x7; fp32, fp16, bf16.
 template <typename T>

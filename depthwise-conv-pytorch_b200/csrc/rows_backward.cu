@@ -10,6 +10,12 @@ namespace {
 
 __device__ int g_backward_error_flag;
 
+// The cluster form of the second pass needs one CTA per work item, all resident at once, and a
+// cluster of at most 8 CTAs (the portable limit).
+inline bool direct_possible(long long items, int slots, int SL) {
+  return items <= slots && SL >= 1 && SL <= 8 && tuning_int("CLUSTER", 1) != 0;
+}
+
 // One CTA per SM where the taps plus the gradient accumulators (2 * K * K registers) leave no
 // room for two.
 constexpr int backward_minb(int K) { return K <= 3 ? 2 : 1; }
@@ -145,6 +151,17 @@ int launch_variant(const RowsBackwardParams &p, cudaStream_t st) {
   if (flag == nullptr) return ROWS_DECLINED;
   const long long items = (long long)p.NCG * p.SL;
   const int grid = (int)min((long long)sm_count() * MINB, items);
+  if (p.dw_direct != nullptr) {
+    // every item has its own CTA: the SL CTAs of a channel group form a cluster that finishes dW
+    static ClusterLimits cluster_ok;
+    if (direct_possible(items, sm_count() * MINB, p.SL) &&
+        launch_dependent_cluster(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, p.SL, cluster_ok, p, flag))
+      return ROWS_SERVED_DW;
+    RowsBackwardParams q = p;
+    q.dw_direct = nullptr;
+    launch_dependent(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, q, flag);
+    return ROWS_SERVED;
+  }
   launch_dependent(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, p, flag);
   return ROWS_SERVED;
 }
@@ -185,19 +202,29 @@ template <> struct RowsDtype<float> { static constexpr bool ok = true; };
 template <> struct RowsDtype<__half> { static constexpr bool ok = true; };
 
 // ---- small maps: a lane owns a row (lanerow_backward.cuh) ----
-// fp32, stride 1, 3x3 / 5x5, maps 7 or 14 columns wide and at most 32 rows high.
+// Stride 1, padding k/2, maps 7, 14 or 28 columns wide and at most 32 rows high; fp32 and fp16.
+// One CTA per SM where 3 * W row registers plus 2 * K * K taps and sums do not leave room for two.
+constexpr bool lanerow_compiled(int K, int W) {
+  return (K == 3 || K == 5 || K == 7) && (W == 7 || W == 14 || W == 28) && !(K == 7 && W == 7);
+}
+constexpr int lanerow_minb(int K, int W) { return (3 * W + 2 * K * K + 24 <= 128) ? 2 : 1; }
+
 inline bool lanerow_shape_ok(const Shape &s) {
-  return s.kh == s.kw && (s.kh == 3 || s.kh == 5) && s.sh == 1 && s.sw == 1 && s.ph == s.kh / 2 &&
-         s.pw == s.kw / 2 && (s.W == 7 || s.W == 14) && s.H <= 32 && s.Ho == s.H && s.Wo == s.W;
+  return s.kh == s.kw && s.sh == 1 && s.sw == 1 && s.ph == s.kh / 2 && s.pw == s.kw / 2 &&
+         lanerow_compiled(s.kh, s.W) && s.H <= 32 && s.Ho == s.H && s.Wo == s.W;
 }
 
-inline bool plan_lanerow(const Shape &s, LaneRowParams &p) {
+// Where the column-per-lane kernel measured faster: 3x3 fp32 on 28-column maps (four columns per
+// lane there: 43.9 against 49.5 us on N128 C192 28x28).
+inline bool lanerow_not_worth_it(const Shape &s, int esize) { return s.kh == 3 && s.W == 28 && esize == 4; }
+
+inline bool plan_lanerow(const Shape &s, int esize, LaneRowParams &p) {
   if (!lanerow_shape_ok(s)) return false;
   const int lanes = ROWS_CWARPS * 32;
   int G = lanes / s.H;
   if (G > s.C) G = s.C;
   if (G < 1) return false;
-  const int plane_bytes = s.H * s.W * 4;
+  const int plane_bytes = s.H * s.W * esize;
   auto region = [&](int g) { return round_up(g * plane_bytes + 16, 16); };
   auto stage_need = [&](int g) { return LANEROW_ZERO_BYTES + 3 * region(g); };
   while (G > 1 && stage_need(G) > ROWS_RING_BYTES / 2) --G;
@@ -208,7 +235,7 @@ inline bool plan_lanerow(const Shape &s, LaneRowParams &p) {
   p.XOFF = p.DYOFF + region(G);
   p.OUTOFF = p.XOFF + region(G);
   p.NCG = ceil_div(s.C, G);
-  const int slots = sm_count() * 2;
+  const int slots = sm_count() * lanerow_minb(s.kh, s.W);
   int SL = slots / p.NCG;
   if (SL < 1 || (long long)SL * p.NCG * 100 < 85ll * slots) SL = ceil_div(2 * slots, p.NCG);
   if (SL > s.N) SL = s.N;
@@ -217,17 +244,42 @@ inline bool plan_lanerow(const Shape &s, LaneRowParams &p) {
   return true;
 }
 
-template <int K, int W>
+template <typename T, int K, int W>
 int launch_lanerow(const LaneRowParams &p, cudaStream_t st) {
-  auto kernel = lanerow_backward_kernel<K, W, 2>;
-  static std::atomic<unsigned long long> smem_done{0};
-  if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
-  int *flag = backward_flag_address();
-  if (flag == nullptr) return ROWS_DECLINED;
-  const long long items = (long long)p.NCG * p.SL;
-  const int grid = (int)min((long long)sm_count() * 2, items);
-  launch_dependent(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, p, flag);
-  return ROWS_SERVED;
+  if constexpr (!lanerow_compiled(K, W)) {
+    return ROWS_DECLINED;
+  } else {
+    constexpr int MINB = lanerow_minb(K, W);
+    auto kernel = lanerow_backward_kernel<T, K, W, MINB>;
+    static std::atomic<unsigned long long> smem_done{0};
+    if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
+    int *flag = backward_flag_address();
+    if (flag == nullptr) return ROWS_DECLINED;
+    const long long items = (long long)p.NCG * p.SL;
+    const int grid = (int)min((long long)sm_count() * MINB, items);
+    if (p.dw_direct != nullptr) {
+      static ClusterLimits cluster_ok;
+      if (direct_possible(items, sm_count() * MINB, p.SL) &&
+          launch_dependent_cluster(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, p.SL, cluster_ok, p, flag))
+        return ROWS_SERVED_DW;
+      LaneRowParams q = p;
+      q.dw_direct = nullptr;
+      launch_dependent(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, q, flag);
+      return ROWS_SERVED;
+    }
+    launch_dependent(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, p, flag);
+    return ROWS_SERVED;
+  }
+}
+
+template <typename T, int K>
+int launch_lanerow_w(const LaneRowParams &p, int W, cudaStream_t st) {
+  switch (W) {
+    case 7: return launch_lanerow<T, K, 7>(p, st);
+    case 14: return launch_lanerow<T, K, 14>(p, st);
+    case 28: return launch_lanerow<T, K, 28>(p, st);
+    default: return ROWS_DECLINED;
+  }
 }
 
 }  // namespace
@@ -242,36 +294,41 @@ template <typename T> int rows_backward_slices(const Shape &s) {
     for (int a16 = 0; a16 < 2; ++a16)
       if (plan_backward<T>(s, a16 != 0, f) && f.p.SL > best) best = f.p.SL;
     LaneRowParams lp{};
-    if (sizeof(T) == 4 && plan_lanerow(s, lp) && lp.SL > best) best = lp.SL;
+    if (plan_lanerow(s, (int)sizeof(T), lp) && lp.SL > best) best = lp.SL;
     return best;
   }
 }
 
 template <typename T>
 int rows_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<T>::acc_t *partial,
-                  const Shape &s, cudaStream_t st, int *slices_out) {
+                  const Shape &s, cudaStream_t st, int *slices_out, T *dw_direct) {
   if constexpr (!RowsDtype<T>::ok) {
     return ROWS_DECLINED;
   } else {
     const bool a16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
                        reinterpret_cast<uintptr_t>(dx)) & 15) == 0;
-    if constexpr (sizeof(T) == 4) {
+    {
       LaneRowParams lp{};
-      if (a16 && tuning_int("LANEROW", 1) != 0 && plan_lanerow(s, lp)) {
+      const int mode = tuning_int("LANEROW", 1);
+      if (a16 && mode != 0 && (mode == 2 || !lanerow_not_worth_it(s, (int)sizeof(T))) &&
+          plan_lanerow(s, (int)sizeof(T), lp)) {
         lp.x = x; lp.dy = dy; lp.w = w; lp.dx = dx; lp.partial = partial;
+        lp.dw_direct = dw_direct;
         *slices_out = lp.SL;
-        switch (s.kh * 100 + s.W) {
-          case 307: return launch_lanerow<3, 7>(lp, st);
-          case 314: return launch_lanerow<3, 14>(lp, st);
-          case 507: return launch_lanerow<5, 7>(lp, st);
-          case 514: return launch_lanerow<5, 14>(lp, st);
+        int r = ROWS_DECLINED;
+        switch (s.kh) {
+          case 3: r = launch_lanerow_w<T, 3>(lp, s.W, st); break;
+          case 5: r = launch_lanerow_w<T, 5>(lp, s.W, st); break;
+          case 7: r = launch_lanerow_w<T, 7>(lp, s.W, st); break;
           default: break;
         }
+        if (r != ROWS_DECLINED) return r;
       }
     }
     BackwardPlan f{};
     if (!plan_backward<T>(s, a16, f)) return ROWS_DECLINED;
     f.p.x = x; f.p.dy = dy; f.p.w = w; f.p.dx = dx; f.p.partial = partial;
+    f.p.dw_direct = dw_direct;
     *slices_out = f.p.SL;
     switch (s.kh * 10 + s.sh) {
       case 31: return launch_backward<T, 3, 1>(f, st);
@@ -301,12 +358,20 @@ int rows_backward_take_error() {
 template int rows_backward_slices<float>(const Shape &);
 template int rows_backward_slices<__half>(const Shape &);
 template int rows_backward_slices<double>(const Shape &);
-template int rows_backward<float>(const float *, const float *, const float *, float *, float *, const Shape &, cudaStream_t, int *);
-template int rows_backward<__half>(const __half *, const __half *, const __half *, __half *, float *, const Shape &, cudaStream_t, int *);
-template int rows_backward<double>(const double *, const double *, const double *, double *, double *, const Shape &, cudaStream_t, int *);
+template int rows_backward<float>(const float *, const float *, const float *, float *, float *, const Shape &, cudaStream_t, int *, float *);
+template int rows_backward<__half>(const __half *, const __half *, const __half *, __half *, float *, const Shape &, cudaStream_t, int *, __half *);
+template int rows_backward<double>(const double *, const double *, const double *, double *, double *, const Shape &, cudaStream_t, int *, double *);
 
 // Tiling the fused backward pass would use, for inspection (same layout as the other plans).
 int rows_debug_backward_plan(int esize, const Shape &s, int a16, int *out) {
+  LaneRowParams lp{};
+  if (a16 && plan_lanerow(s, esize, lp) && !lanerow_not_worth_it(s, esize)) {
+    // the lane-per-row kernel: W columns per lane, one row each
+    const int v[24] = {s.W, s.W, 1, 0, 1, lp.G, 1, s.H, s.H, 1, lp.NST, 1, 0, 0, 0, lp.XOFF, s.N, lp.SL, 0,
+                       lp.NCG, 2 /* lane per row */, 0, 0, 0};
+    for (int i = 0; i < 24; ++i) out[i] = v[i];
+    return 1;
+  }
   BackwardPlan f{};
   bool ok = esize == 4 ? plan_backward<float>(s, a16 != 0, f) : plan_backward<__half>(s, a16 != 0, f);
   if (!ok) return 0;

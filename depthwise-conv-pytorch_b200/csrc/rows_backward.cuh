@@ -21,9 +21,37 @@
 // sums per (channel, slice, tap) have one writer and are added in order by the second pass.
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "rows_engine.cuh"
 
 namespace dwb {
+
+// Second pass inside the first, for problems whose work items all run at once (one per CTA) with
+// at most 8 image slices per channel group: the SL CTAs of a channel group are launched as one
+// thread-block CLUSTER; each leaves its per-channel sums in its own shared memory, the cluster
+// meets, and CTA 0 of the cluster adds the SL values of every (channel, tap) in slice order
+// straight out of the other CTAs' shared memory (distributed shared memory) and writes dW.  No
+// partial sums in global memory, no second kernel: one launch fewer per backward, which is what
+// small problems are made of.  Deterministic (fixed order), no atomics.
+// `fin`: gcount * KK floats in this CTA's shared memory, complete on entry for this CTA's consumer
+// threads (they have met); called by ALL threads of every CTA of the cluster (`worker` false for
+// the producer warp, which only takes part in the two cluster barriers).
+template <typename T>
+__device__ __forceinline__ void cluster_finalize(float *fin, int count, T *__restrict__ dw_group,
+                                                 int slices, bool worker) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();  // every CTA's sums are in its shared memory
+  if (worker && cluster.block_rank() == 0) {
+    for (int idx = threadIdx.x; idx < count; idx += ROWS_CWARPS * 32) {
+      float total = 0.f;
+      for (int r = 0; r < slices; ++r) total += *cluster.map_shared_rank(fin + idx, r);
+      dw_group[idx] = Elem<T>::from_acc(total);
+    }
+  }
+  cluster.sync();  // nobody's shared memory goes away before CTA 0 has read it
+}
 
 struct RowsBackwardParams {
   const void *x;
@@ -43,6 +71,8 @@ struct RowsBackwardParams {
   int SL;     // work items (slices of that tile list) per channel group
   int XOFF;   // byte offset of the x rows inside a stage (16-byte aligned); the stage starts
               // with 16 zero bytes, the dy rows follow
+  void *dw_direct;  // not null: one item per CTA, SL CTAs per cluster, dW written here (see
+                    // cluster_finalize); `partial` is then unused
 };
 
 struct BackwardTile {
@@ -137,6 +167,7 @@ rows_backward_kernel(const RowsBackwardParams p, int *__restrict__ error_flag) {
         }
       }
     }
+    if (p.dw_direct != nullptr) cluster_finalize<T>(nullptr, 0, static_cast<T *>(nullptr), 0, false);
     return;
   }
 
@@ -297,14 +328,21 @@ rows_backward_kernel(const RowsBackwardParams p, int *__restrict__ error_flag) {
         if (j == 0 && seg < ntasks) red[seg * KK + (KK - 1 - (ty * K + tx))] = v;
       }
     consumer_sync();
+    // direct mode: the ring is idle (this CTA's only item is done), its first stage holds the sums
+    float *fin = reinterpret_cast<float *>(ring.stage(0) + 16);
     for (int idx = threadIdx.x; idx < gcount * KK; idx += ROWS_CWARPS * 32) {
       const int gg = idx / KK;
       const int tap = idx - gg * KK;
       float s = 0.f;
       for (int b = 0; b < p.NRB; ++b) s += red[(gg * p.NRB + b) * KK + tap];
-      p.partial[((size_t)(c0 + gg) * p.SL + slice) * KK + tap] = s;
+      if (p.dw_direct != nullptr)
+        fin[idx] = s;
+      else
+        p.partial[((size_t)(c0 + gg) * p.SL + slice) * KK + tap] = s;
     }
-    consumer_sync();  // red is rewritten by the next item
+    consumer_sync();  // red is rewritten by the next item; fin is complete
+    if (p.dw_direct != nullptr)
+      cluster_finalize<T>(fin, gcount * KK, static_cast<T *>(p.dw_direct) + (size_t)c0 * KK, p.SL, true);
   }
 }
 

@@ -4,6 +4,7 @@
 // each translation unit has its own error flag and its own once-only kernel set-up.
 #pragma once
 
+#include "lanerow_conv.cuh"
 #include "rows_plan.cuh"
 
 namespace dwb {
@@ -153,8 +154,81 @@ int select_conv(const RowsParams &p, cudaStream_t st) {
   return ROWS_DECLINED;
 }
 
+// ---- small maps, stride 1: a lane owns a row (lanerow_conv.cuh) ----
+constexpr bool lanerow_conv_compiled(int K, int W) {
+  return (K == 3 || K == 5 || K == 7) && (W == 7 || W == 14 || W == 28) && !(K == 7 && W == 7);
+}
+constexpr int lanerow_conv_minb(int K, int W) { return (2 * W + K * K + 20 <= 128) ? 2 : 1; }
+
+template <typename T, int K, int W>
+int launch_lanerow_conv(const LaneRowConvParams &p, cudaStream_t st) {
+  if constexpr (!lanerow_conv_compiled(K, W)) {
+    return ROWS_DECLINED;
+  } else {
+    constexpr int MINB = lanerow_conv_minb(K, W);
+    auto kernel = lanerow_conv_kernel<T, K, W, MINB>;
+    static std::atomic<unsigned long long> smem_done{0};
+    if (!ensure_smem(kernel, ROWS_SMEM_BYTES, smem_done)) return ROWS_DECLINED;
+    int *flag = conv_flag_address();
+    if (flag == nullptr) return ROWS_DECLINED;
+    const int grid = (int)min((long long)sm_count() * MINB, (long long)p.ntiles);
+    launch_dependent(kernel, grid, ROWS_THREADS, ROWS_SMEM_BYTES, st, p, flag);
+    return ROWS_SERVED;
+  }
+}
+
+template <typename T, int K>
+int launch_lanerow_conv_w(const LaneRowConvParams &p, int W, cudaStream_t st) {
+  switch (W) {
+    case 7: return launch_lanerow_conv<T, K, 7>(p, st);
+    case 14: return launch_lanerow_conv<T, K, 14>(p, st);
+    case 28: return launch_lanerow_conv<T, K, 28>(p, st);
+    default: return ROWS_DECLINED;
+  }
+}
+
+// Maps 7, 14 or 28 columns wide and at most 32 rows high, 16-byte aligned tensors.  3x3 on 14-
+// and 28-column maps stays with the window kernel, which already runs at the speed of a plain
+// copy there (22.0 us against 22.8 us in this layout on N128 C576 14x14, 28.7 against 30.6 us
+// on N128 C192 28x28); 5x5 on 14-column maps: 28.6 against 32.0 us; 7x7: 37.3 against 48.6 us.
+template <typename T>
+int try_lanerow_conv(const RowsParams &rp, int K, int S, cudaStream_t st) {
+  if (S != 1 || !lanerow_conv_compiled(K, rp.Win) || rp.Hin > 32 || rp.Hout != rp.Hin ||
+      rp.Wout != rp.Win || t_plan_out != nullptr)
+    return ROWS_DECLINED;
+  if (((reinterpret_cast<uintptr_t>(rp.in) | reinterpret_cast<uintptr_t>(rp.out)) & 15) != 0)
+    return ROWS_DECLINED;
+  const int mode = tuning_int("LANEROW", 1);
+  if (mode == 0) return ROWS_DECLINED;
+  if (K == 3 && rp.Win >= 14 && mode != 2) return ROWS_DECLINED;
+  LaneRowConvParams p{};
+  const int lanes = ROWS_CWARPS * 32;
+  const int plane_bytes = rp.Hin * rp.Win * (int)sizeof(T);
+  int G = lanes / rp.Hin;
+  if (G > rp.NC) G = rp.NC;
+  auto region = [&](int g) { return round_up(g * plane_bytes + 16, 16); };
+  auto need = [&](int g) { return LANEROW_ZERO_BYTES + 2 * region(g); };
+  while (G > 1 && need(G) > ROWS_RING_BYTES / 2) --G;
+  if (G < 1 || need(G) > ROWS_RING_BYTES / 2) return ROWS_DECLINED;
+  p.NST = need(G) <= ROWS_RING_BYTES / 3 ? 3 : 2;
+  p.in = rp.in; p.w = rp.w; p.out = rp.out;
+  p.NC = rp.NC; p.C = rp.C; p.H = rp.Hin; p.G = G;
+  p.INOFF = LANEROW_ZERO_BYTES;
+  p.OUTOFF = p.INOFF + region(G);
+  p.ntiles = ceil_div(rp.NC, G);
+  p.flip = rp.flip;
+  p.ep = rp.ep;
+  switch (K) {
+    case 3: return launch_lanerow_conv_w<T, 3>(p, rp.Win, st);
+    case 5: return launch_lanerow_conv_w<T, 5>(p, rp.Win, st);
+    case 7: return launch_lanerow_conv_w<T, 7>(p, rp.Win, st);
+    default: return ROWS_DECLINED;
+  }
+}
+
 template <typename T, int MODE, bool EPI>
 int select_k(const RowsParams &p, int K, int S, cudaStream_t st) {
+  if (try_lanerow_conv<T>(p, K, S, st) == ROWS_SERVED) return ROWS_SERVED;
   switch (K * 10 + S) {
     case 31: return select_conv<T, 3, 1, MODE_FWD, EPI>(p, st);
     case 51: return select_conv<T, 5, 1, MODE_FWD, EPI>(p, st);
