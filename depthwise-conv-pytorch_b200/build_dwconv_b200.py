@@ -113,8 +113,65 @@ def _build(force, verbose, defines, lib_path):
     return lib_path
 
 
+BINDING_NAME = "_dwconv_b200_torch"
+BINDING_SRC = os.path.join(CSRC, "torch_binding.cpp")
+BINDING_PATH = os.path.join(LIB_DIR, BINDING_NAME + ".so")
+
+
+def binding_is_stale():
+    if not os.path.exists(BINDING_PATH):
+        return True
+    t = os.path.getmtime(BINDING_PATH)
+    return any(os.path.getmtime(f) > t
+               for f in [BINDING_SRC] + glob.glob(os.path.join(INCLUDE, "*.h")))
+
+
+def build_binding(force=False):
+    """Compile ``csrc/torch_binding.cpp`` (the tensor-level pybind11 module, host code only)
+    into ``lib/_dwconv_b200_torch.so`` with the C++ compiler, against this interpreter's
+    torch headers, linked to ``libdwconv_b200.so`` beside it.  Returns its path.
+
+    The module is an accelerator for the Python call path: ``dwconv_b200._C`` runs over
+    ctypes without it.
+    """
+    if not force and not binding_is_stale():
+        return BINDING_PATH
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension as ce
+    build_library()
+    # the system compiler by name: the module must share the process's libstdc++.so with torch
+    # (a toolchain that links its own static copy yields a module that crashes in iostreams)
+    cxx = os.environ.get("DWCONV_B200_CXX", "g++")
+    flags = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+             f"-DTORCH_EXTENSION_NAME={BINDING_NAME}", "-DTORCH_API_INCLUDE_EXTENSION_H",
+             f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    get_abi = getattr(ce, "_get_pybind11_abi_build_flags", None)
+    if get_abi is not None:
+        flags += get_abi()
+    includes = [INCLUDE, sysconfig.get_path("include")] + ce.include_paths("cuda")
+    lib_dirs = ce.library_paths("cuda")
+    tmp = BINDING_PATH + ".tmp"
+    cmd = ([cxx] + flags + [f"-I{i}" for i in includes] + ["-o", tmp, BINDING_SRC]
+           + [f"-L{d}" for d in lib_dirs + [LIB_DIR]]
+           + ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+              "-ldwconv_b200", "-Wl,-rpath,$ORIGIN"])
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"{cxx} failed on torch_binding.cpp:\n{res.stdout}{res.stderr}")
+    nm = subprocess.run(["nm", "-D", "--defined-only", tmp], capture_output=True, text=True)
+    if nm.returncode == 0 and "_ZNSt8ios_base4InitC1Ev" in nm.stdout:
+        os.remove(tmp)
+        raise RuntimeError(f"{cxx} linked a static copy of libstdc++ into the module; build it with "
+                           "a compiler that links libstdc++.so (set DWCONV_B200_CXX)")
+    os.replace(tmp, BINDING_PATH)
+    return BINDING_PATH
+
+
 if __name__ == "__main__":
     _defs = [a[2:] for a in sys.argv[1:] if a.startswith("-D")]
     _out = next((a[6:] for a in sys.argv[1:] if a.startswith("--out=")), None)
     print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
                         defines=_defs, out=_out))
+    if _out is None and "--no-binding" not in sys.argv:
+        print(build_binding(force="--force" in sys.argv))

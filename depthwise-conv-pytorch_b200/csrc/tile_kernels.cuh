@@ -8,8 +8,13 @@
 // use exactly such shapes (padding 0; 63x65 and 33x35 maps).
 //
 // A CTA takes a tile of TW x 32 (or 32 x 64) outputs of one plane.  All threads copy the input
-// tile with its halo from global to shared memory with coalesced scalar loads (any alignment;
-// elements outside the map become zero, which is the padding), converting to fp32 on the way.
+// tile with its halo from global to shared memory (elements outside the map become zero, which
+// is the padding), converting to fp32 on the way.  Two forms of that copy: 16-byte loads and
+// stores when every row of the map starts on a 16-byte boundary (width a multiple of 4 fp32 /
+// 8 fp16 elements, aligned base): the staged region then starts at the 16-byte boundary at or
+// left of the halo, a 16-byte chunk is either wholly inside the map or wholly padding, and the
+// copy costs about 3 instructions per element; coalesced scalar loads with one bounds test per
+// element for everything else (odd widths, misaligned views, the up-sampled gradient).
 // A thread then owns ONE output column and a strip of R = 8 output rows: it walks the strip's
 // input rows once, reads the K values of a row under its column from shared memory (consecutive
 // threads read consecutive words: no bank conflicts; stride 2 keeps even and odd columns in
@@ -37,6 +42,7 @@ struct TileParams {
   int Hin, Win, Hout, Wout;
   int pt, pl;    // rows / columns of zero padding above / left of the input
   int flip;      // apply the filter flipped in both axes (backward-input)
+  int off;       // 16-byte staging: columns between the staged region's start and the halo's
   int tiles_x, tiles_y;
   long long ntiles;
   EpilogueArgs ep;  // forward with a fused epilogue (ep.on)
@@ -48,15 +54,88 @@ template <int S, int HALF> __device__ __forceinline__ int tile_col(int x) {
   return S == 1 ? x : (x & 1) * HALF + (x >> 1);
 }
 
-template <typename T, int K, int S, int TW>
+// VEC = 0: scalar staging, the staged region starts at the halo.  VEC = 16 / sizeof(T): staging
+// in 16-byte chunks, the staged region starts up to VEC-1 columns left of the halo (`off`).
+template <typename T, int K, int S, int TW, int VEC = 0>
 struct TileGeo {
   static constexpr int TH = TILE_THREADS / TW * TILE_R;     // output rows per tile
   static constexpr int IH = (TH - 1) * S + K;               // input rows per tile
   static constexpr int IW = (TW - 1) * S + K;               // input columns per tile
-  static constexpr int HALF = (IW + 1) / 2;
-  static constexpr int PITCH = S == 1 ? IW : 2 * HALF;
+  static constexpr int NCH = VEC ? (IW + 2 * VEC - 2) / VEC : 0;  // chunks per staged row
+  static constexpr int IWA = VEC ? NCH * VEC : IW;          // staged columns
+  static constexpr int HALF = (IWA + 1) / 2;
+  static constexpr int PITCH = S == 1 ? IWA : 2 * HALF;
   static constexpr int IR = (TILE_R - 1) * S + K;           // input rows under one thread's strip
 };
+
+// 16 bytes of T from global memory (16-byte aligned) as floats.
+__device__ __forceinline__ void ld16(const float *p, float (&v)[4]) {
+  const float4 q = __ldg(reinterpret_cast<const float4 *>(p));
+  v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+}
+__device__ __forceinline__ void ld16(const __half *p, float (&v)[8]) {
+  const uint4 q = __ldg(reinterpret_cast<const uint4 *>(p));
+  const __half2 *h = reinterpret_cast<const __half2 *>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void ld16(const __nv_bfloat16 *p, float (&v)[8]) {
+  const uint4 q = __ldg(reinterpret_cast<const uint4 *>(p));
+  const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+  }
+}
+
+// The input tile in 16-byte chunks: row iy of the tile is map row gy0 + iy, chunk cx of a row
+// holds map columns ax0 + cx*V .. + V-1 with ax0 a multiple of V (so is the map's width: a chunk
+// never straddles the edge).  `sm` is 16-byte aligned, PITCH (and HALF) a multiple of 4 words.
+template <typename T, int S, int IH, int NCH, int HALF, int PITCH>
+__device__ __forceinline__ void tile_stage_vec(float *sm, const T *__restrict__ plane, int Hin, int Win,
+                                               int gy0, int ax0) {
+  constexpr int V = 16 / (int)sizeof(T);
+  constexpr int TOTAL = IH * NCH;
+  constexpr int UNROLL = V == 4 ? 4 : 2;
+  for (int base = threadIdx.x; base < TOTAL; base += TILE_THREADS * UNROLL) {
+    float v[UNROLL][V];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int idx = base + u * TILE_THREADS;
+      const int iy = idx / NCH, cx = idx - iy * NCH;
+      const int gy = gy0 + iy, gx = ax0 + cx * V;
+#pragma unroll
+      for (int e = 0; e < V; ++e) v[u][e] = 0.f;
+      if (idx < TOTAL && (unsigned)gy < (unsigned)Hin && gx >= 0 && gx + V <= Win)
+        ld16(plane + (size_t)gy * Win + gx, v[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int idx = base + u * TILE_THREADS;
+      const int iy = idx / NCH, cx = idx - iy * NCH;
+      if (idx < TOTAL) {
+        if (S == 1) {
+          float4 *d = reinterpret_cast<float4 *>(sm + iy * PITCH + cx * V);
+#pragma unroll
+          for (int q = 0; q < V / 4; ++q)
+            d[q] = make_float4(v[u][4 * q], v[u][4 * q + 1], v[u][4 * q + 2], v[u][4 * q + 3]);
+        } else if (V == 4) {  // even columns in the first half of the row, odd ones in the second
+          float2 *d = reinterpret_cast<float2 *>(sm + iy * PITCH + cx * 2);
+          d[0] = make_float2(v[u][0], v[u][2]);
+          d[HALF / 2] = make_float2(v[u][1], v[u][3]);
+        } else {
+          float4 *d = reinterpret_cast<float4 *>(sm + iy * PITCH + cx * 4);
+          d[0] = make_float4(v[u][0], v[u][2], v[u][4], v[u][6]);
+          d[HALF / 4] = make_float4(v[u][1], v[u][3], v[u][5], v[u][7]);
+        }
+      }
+    }
+  }
+}
 
 // Copies the input tile whose first element is (gy0, gx0) of `plane` into shared memory.
 // UP > 1: (gy, gx) address the map up-sampled by UP with zeros in between ((Hin-1)*UP+1 rows);
@@ -66,13 +145,20 @@ __device__ __forceinline__ void tile_stage(float *sm, const T *__restrict__ plan
                                            int gy0, int gx0) {
   constexpr int TOTAL = IH * IW;
   constexpr int UNROLL = 4;
+  // element idx = base + u*TILE_THREADS sits at (iy, ix); both advance by constants, so the one
+  // division is outside the loop
+  constexpr int DY = TILE_THREADS / IW, DX = TILE_THREADS % IW;
+  int iy = threadIdx.x / IW, ix = threadIdx.x - iy * IW;
   for (int base = threadIdx.x; base < TOTAL; base += TILE_THREADS * UNROLL) {
     float v[UNROLL];
+    int pos[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int idx = base + u * TILE_THREADS;
-      const int iy = idx / IW, ix = idx - iy * IW;
       const int gy = gy0 + iy, gx = gx0 + ix;
+      pos[u] = iy * PITCH + tile_col<S, HALF>(ix);
+      ix += DX; iy += DY;
+      if (ix >= IW) { ix -= IW; ++iy; }
       v[u] = 0.f;
       if (UP == 1) {
         if (idx < TOTAL && (unsigned)gy < (unsigned)Hin && (unsigned)gx < (unsigned)Win)
@@ -84,23 +170,26 @@ __device__ __forceinline__ void tile_stage(float *sm, const T *__restrict__ plan
       }
     }
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int idx = base + u * TILE_THREADS;
-      const int iy = idx / IW, ix = idx - iy * IW;
-      if (idx < TOTAL) sm[iy * PITCH + tile_col<S, HALF>(ix)] = v[u];
-    }
+    for (int u = 0; u < UNROLL; ++u)
+      if (base + u * TILE_THREADS < TOTAL) sm[pos[u]] = v[u];
   }
 }
 
 // out[oy][ox] = sum over (ky, kx) of in[oy*S - pt + ky][ox*S - pl + kx] * tap[ky][kx], `in` being
 // the map up-sampled by UP.
-template <typename T, int K, int S, int TW, int UP = 1>
+template <typename T, int K, int S, int TW, int UP = 1, int VEC = 0>
 __global__ void __launch_bounds__(TILE_THREADS)
 tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restrict__ out,
                  const TileParams p) {
-  using G = TileGeo<T, K, S, TW>;
+  using G = TileGeo<T, K, S, TW, VEC>;
   constexpr int KK = K * K;
-  __shared__ float sm[G::IH * G::PITCH];
+  static_assert(VEC == 0 || UP == 1, "the up-sampled gradient is staged element by element");
+  __shared__ __align__(16) float sm[G::IH * G::PITCH];
+  // position, inside a staged row, of the K columns under this thread's output column
+  int cpos[K];
+#pragma unroll
+  for (int kx = 0; kx < K; ++kx)
+    cpos[kx] = tile_col<S, G::HALF>((VEC ? p.off : 0) + (int)(threadIdx.x % TW) * S + kx);
   const int tc = threadIdx.x % TW;   // output column inside the tile
   const int tr = threadIdx.x / TW;   // strip of TILE_R output rows
   const size_t plane_in = (size_t)p.Hin * p.Win, plane_out = (size_t)p.Hout * p.Wout;
@@ -111,8 +200,13 @@ tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restric
     const int ty = rest / p.tiles_x, tx = rest - ty * p.tiles_x;
     const int y0 = ty * G::TH, x0 = tx * TW;  // first output of the tile
     __syncthreads();                         // the previous tile's readers are done
-    tile_stage<T, S, G::IH, G::IW, G::HALF, G::PITCH, UP>(sm, in + (size_t)plane * plane_in, p.Hin,
-                                                          p.Win, y0 * S - p.pt, x0 * S - p.pl);
+    if constexpr (VEC != 0)
+      tile_stage_vec<T, S, G::IH, G::NCH, G::HALF, G::PITCH>(sm, in + (size_t)plane * plane_in, p.Hin,
+                                                             p.Win, y0 * S - p.pt,
+                                                             x0 * S - p.pl - p.off);
+    else
+      tile_stage<T, S, G::IH, G::IW, G::HALF, G::PITCH, UP>(sm, in + (size_t)plane * plane_in, p.Hin,
+                                                            p.Win, y0 * S - p.pt, x0 * S - p.pl);
     float tap[K][K];
     {
       const T *tp = w + (size_t)(plane % p.C) * KK;
@@ -131,7 +225,7 @@ tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restric
     for (int ir = 0; ir < G::IR; ++ir) {
       float v[K];
 #pragma unroll
-      for (int kx = 0; kx < K; ++kx) v[kx] = row[ir * G::PITCH + tile_col<S, G::HALF>(tc * S + kx)];
+      for (int kx = 0; kx < K; ++kx) v[kx] = row[ir * G::PITCH + cpos[kx]];
 #pragma unroll
       for (int o = 0; o < TILE_R; ++o) {
         const int ky = ir - o * S;
@@ -166,18 +260,23 @@ tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restric
 struct TileFilterParams {
   int N, C, H, W, Ho, Wo;
   int pt, pl;
+  int off;  // as in TileParams
   int SL;
   int tiles_x, tiles_y;
 };
 
-template <typename T, int K, int S, int TW>
+template <typename T, int K, int S, int TW, int VEC = 0>
 __global__ void __launch_bounds__(TILE_THREADS)
 tile_filter_kernel(const T *__restrict__ x, const T *__restrict__ dy, float *__restrict__ partial,
                    const TileFilterParams p) {
-  using G = TileGeo<T, K, S, TW>;
+  using G = TileGeo<T, K, S, TW, VEC>;
   constexpr int KK = K * K;
-  __shared__ float sx[G::IH * G::PITCH];
-  __shared__ float sdy[G::TH * TW];
+  __shared__ __align__(16) float sx[G::IH * G::PITCH];
+  __shared__ __align__(16) float sdy[G::TH * TW];
+  int cpos[K];
+#pragma unroll
+  for (int kx = 0; kx < K; ++kx)
+    cpos[kx] = tile_col<S, G::HALF>((VEC ? p.off : 0) + (int)(threadIdx.x % TW) * S + kx);
   __shared__ float red[TILE_THREADS / 32][KK];
   pdl_launch_dependents();  // the second pass may take its place on the SMs early
   const int c = blockIdx.x / p.SL;
@@ -199,8 +298,15 @@ tile_filter_kernel(const T *__restrict__ x, const T *__restrict__ dy, float *__r
       for (int tx = 0; tx < p.tiles_x; ++tx) {
         const int y0 = ty * G::TH, x0 = tx * TW;
         __syncthreads();
-        tile_stage<T, S, G::IH, G::IW, G::HALF, G::PITCH>(sx, xp, p.H, p.W, y0 * S - p.pt, x0 * S - p.pl);
-        tile_stage<T, 1, G::TH, TW, 0, TW>(sdy, gp, p.Ho, p.Wo, y0, x0);
+        if constexpr (VEC != 0) {
+          tile_stage_vec<T, S, G::IH, G::NCH, G::HALF, G::PITCH>(sx, xp, p.H, p.W, y0 * S - p.pt,
+                                                                 x0 * S - p.pl - p.off);
+          tile_stage_vec<T, 1, G::TH, TW / VEC, 0, TW>(sdy, gp, p.Ho, p.Wo, y0, x0);
+        } else {
+          tile_stage<T, S, G::IH, G::IW, G::HALF, G::PITCH>(sx, xp, p.H, p.W, y0 * S - p.pt,
+                                                            x0 * S - p.pl);
+          tile_stage<T, 1, G::TH, TW, 0, TW>(sdy, gp, p.Ho, p.Wo, y0, x0);
+        }
         __syncthreads();
         float g[TILE_R];
 #pragma unroll
@@ -210,7 +316,7 @@ tile_filter_kernel(const T *__restrict__ x, const T *__restrict__ dy, float *__r
         for (int ir = 0; ir < G::IR; ++ir) {
           float v[K];
 #pragma unroll
-          for (int kx = 0; kx < K; ++kx) v[kx] = row[ir * G::PITCH + tile_col<S, G::HALF>(tc * S + kx)];
+          for (int kx = 0; kx < K; ++kx) v[kx] = row[ir * G::PITCH + cpos[kx]];
 #pragma unroll
           for (int o = 0; o < TILE_R; ++o) {
             const int ky = ir - o * S;

@@ -24,14 +24,34 @@ inline int pick_tw(int Wout) {
   return w32 < w64 ? 32 : 64;
 }
 
+// 16-byte staging needs every row of the map to start on a 16-byte boundary.
+template <typename T> inline bool rows_aligned16(const T *base, int width) {
+  constexpr int V = 16 / (int)sizeof(T);
+  return width % V == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+}
+// Columns between the 16-byte boundary at or left of the halo and the halo: a tile's first
+// output column times the stride is a multiple of the chunk, so only the padding counts.
+template <typename T> inline int stage_off(int pl) {
+  constexpr int V = 16 / (int)sizeof(T);
+  return ((-pl) % V + V) % V;
+}
+
 template <typename T, int K, int S, int TW, int UP = 1>
 void launch_conv(const T *in, const T *w, T *out, TileParams p, cudaStream_t st) {
   constexpr int TH = TileGeo<T, K, S, TW>::TH;
+  constexpr int V = 16 / (int)sizeof(T);
   p.tiles_x = ceil_div(p.Wout, TW);
   p.tiles_y = ceil_div(p.Hout, TH);
   p.ntiles = (long long)p.NC * p.tiles_x * p.tiles_y;
   const long long cap = 148ll * 16;  // grid-stride beyond this
   const int grid = (int)(p.ntiles < cap ? p.ntiles : cap);
+  if constexpr (UP == 1) {
+    if (rows_aligned16(in, p.Win)) {
+      p.off = stage_off<T>(p.pl);
+      tile_conv_kernel<T, K, S, TW, 1, V><<<grid, TILE_THREADS, 0, st>>>(in, w, out, p);
+      return;
+    }
+  }
   tile_conv_kernel<T, K, S, TW, UP><<<grid, TILE_THREADS, 0, st>>>(in, w, out, p);
 }
 
@@ -61,6 +81,18 @@ void launch_filter(const T *x, const T *dy, float *partial, TileFilterParams p, 
   constexpr int TH = TileGeo<T, K, S, TW>::TH;
   p.tiles_x = ceil_div(p.Wo, TW);
   p.tiles_y = ceil_div(p.Ho, TH);
+  constexpr int V = 16 / (int)sizeof(T);
+  using GV = TileGeo<T, K, S, TW, V>;
+  // the wider staged rows of the 16-byte form must still fit the static shared memory of a CTA
+  constexpr bool fits =
+      (GV::IH * GV::PITCH + GV::TH * TW + TILE_THREADS / 32 * K * K) * sizeof(float) <= 48 * 1024;
+  if constexpr (fits) {
+    if (rows_aligned16(x, p.W) && rows_aligned16(dy, p.Wo)) {
+      p.off = stage_off<T>(p.pl);
+      tile_filter_kernel<T, K, S, TW, V><<<p.C * p.SL, TILE_THREADS, 0, st>>>(x, dy, partial, p);
+      return;
+    }
+  }
   tile_filter_kernel<T, K, S, TW><<<p.C * p.SL, TILE_THREADS, 0, st>>>(x, dy, partial, p);
 }
 

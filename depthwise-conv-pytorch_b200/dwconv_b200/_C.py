@@ -4,6 +4,11 @@ the reference's pybind11 module ``torch_dwconv._C`` (torch_dwconv/dwconv.cpp:60-
 Each function takes torch tensors, allocates the result with torch (the shared
 library never allocates) and calls the matching C entry point on the tensor's
 device and the current stream of that device.
+
+The four operator functions below are written over ``ctypes``; when the compiled module
+``csrc/torch_binding.cpp`` has been built (``_lib.native``), the names are bound to its
+functions instead: same arguments, same checks and texts, a few microseconds of host time
+per call instead of 15-20.
 """
 import torch
 
@@ -142,3 +147,13 @@ def dwconv2d_backward_kernel(input, out_grad, kernel, up_h, up_w, down_h, down_w
             N, C, H, W, oh, ow, kh, kw, up_h, up_w, down_h, down_w, pad_h, pad_w, _stream(input))
     _lib.check(st, "dwconv2d_backward_kernel")
     return dkernel
+
+
+# the ctypes forms stay reachable (tests compare the two call paths)
+CTYPES_FORMS = {"dwconv2d": dwconv2d, "dwconv2d_small": dwconv2d_small,
+                "dwconv2d_backward_kernel": dwconv2d_backward_kernel}
+
+if _lib.native is not None:
+    dwconv2d = _lib.native.dwconv2d
+    dwconv2d_small = _lib.native.dwconv2d_small
+    dwconv2d_backward_kernel = _lib.native.dwconv2d_backward_kernel

@@ -85,6 +85,43 @@ def _load():
 
 
 lib = _load()
+
+NATIVE_PATH = os.path.join(os.path.dirname(LIB_PATH), "_dwconv_b200_torch.so")
+
+
+def _load_native():
+    """The compiled tensor-level module (``csrc/torch_binding.cpp``), or None.
+
+    It is an accelerator for the Python call path, not a second implementation: it calls the
+    same ``libdwconv_b200.so`` (linked by a relative run path, so the dynamic loader hands it
+    the image ``ctypes`` loaded above).  Not used when ``DWCONV_B200_LIB`` points at another
+    library, when ``DWCONV_B200_NO_NATIVE`` is set, or when it was built against another
+    library version.
+    """
+    if (os.environ.get("DWCONV_B200_NO_NATIVE", "0") not in ("", "0")
+            or "DWCONV_B200_LIB" in os.environ or not os.path.exists(NATIVE_PATH)):
+        return None
+    import importlib.machinery
+    import importlib.util
+    import torch  # noqa: F401  (the module's torch symbols must be loaded first)
+    name = "_dwconv_b200_torch"
+    try:
+        loader = importlib.machinery.ExtensionFileLoader(name, NATIVE_PATH)
+        spec = importlib.util.spec_from_file_location(name, NATIVE_PATH, loader=loader)
+        mod = importlib.util.module_from_spec(spec)
+        loader.exec_module(mod)
+    except ImportError as e:  # built against another torch: say so once, run over ctypes
+        import warnings
+        warnings.warn(f"dwconv_b200: {NATIVE_PATH} does not load ({e}); using the ctypes path. "
+                      f"Rebuild it with `{_BUILD_HINT}`.")
+        return None
+    if mod.library_version() != lib.dwconv_b200_version():
+        return None
+    return mod
+
+
+native = _load_native()
+
 EXPORTS = (
     "dwconv_b200_version", "dwconv_b200_status_string", "dwconv_b200_last_cuda_error",
     "dwconv_b200_set_path", "dwconv_b200_last_path", "dwconv_b200_device_status",

@@ -19,6 +19,8 @@ from torch.nn import functional as F
 
 from . import _C, _lib
 
+_native = _lib.native
+
 
 def use_dwconv2d_small(input, weight, up, stride, padding):
     """torch_dwconv/dwconv.py:9-12."""
@@ -76,11 +78,18 @@ class DepthwiseConv2dFunction(Function):
 
     @staticmethod
     def forward(ctx, input, kernel, stride, pad, small=False):
+        stride = tuple(int(v) for v in stride)
+        pad = tuple(int(v) for v in pad)
+        ctx.stride, ctx.pad, ctx.use_small = stride, pad, small
+        if _native is not None:
+            # checks, layout decisions, allocation and the library call in one compiled call
+            out, input, kernel, ctx.nhwc = _native.forward(input, kernel, stride[0], stride[1],
+                                                           pad[0], pad[1])
+            ctx.save_for_backward(input, kernel)
+            return out
         _C._check_cuda(input, "input")
         _C._check_cuda(kernel, "kernel")
         code = _C._dtype_code(input, kernel)
-        stride = tuple(int(v) for v in stride)
-        pad = tuple(int(v) for v in pad)
         _C._check_filter(input, kernel)
         # channels-last maps are read and written in place (no NCHW copy); the result follows
         # the input's layout, as PyTorch's own convolution does
@@ -105,18 +114,19 @@ class DepthwiseConv2dFunction(Function):
         ctx.save_for_backward(input, kernel)
         ctx.shape = shape
         ctx.code = code
-        ctx.stride = stride
-        ctx.pad = pad
-        ctx.use_small = small
-        # what the reference's backward passes to its operator (dwconv.py:39-44);
-        # kept for introspection, the C entry point takes the forward geometry
-        ctx.g_pad = (shape.kh - pad[0] - 1, shape.H - shape.Ho * stride[0] + pad[0],
-                     shape.kw - pad[1] - 1, shape.W - shape.Wo * stride[1] + pad[1])
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
         input, kernel = ctx.saved_tensors
+        if _native is not None:
+            stride, pad = ctx.stride, ctx.pad
+            grad_input, grad_kernel = _native.backward(
+                input, grad_output, kernel, stride[0], stride[1], pad[0], pad[1], ctx.nhwc,
+                ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+            if _lib.CHECK_STATUS:
+                _lib.check_device_status("backward")
+            return grad_input, grad_kernel, None, None, None
         shape, code = ctx.shape, ctx.code
         if tuple(grad_output.shape) != (shape.N, shape.C, shape.Ho, shape.Wo):
             raise RuntimeError(f"depthwise_conv2d backward: grad_output has shape "

@@ -31,9 +31,11 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture(scope="session", autouse=True)
 def _built_library():
-    """The shared library is built from source once per session (nvcc needs no GPU)."""
-    from build_dwconv_b200 import build_library
+    """The shared library and the compiled tensor-level module are built from source once per
+    session (neither nvcc nor the C++ compiler needs a GPU)."""
+    from build_dwconv_b200 import build_binding, build_library
     build_library()
+    build_binding()
 
 
 class Golden:

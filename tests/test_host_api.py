@@ -143,6 +143,40 @@ def test_cpu_tensors_never_fall_back():
                                       torch.zeros(2, 1, 3, 3), 1, 1, 1, 1, 1, 1)
 
 
+def test_compiled_binding_loads_and_mirrors_the_ctypes_forms():
+    """The pybind11 module is built, loads without a GPU, reports the library's version, has the
+    reference module's four names plus forward / backward, and refuses bad arguments with the
+    same texts as the ctypes forms it replaces."""
+    import dwconv_b200 as d
+    from dwconv_b200 import _lib
+    nat = _lib.native
+    assert nat is not None, "lib/_dwconv_b200_torch.so missing: run build_dwconv_b200.py"
+    assert nat.library_version() == _lib.lib.dwconv_b200_version()
+    for fn in ("use_dwconv2d_small", "dwconv2d", "dwconv2d_small", "dwconv2d_backward_kernel",
+               "forward", "backward"):
+        assert callable(getattr(nat, fn))
+    assert d._C.dwconv2d is nat.dwconv2d
+    x, w = torch.zeros(1, 2, 8, 8), torch.zeros(2, 1, 3, 3)
+    bad = [
+        ("dwconv2d", (x, w, 1, 1, 1, 1, 1, 1, 1, 1, True)),
+        ("dwconv2d", (x.cuda() if torch.cuda.is_available() else x, w, 1, 1, 1, 1, 1, 1, 1, 1, True)),
+        ("dwconv2d_small", (x, w, 1, 1, 1, 1, 1, 1, True)),
+        ("dwconv2d_backward_kernel", (x, x, w, 1, 1, 1, 1, 1, 1)),
+    ]
+    for name, args in bad:
+        texts = []
+        for fn in (d._C.CTYPES_FORMS[name], getattr(nat, name)):
+            with pytest.raises(RuntimeError) as ei:
+                fn(*args)
+            texts.append(str(ei.value).splitlines()[0])
+        assert texts[0] == texts[1], name
+    for small in ((14, 14, 3, 1, 1), (40, 40, 3, 1, 1), (14, 14, 5, 2, 2), (7, 7, 3, 1, 0)):
+        H, W, k, s, p = small
+        xs, ws = torch.zeros(1, 1, H, W), torch.zeros(1, 1, k, k)
+        assert nat.use_dwconv2d_small(xs, ws, 1, 1, s, s, p, p) == \
+            d._C.use_dwconv2d_small(xs, ws, 1, 1, s, s, p, p)
+
+
 def test_module_surface_and_state_dict():
     import dwconv_b200 as d
     m = d.DepthwiseConv2d(6, 6, 5, stride=2, padding=2)

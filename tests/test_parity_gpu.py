@@ -246,6 +246,21 @@ def test_misaligned_views_are_served():
     dyo = bufd[3:3 + dy.numel()].view_as(dy).copy_(dy)
     assert xo.data_ptr() % 16 != 0 and dyo.data_ptr() % 16 != 0
     _check_three_ops(xo, w, dyo, 1, 1, torch.float32, "auto", "misaligned")
+    # the tile kernels copy in 16-byte chunks when rows are aligned and element by element
+    # otherwise: the same map through both, and only one of the two operands misaligned
+    for dt, cfg in ((torch.float32, (2, 3, 40, 72, 5, 1, 0)), (torch.float16, (2, 3, 40, 72, 3, 2, 1))):
+        N, C, H, W, k, s, p = cfg
+        x, w, dy = seeded((N, C, H, W), (k, k), s, p, dt, seed=7)
+        buf = torch.zeros(x.numel() + 3, device="cuda", dtype=dt)
+        xo = buf[1:1 + x.numel()].view_as(x).copy_(x)
+        bufd = torch.zeros(dy.numel() + 3, device="cuda", dtype=dt)
+        dyo = bufd[1:1 + dy.numel()].view_as(dy).copy_(dy)
+        assert xo.data_ptr() % 16 != 0 and dyo.data_ptr() % 16 != 0
+        want = _check_three_ops(x, w, dy, s, p, dt, "tiles", "tiles aligned")
+        for xa, dya, what in ((xo, dyo, "both"), (xo, dy, "x"), (x, dyo, "dy")):
+            got = _check_three_ops(xa, w, dya, s, p, dt, "tiles", f"tiles misaligned {what}")
+            for key in ("y", "dx", "dw"):
+                assert torch.equal(got[key], want[key]), f"{what}/{key}"
 
 
 def test_operator_form_entry_points():
@@ -290,6 +305,76 @@ def test_autograd_matches_pytorch_autograd():
         assert (ya - yb).abs().max().item() <= tol * max(1.0, yb.abs().max().item())
         assert (xa.grad - xb.grad).abs().max().item() <= tol * max(1.0, xb.grad.abs().max().item())
         assert (wa.grad - wb.grad).abs().max().item() <= tol * max(1.0, wb.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc", "strided"])
+def test_compiled_and_ctypes_call_paths_agree(layout, monkeypatch):
+    """The autograd function runs through the compiled tensor-level module when it is built
+    and over ctypes otherwise; the operator functions likewise.  Same library calls, so the
+    same bits, the same layouts of the results and the same gradients asked for."""
+    import dwconv_b200
+    from dwconv_b200 import dwconv as dw_mod
+    nat = _lib.native
+    assert nat is not None, "lib/_dwconv_b200_torch.so missing: run build_dwconv_b200.py"
+    for dt, (N, C, H, W, k, s, p) in [(torch.float32, (4, 6, 28, 28, 3, 2, 1)),
+                                      (torch.float32, (3, 8, 14, 14, 5, 1, 2)),
+                                      (torch.float16, (2, 4, 28, 28, 7, 1, 3)),
+                                      (torch.float32, (2, 3, 19, 23, 3, 1, 0)),
+                                      (torch.float64, (2, 3, 19, 23, 3, 1, 1))]:
+        x, w, dy = seeded((N, C, H, W), (k, k), s, p, dt, seed=k + H)
+        if layout == "nhwc":
+            x = x.contiguous(memory_format=torch.channels_last)
+        elif layout == "strided":
+            x = x.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
+        got = []
+        for use_native in (True, False):
+            monkeypatch.setattr(dw_mod, "_native", nat if use_native else None)
+            xa, wa = x.clone(memory_format=torch.preserve_format).requires_grad_(True), \
+                w.clone().requires_grad_(True)
+            if layout == "strided":
+                xa = x.detach().requires_grad_(True)
+            y = dwconv_b200.depthwise_conv2d(xa, wa, None, s, p)
+            y.backward(dy)
+            got.append((y.detach(), xa.grad, wa.grad))
+            # only one gradient asked for
+            xo = x.detach().clone(memory_format=torch.preserve_format).requires_grad_(True)
+            dwconv_b200.depthwise_conv2d(xo, w, None, s, p).backward(dy)
+            assert torch.equal(xo.grad, xa.grad)
+            wo = w.detach().clone().requires_grad_(True)
+            dwconv_b200.depthwise_conv2d(x, wo, None, s, p).backward(dy)
+            assert wo.grad is not None and x.grad is None
+        (ya, dxa, dwa), (yb, dxb, dwb) = got
+        assert torch.equal(ya, yb) and ya.stride() == yb.stride()
+        assert torch.equal(dxa, dxb) and dxa.stride() == dxb.stride()
+        assert torch.equal(dwa, dwb)
+        if dt != torch.float64:
+            assert torch.equal(ya.contiguous().cpu(), oracle.forward_seq(x.contiguous(), w, s, p))
+    # a grad_output of the wrong shape is refused by both (autograd itself never hands one over;
+    # the context here is a stand-in with the attributes the function keeps on a real one)
+    class Ctx:
+        needs_input_grad = (True, True, False, False, False)
+
+        def save_for_backward(self, *t):
+            self.saved_tensors = t
+
+    x, w, dy = seeded((2, 3, 14, 14), (3, 3), 1, 1, torch.float32, seed=4)
+    for use_native in (True, False):
+        monkeypatch.setattr(dw_mod, "_native", nat if use_native else None)
+        ctx = Ctx()
+        y = dw_mod.DepthwiseConv2dFunction.forward(ctx, x, w, (1, 1), (1, 1))
+        assert torch.equal(y.cpu(), oracle.forward_seq(x, w, 1, 1))
+        with pytest.raises(RuntimeError, match="grad_output has shape"):
+            dw_mod.DepthwiseConv2dFunction.backward(ctx, dy[:, :, :7])
+        dx, dw = dw_mod.DepthwiseConv2dFunction.backward(ctx, dy)[:2]
+        assert torch.equal(dx.cpu(), oracle.backward_input_seq(dy, w, (14, 14), 1, 1))
+    # the operator functions
+    C_ = dwconv_b200._C
+    for (H, W, k, s, p) in [(40, 44, 3, 2, 1), (14, 14, 3, 1, 1)]:
+        x, w, dy = seeded((2, 3, H, W), (k, k), s, p, torch.float32, seed=H)
+        for name, args in (("dwconv2d", (x, w, 1, 1, s, s, p, p, p, p, True)),
+                           ("dwconv2d_small", (x, w, 1, 1, s, s, p, p, True)),
+                           ("dwconv2d_backward_kernel", (x, dy, w, 1, 1, s, s, p, p))):
+            assert torch.equal(getattr(nat, name)(*args), C_.CTYPES_FORMS[name](*args)), name
 
 
 def test_autograd_only_computes_requested_gradients():
@@ -371,6 +456,10 @@ TILES_CASES = [
     (1, 3, 130, 150, 7, 2, 3), (2, 2, 40, 200, 5, 1, 1), (1, 2, 50, 70, 5, 1, (0, 2)),
     (1, 2, 40, 40, 3, 1, 2), (1, 2, 33, 35, 5, 2, (4, 1)), (2, 2, 40, 300, 7, 2, 0),
     (1, 1, 97, 33, 3, 1, 0), (1, 2, 129, 129, 7, 1, 6),
+    # rows that start on 16-byte boundaries (copied in 16-byte chunks): every distance between
+    # the chunk boundary and the halo, tiles that end mid-map, stride 2 with its split rows
+    (2, 2, 40, 100, 3, 1, 1), (1, 3, 48, 136, 5, 2, 3), (2, 2, 33, 72, 7, 2, 3), (1, 2, 70, 36, 5, 1, 3),
+    (1, 2, 40, 160, 7, 1, 5), (2, 1, 64, 96, 3, 2, 2), (1, 2, 36, 88, 5, 2, 0), (1, 2, 66, 264, 7, 2, (2, 6)),
 ]
 
 
