@@ -160,6 +160,8 @@ size_t filter_workspace_t(const Shape &s) {
   if (fs > slices) slices = fs;
   const size_t ns = (size_t)nhwc_filter_slices(s);  // and so do the channels-last kernels
   if (ns > slices) slices = ns;
+  const size_t ts = (size_t)tiles_filter_slices(s);  // and the tiles family
+  if (ts > slices) slices = ts;
   size_t b = (size_t)s.C * slices * kk * sizeof(A);
   return b < 16 ? 16 : ((b + 15) / 16) * 16;
 }
@@ -183,9 +185,10 @@ int filter_first_pass_t(const void *x, const void *dy, void *ws, size_t ws_bytes
     }
   }
   if (S == 0 && (forced == DWCONV_B200_PATH_AUTO || forced == DWCONV_B200_PATH_TILES)) {
-    const int slices = direct_filter_slices(s);  // the same batch split as the kernels below
-    if (tiles_backward_filter<T>((const T *)x, (const T *)dy, (A *)ws, s, slices, st) == ROWS_SERVED) {
-      S = slices;
+    int used = 0;
+    if (tiles_backward_filter<T>((const T *)x, (const T *)dy, (A *)ws, s, tiles_filter_slices(s), st,
+                                 &used) == ROWS_SERVED) {
+      S = used;
       t_last_path = DWCONV_B200_PATH_TILES;
       int e = launch_status();
       if (e != DWCONV_B200_OK) return e;

@@ -36,9 +36,13 @@ template <typename T>
 int tiles_forward(const T *x, const T *w, T *y, const Shape &s, const EpilogueArgs &ep, cudaStream_t st);
 template <typename T>
 int tiles_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStream_t st);
+// Upper bound of the slices per channel the tiles family's filter-gradient first pass uses
+// (0: the family does not serve the shape); sizes the workspace.
+int tiles_filter_slices(const Shape &s);
+// `slices` is that bound; *slices_used (<= slices) is what the launch wrote.
 template <typename T>
 int tiles_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *partial, const Shape &s,
-                          int slices, cudaStream_t st);
+                          int slices, cudaStream_t st, int *slices_used);
 
 // Channels-last (NHWC) operators (nhwc.cu): 3x3 / 5x5 / 7x7, stride 1 or 2, any padding; fp32,
 // fp16, bf16.

@@ -193,12 +193,14 @@ tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restric
   const int tc = threadIdx.x % TW;   // output column inside the tile
   const int tr = threadIdx.x / TW;   // strip of TILE_R output rows
   const size_t plane_in = (size_t)p.Hin * p.Win, plane_out = (size_t)p.Hout * p.Wout;
-  const int per_plane = p.tiles_x * p.tiles_y;
-  for (long long tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
-    const int plane = (int)(tile / per_plane);
-    const int rest = (int)(tile - (long long)plane * per_plane);
-    const int ty = rest / p.tiles_x, tx = rest - ty * p.tiles_x;
-    const int y0 = ty * G::TH, x0 = tx * TW;  // first output of the tile
+  // grid: x = the tile's position inside a plane, y = first plane; a CTA keeps its position and
+  // walks the planes y, y + gridDim.y, ... (no division inside the loop; neighbouring CTAs
+  // work on neighbouring tiles of one plane, so halo columns and rows are re-read from L2)
+  const int ty = (int)blockIdx.x / p.tiles_x, tx = (int)blockIdx.x - ty * p.tiles_x;
+  const int y0 = ty * G::TH, x0 = tx * TW;  // first output of the tile
+  int chan = (int)blockIdx.y % p.C;
+  const int chan_step = (int)gridDim.y % p.C;
+  for (int plane = blockIdx.y; plane < p.NC; plane += gridDim.y) {
     __syncthreads();                         // the previous tile's readers are done
     if constexpr (VEC != 0)
       tile_stage_vec<T, S, G::IH, G::NCH, G::HALF, G::PITCH>(sm, in + (size_t)plane * plane_in, p.Hin,
@@ -209,7 +211,7 @@ tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restric
                                                             p.Win, y0 * S - p.pt, x0 * S - p.pl);
     float tap[K][K];
     {
-      const T *tp = w + (size_t)(plane % p.C) * KK;
+      const T *tp = w + (size_t)chan * KK;
 #pragma unroll
       for (int ky = 0; ky < K; ++ky)
 #pragma unroll
@@ -237,22 +239,28 @@ tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restric
     }
     if (p.ep.on) {
       float sc, bi;
-      epilogue_coeffs<T>(p.ep, plane % p.C, sc, bi);
+      epilogue_coeffs<T>(p.ep, chan, sc, bi);
 #pragma unroll
       for (int o = 0; o < TILE_R; ++o) acc[o] = apply_epilogue<float>(acc[o], sc, bi, p.ep.act);
     }
     const int ox = x0 + tc;
     if (ox < p.Wout) {
       T *op = out + (size_t)plane * plane_out + (size_t)(y0 + tr * TILE_R) * p.Wout + ox;
+      const int rows = p.Hout - (y0 + tr * TILE_R);  // rows of this strip inside the map
 #pragma unroll
-      for (int o = 0; o < TILE_R; ++o)
-        if (y0 + tr * TILE_R + o < p.Hout) op[(size_t)o * p.Wout] = Elem<T>::from_acc(acc[o]);
+      for (int o = 0; o < TILE_R; ++o) {
+        if (o < rows) *op = Elem<T>::from_acc(acc[o]);
+        op += p.Wout;
+      }
     }
+    chan += chan_step;
+    if (chan >= p.C) chan -= p.C;
   }
 }
 
-// Backward-filter, first pass.  Block (c, slice) owns the images [slice*N/SL, (slice+1)*N/SL) of
-// channel c and walks their tiles: the x tile (with halo) and the dy tile are staged in shared
+// Backward-filter, first pass.  Block (c, slice) owns one of SL equal ranges of channel c's tiles
+// (all images, image-major; SL may exceed the batch size) and walks them: the x tile (with halo)
+// and the dy tile are staged in shared
 // memory; a thread owns one dy column and a strip of dy rows, keeps K*K accumulators, walks the
 // strip's x rows once and adds dy[o] * x-row values to the tap row each (x row, dy row) pair
 // belongs to.  At the end the block adds its threads' accumulators in a fixed order (warp
@@ -281,8 +289,13 @@ tile_filter_kernel(const T *__restrict__ x, const T *__restrict__ dy, float *__r
   pdl_launch_dependents();  // the second pass may take its place on the SMs early
   const int c = blockIdx.x / p.SL;
   const int slice = blockIdx.x - c * p.SL;
-  const int n0 = (int)((long long)slice * p.N / p.SL);
-  const int n1 = (int)((long long)(slice + 1) * p.N / p.SL);
+  // the channel's tiles, image-major, in SL contiguous ranges of equal length (+-1)
+  const int per_img = p.tiles_x * p.tiles_y;
+  const long long total = (long long)p.N * per_img;
+  const long long t0 = slice * total / p.SL, t1 = (slice + 1) * total / p.SL;
+  int n = (int)(t0 / per_img);
+  int ty = (int)(t0 - (long long)n * per_img) / p.tiles_x;
+  int tx = (int)(t0 - (long long)n * per_img) - ty * p.tiles_x;
   const int tc = threadIdx.x % TW, tr = threadIdx.x / TW;
   const size_t plane_x = (size_t)p.H * p.W, plane_dy = (size_t)p.Ho * p.Wo;
   float acc[K][K];
@@ -291,11 +304,11 @@ tile_filter_kernel(const T *__restrict__ x, const T *__restrict__ dy, float *__r
 #pragma unroll
     for (int kx = 0; kx < K; ++kx) acc[ky][kx] = 0.f;
 
-  for (int n = n0; n < n1; ++n) {
+  for (long long t = t0; t < t1; ++t) {
     const T *xp = x + ((size_t)n * p.C + c) * plane_x;
     const T *gp = dy + ((size_t)n * p.C + c) * plane_dy;
-    for (int ty = 0; ty < p.tiles_y; ++ty)
-      for (int tx = 0; tx < p.tiles_x; ++tx) {
+    {
+      {
         const int y0 = ty * G::TH, x0 = tx * TW;
         __syncthreads();
         if constexpr (VEC != 0) {
@@ -327,6 +340,11 @@ tile_filter_kernel(const T *__restrict__ x, const T *__restrict__ dy, float *__r
           }
         }
       }
+    }
+    if (++tx == p.tiles_x) {
+      tx = 0;
+      if (++ty == p.tiles_y) { ty = 0; ++n; }
+    }
   }
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 #pragma unroll

@@ -2,7 +2,14 @@
 #include "tile_kernels.cuh"
 #include "rows_api.cuh"
 
+#include <atomic>
+#include <cstdlib>
+
 namespace dwb {
+
+// tiles_tma.cu: the stride-1 kernels whose input tile arrives by one tensor copy.
+template <typename T>
+int tiles_tma_conv(const T *in, const T *w, T *out, const TileParams &p, int K, int tw, cudaStream_t st);
 
 namespace {
 
@@ -24,6 +31,16 @@ inline int pick_tw(int Wout) {
   return w32 < w64 ? 32 : 64;
 }
 
+// Tuning builds can switch the tensor-copy kernels off to time the other staging forms.
+inline bool tiles_tma_off() {
+#ifdef DWCONV_B200_TUNING
+  const char *v = getenv("DWCONV_B200_TILES_TMA");
+  return v != nullptr && v[0] == '0';
+#else
+  return false;
+#endif
+}
+
 // 16-byte staging needs every row of the map to start on a 16-byte boundary.
 template <typename T> inline bool rows_aligned16(const T *base, int width) {
   constexpr int V = 16 / (int)sizeof(T);
@@ -43,10 +60,21 @@ void launch_conv(const T *in, const T *w, T *out, TileParams p, cudaStream_t st)
   p.tiles_x = ceil_div(p.Wout, TW);
   p.tiles_y = ceil_div(p.Hout, TH);
   p.ntiles = (long long)p.NC * p.tiles_x * p.tiles_y;
-  const long long cap = 148ll * 16;  // grid-stride beyond this
-  const int grid = (int)(p.ntiles < cap ? p.ntiles : cap);
+  // x: tile position inside a plane; y: as many planes side by side as keep about 16 CTAs per
+  // SM in the grid, the rest of the planes by striding inside the kernel
+  const int per_plane = p.tiles_x * p.tiles_y;
+  const int cap = 148 * 16;
+  int gy = cap / per_plane;
+  if (gy < 1) gy = 1;
+  if (gy > p.NC) gy = p.NC;
+  const dim3 grid(per_plane, gy);
   if constexpr (UP == 1) {
     if (rows_aligned16(in, p.Win)) {
+      // stride 1: one tensor copy per tile; else (or if the driver offers no encoder) 16-byte
+      // loads and stores through registers
+      if constexpr (S == 1) {
+        if (!tiles_tma_off() && tiles_tma_conv<T>(in, w, out, p, K, TW, st) == ROWS_SERVED) return;
+      }
       p.off = stage_off<T>(p.pl);
       tile_conv_kernel<T, K, S, TW, 1, V><<<grid, TILE_THREADS, 0, st>>>(in, w, out, p);
       return;
@@ -76,8 +104,38 @@ int conv_dispatch(const T *in, const T *w, T *out, const TileParams &p, int K, i
   }
 }
 
+// Resident CTAs of a kernel on the whole device (asked once per instantiation).
+template <typename Kernel> int resident_ctas(Kernel kernel) {
+  static std::atomic<int> cached{0};
+  int v = cached.load(std::memory_order_relaxed);
+  if (v == 0) {
+    int per_sm = 0, dev = 0, sms = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, TILE_THREADS, 0) != cudaSuccess ||
+        cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return 148;
+    }
+    v = per_sm * sms;
+    if (v < 1) v = 1;
+    cached.store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+// Slices per channel: as many as give every CTA a place on the device at once (one wave of
+// CTAs with equal tile counts), within the bound the workspace was sized for.
+template <typename Kernel>
+int filter_slices_for(Kernel kernel, const TileFilterParams &p, int bound) {
+  int S = resident_ctas(kernel) / p.C;
+  if (S > bound) S = bound;
+  const long long total = (long long)p.N * p.tiles_x * p.tiles_y;
+  if (S > total) S = (int)total;
+  return S < 1 ? 1 : S;
+}
+
 template <typename T, int K, int S, int TW>
-void launch_filter(const T *x, const T *dy, float *partial, TileFilterParams p, cudaStream_t st) {
+int launch_filter(const T *x, const T *dy, float *partial, TileFilterParams p, int bound, cudaStream_t st) {
   constexpr int TH = TileGeo<T, K, S, TW>::TH;
   p.tiles_x = ceil_div(p.Wo, TW);
   p.tiles_y = ceil_div(p.Ho, TH);
@@ -89,19 +147,21 @@ void launch_filter(const T *x, const T *dy, float *partial, TileFilterParams p, 
   if constexpr (fits) {
     if (rows_aligned16(x, p.W) && rows_aligned16(dy, p.Wo)) {
       p.off = stage_off<T>(p.pl);
+      p.SL = filter_slices_for(tile_filter_kernel<T, K, S, TW, V>, p, bound);
       tile_filter_kernel<T, K, S, TW, V><<<p.C * p.SL, TILE_THREADS, 0, st>>>(x, dy, partial, p);
-      return;
+      return p.SL;
     }
   }
+  p.SL = filter_slices_for(tile_filter_kernel<T, K, S, TW, 0>, p, bound);
   tile_filter_kernel<T, K, S, TW><<<p.C * p.SL, TILE_THREADS, 0, st>>>(x, dy, partial, p);
+  return p.SL;
 }
 
 template <typename T, int K, int S>
-void launch_filter_tw(const T *x, const T *dy, float *partial, const TileFilterParams &p, cudaStream_t st) {
-  if (pick_tw(p.Wo) == 32)
-    launch_filter<T, K, S, 32>(x, dy, partial, p, st);
-  else
-    launch_filter<T, K, S, 64>(x, dy, partial, p, st);
+int launch_filter_tw(const T *x, const T *dy, float *partial, const TileFilterParams &p, int bound,
+                     cudaStream_t st) {
+  if (pick_tw(p.Wo) == 32) return launch_filter<T, K, S, 32>(x, dy, partial, p, bound, st);
+  return launch_filter<T, K, S, 64>(x, dy, partial, p, bound, st);
 }
 
 }  // namespace
@@ -144,27 +204,38 @@ int tiles_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStr
   }
 }
 
-// First pass of the filter gradient with `slices` batch slices per channel (the caller sized
-// the workspace for them): partial[C][slices][K*K].
+int tiles_filter_slices(const Shape &s) {
+  if (!tiles_filter_ok(s) || !tiles_worth_it(s.Ho, s.Wo)) return 0;
+  const int TW = pick_tw(s.Wo), TH = TILE_THREADS / TW * TILE_R;
+  const long long total = (long long)s.N * ceil_div(s.Wo, TW) * ceil_div(s.Ho, TH);
+  long long S = 8 * 148 / s.C;  // no kernel of the family keeps more than 8 CTAs on an SM
+  if (S > total) S = total;
+  return S < 1 ? 1 : (int)S;
+}
+
+// First pass of the filter gradient: partial[C][*slices_used][K*K], *slices_used <= slices (the
+// bound the caller sized the workspace for, tiles_filter_slices).
 template <typename T>
 int tiles_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *partial, const Shape &s,
-                          int slices, cudaStream_t st) {
+                          int slices, cudaStream_t st, int *slices_used) {
   if constexpr (!TilesDtype<T>::ok) {
     return ROWS_DECLINED;
   } else {
-    if (!tiles_filter_ok(s) || !tiles_worth_it(s.Ho, s.Wo)) return ROWS_DECLINED;
+    if (!tiles_filter_ok(s) || !tiles_worth_it(s.Ho, s.Wo) || slices < 1) return ROWS_DECLINED;
     TileFilterParams p{};
     p.N = s.N; p.C = s.C; p.H = s.H; p.W = s.W; p.Ho = s.Ho; p.Wo = s.Wo;
-    p.pt = s.ph; p.pl = s.pw; p.SL = slices;
+    p.pt = s.ph; p.pl = s.pw;
+    int used = 0;
     switch (s.kh * 10 + s.sh) {
-      case 31: launch_filter_tw<T, 3, 1>(x, dy, partial, p, st); break;
-      case 51: launch_filter_tw<T, 5, 1>(x, dy, partial, p, st); break;
-      case 71: launch_filter_tw<T, 7, 1>(x, dy, partial, p, st); break;
-      case 32: launch_filter_tw<T, 3, 2>(x, dy, partial, p, st); break;
-      case 52: launch_filter_tw<T, 5, 2>(x, dy, partial, p, st); break;
-      case 72: launch_filter_tw<T, 7, 2>(x, dy, partial, p, st); break;
+      case 31: used = launch_filter_tw<T, 3, 1>(x, dy, partial, p, slices, st); break;
+      case 51: used = launch_filter_tw<T, 5, 1>(x, dy, partial, p, slices, st); break;
+      case 71: used = launch_filter_tw<T, 7, 1>(x, dy, partial, p, slices, st); break;
+      case 32: used = launch_filter_tw<T, 3, 2>(x, dy, partial, p, slices, st); break;
+      case 52: used = launch_filter_tw<T, 5, 2>(x, dy, partial, p, slices, st); break;
+      case 72: used = launch_filter_tw<T, 7, 2>(x, dy, partial, p, slices, st); break;
       default: return ROWS_DECLINED;
     }
+    *slices_used = used;
     return ROWS_SERVED;
   }
 }
@@ -174,7 +245,7 @@ int tiles_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *part
                                 cudaStream_t);                                                  \
   template int tiles_backward_input<T>(const T *, const T *, T *, const Shape &, cudaStream_t); \
   template int tiles_backward_filter<T>(const T *, const T *, typename Elem<T>::acc_t *,        \
-                                        const Shape &, int, cudaStream_t);
+                                        const Shape &, int, cudaStream_t, int *);
 DWB_TILES_INSTANTIATE(float)
 DWB_TILES_INSTANTIATE(__half)
 DWB_TILES_INSTANTIATE(__nv_bfloat16)

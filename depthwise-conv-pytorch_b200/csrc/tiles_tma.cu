@@ -1,0 +1,141 @@
+// Tiles family, tensor-copy staged kernels: tensor-map encoding and launches
+// (kernels: tile_tma_kernels.cuh).
+#include "tile_tma_kernels.cuh"
+
+#include <atomic>
+
+namespace dwb {
+
+namespace {
+
+__device__ int g_tiles_tma_error_flag;
+
+// cuTensorMapEncodeTiled, looked up in the driver at run time (the library does not link
+// libcuda).  Null when the driver has none: the callers then use the other staging forms.
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                 const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                 const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+  static std::atomic<int> state{0};  // 0 not asked yet, 1 found, 2 absent
+  static std::atomic<void *> fn{nullptr};
+  int s = state.load(std::memory_order_acquire);
+  if (s == 0) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess) (void)cudaGetLastError();
+    const bool ok = e == cudaSuccess && q == cudaDriverEntryPointSuccess && p != nullptr;
+    fn.store(ok ? p : nullptr, std::memory_order_relaxed);
+    s = ok ? 1 : 2;
+    state.store(s, std::memory_order_release);
+  }
+  return s == 1 ? reinterpret_cast<EncodeTiled>(fn.load(std::memory_order_relaxed)) : nullptr;
+}
+
+int *error_flag_ptr() {
+  static std::atomic<int *> cached{nullptr};
+  int *p = cached.load(std::memory_order_relaxed);
+  if (p == nullptr) {
+    if (cudaGetSymbolAddress((void **)&p, g_tiles_tma_error_flag) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    cached.store(p, std::memory_order_relaxed);
+  }
+  return p;
+}
+
+template <typename T> struct MapType;
+template <> struct MapType<float> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; };
+template <> struct MapType<__half> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; };
+template <> struct MapType<__nv_bfloat16> {
+  static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+};
+
+// The maps [planes][H][W] as a (W, H, planes) tensor read in boxes of (bw, bh, 1) elements;
+// what a box holds outside the tensor reads as zero.
+template <typename T>
+bool encode_planes(CUtensorMap *map, const T *base, int W, int H, int planes, int bw, int bh) {
+  EncodeTiled enc = encoder();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)planes};
+  const cuuint64_t strides[2] = {(cuuint64_t)W * sizeof(T), (cuuint64_t)W * H * sizeof(T)};
+  const cuuint32_t box[3] = {(cuuint32_t)bw, (cuuint32_t)bh, 1u};
+  const cuuint32_t elem[3] = {1u, 1u, 1u};
+  return enc(map, MapType<T>::v, 3, const_cast<T *>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int K, int TW>
+int launch(const T *in, const T *w, T *out, TileParams p, cudaStream_t st) {
+  using G = TileTmaGeo<T, K, TW>;
+  static_assert(2 * G::STAGE_BYTES + 64 <= 48 * 1024, "two stages must fit static shared memory");
+  static_assert(G::BW <= 256 && G::IH <= 256, "a box dimension is at most 256 elements");
+  int *flag = error_flag_ptr();
+  if (flag == nullptr) return ROWS_DECLINED;
+  p.off = ((-p.pl) % G::V + G::V) % G::V;
+  if ((p.pl + p.off) % G::V != 0) return ROWS_DECLINED;  // the box must start on a 16-byte boundary
+  alignas(64) CUtensorMap map;
+  if (!encode_planes<T>(&map, in, p.Win, p.Hin, p.NC, G::BW, G::IH)) return ROWS_DECLINED;
+  p.tiles_x = ceil_div(p.Wout, TW);
+  p.tiles_y = ceil_div(p.Hout, G::TH);
+  p.ntiles = (long long)p.NC * p.tiles_x * p.tiles_y;
+  const int per_plane = p.tiles_x * p.tiles_y;
+  // as many CTAs as the device holds at once (the kernel's launch bounds); each walks its share
+  // of the planes, its two stages overlapping copy and arithmetic
+  const int cap = 148 * (K == 3 ? 6 : (K == 5 ? 4 : 3));
+  int gy = cap / per_plane;
+  if (gy < 1) gy = 1;
+  if (gy > p.NC) gy = p.NC;
+  tile_tma_conv_kernel<T, K, TW><<<dim3(per_plane, gy), TILE_THREADS, 0, st>>>(map, w, out, p, flag);
+  return ROWS_SERVED;
+}
+
+template <typename T, int K>
+int launch_tw(const T *in, const T *w, T *out, const TileParams &p, int tw, cudaStream_t st) {
+  return tw == 32 ? launch<T, K, 32>(in, w, out, p, st) : launch<T, K, 64>(in, w, out, p, st);
+}
+
+}  // namespace
+
+// Stride-1 correlation of `in` (rows on 16-byte boundaries) staged by tensor copies; `tw` is
+// the tile width the caller chose (32 or 64).  ROWS_DECLINED when this form cannot run (no
+// encoder in the driver, a geometry outside what a box can describe).
+template <typename T>
+int tiles_tma_conv(const T *in, const T *w, T *out, const TileParams &p, int K, int tw, cudaStream_t st) {
+  constexpr int V = 16 / (int)sizeof(T);
+  if (p.Win % V != 0 || (reinterpret_cast<uintptr_t>(in) & 15) != 0) return ROWS_DECLINED;
+  if (p.NC > (1 << 30) || (long long)p.Win * p.Hin * (long long)sizeof(T) >= (1ll << 40)) return ROWS_DECLINED;
+  switch (K) {
+    case 3: return launch_tw<T, 3>(in, w, out, p, tw, st);
+    case 5: return launch_tw<T, 5>(in, w, out, p, tw, st);
+    case 7: return launch_tw<T, 7>(in, w, out, p, tw, st);
+    default: return ROWS_DECLINED;
+  }
+}
+
+template int tiles_tma_conv<float>(const float *, const float *, float *, const TileParams &, int, int,
+                                   cudaStream_t);
+template int tiles_tma_conv<__half>(const __half *, const __half *, __half *, const TileParams &, int, int,
+                                    cudaStream_t);
+template int tiles_tma_conv<__nv_bfloat16>(const __nv_bfloat16 *, const __nv_bfloat16 *, __nv_bfloat16 *,
+                                           const TileParams &, int, int, cudaStream_t);
+
+// Reads and clears this translation unit's error flag (bit 0: a bounded wait expired).
+int tiles_tma_take_error() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tiles_tma_error_flag, sizeof(int)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  if (v != 0) {
+    const int zero = 0;
+    (void)cudaMemcpyToSymbol(g_tiles_tma_error_flag, &zero, sizeof(int));
+  }
+  return v;
+}
+
+}  // namespace dwb
