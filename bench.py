@@ -66,6 +66,13 @@ WORKLOADS = {
     "c5k7": [(32, 256, 32, 7, 1, 3, "f32")],
     "c5k13": [(32, 256, 32, 13, 1, 6, "f32")],
     "c5k31": [(32, 256, 32, 31, 1, 15, "f32")],
+    # maps wider than the 128 columns the row-staged kernels take, and a layer without padding:
+    # the tile kernels' ground (not BASELINE configurations; the shapes of the reference's own tests
+    # and of a 224x224 stem)
+    "t224": [(32, 32, 224, 3, 1, 1, "f32")],
+    "t224s2": [(32, 32, 224, 3, 2, 1, "f32")],
+    "t224k5h": [(32, 32, 224, 5, 1, 2, "f16")],
+    "t64p0": [(32, 32, 64, 3, 1, 0, "f32")],
 }
 DESCR = {
     "c1": "single depthwise conv N8 C32 56x56 k3 s1 p1 fp32",

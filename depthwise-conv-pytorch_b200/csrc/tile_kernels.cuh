@@ -30,6 +30,8 @@
 // flipped filter; the inserted zeros add nothing, so the sum is the same as the polyphase form's.
 #pragma once
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace dwb {
@@ -361,6 +363,36 @@ tile_filter_kernel(const T *__restrict__ x, const T *__restrict__ dy, float *__r
     for (int q = 0; q < TILE_THREADS / 32; ++q) s += red[q][threadIdx.x];
     partial[((size_t)c * p.SL + slice) * KK + threadIdx.x] = s;
   }
+}
+
+// Resident CTAs of a kernel on the whole device (asked once per instantiation).
+template <typename Kernel> inline int resident_ctas(Kernel kernel) {
+  static std::atomic<int> cached{0};
+  int v = cached.load(std::memory_order_relaxed);
+  if (v == 0) {
+    int per_sm = 0, dev = 0, sms = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, TILE_THREADS, 0) != cudaSuccess ||
+        cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return 148;
+    }
+    v = per_sm * sms;
+    if (v < 1) v = 1;
+    cached.store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+// Slices per channel: as many as give every CTA a place on the device at once (one wave of
+// CTAs with equal tile counts), within the bound the workspace was sized for.
+template <typename Kernel>
+inline int filter_slices_for(Kernel kernel, const TileFilterParams &p, int bound) {
+  int S = resident_ctas(kernel) / p.C;
+  if (S > bound) S = bound;
+  const long long total = (long long)p.N * p.tiles_x * p.tiles_y;
+  if (S > total) S = (int)total;
+  return S < 1 ? 1 : S;
 }
 
 }  // namespace dwb

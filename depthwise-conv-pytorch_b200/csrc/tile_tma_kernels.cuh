@@ -167,4 +167,119 @@ tile_tma_conv_kernel(const __grid_constant__ CUtensorMap in_map, const T *__rest
   }
 }
 
+// Filter gradient, first pass, stride 1: as tile_filter_kernel (block (c, slice) walks one of SL
+// equal ranges of channel c's tiles, a thread owns a dy column and a strip of dy rows and keeps
+// K*K sums), with the x tile (halo included) and the dy tile of every step brought in by one
+// tensor copy each, two steps in flight.  Only thread 0 knows where a tile lies; the arithmetic
+// is relative to the boxes.  What a box holds outside its tensor reads as zero: the padding of
+// x, and dy elements beyond the map's edge (they add nothing).
+template <typename T, int K, int TW>
+__global__ void __launch_bounds__(TILE_THREADS, K == 3 ? 4 : (K == 5 ? 3 : 2))
+tile_tma_filter_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap dy_map,
+                       float *__restrict__ partial, const TileFilterParams p, int *error_flag) {
+  using G = TileTmaGeo<T, K, TW>;
+  constexpr int KK = K * K;
+  constexpr int DY_BYTES = G::TH * TW * (int)sizeof(T);
+  constexpr int X_BYTES = G::STAGE_BYTES;  // the x box, rounded up to 128 bytes
+  constexpr int STEP_BYTES = X_BYTES + (DY_BYTES + 127) / 128 * 128;
+  __shared__ __align__(128) unsigned char stages[2][STEP_BYTES];
+  __shared__ uint64_t full[2];
+  __shared__ float red[TILE_THREADS / 32][KK];
+  pdl_launch_dependents();  // the second pass may take its place on the SMs early
+  const int c = blockIdx.x / p.SL;
+  const int slice = blockIdx.x - c * p.SL;
+  const int per_img = p.tiles_x * p.tiles_y;
+  const long long total = (long long)p.N * per_img;
+  const long long t0 = slice * total / p.SL, t1 = (slice + 1) * total / p.SL;
+  const int steps = (int)(t1 - t0);
+  const int tc = threadIdx.x % TW, tr = threadIdx.x / TW;
+  if (threadIdx.x == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  // thread 0: the next tile to ask for, and the copies asked for / seen complete per stage
+  int n = (int)(t0 / per_img);
+  int ty = (int)(t0 - (long long)n * per_img) / p.tiles_x;
+  int tx = (int)(t0 - (long long)n * per_img) - ty * p.tiles_x;
+  int asked = 0, landed0 = 0, landed1 = 0;
+  auto ask = [&](int s) {
+    const int plane = n * p.C + c;
+    const int y0 = ty * G::TH, x0 = tx * TW;
+    mbar_arrive_expect_tx(&full[s], G::BOX_BYTES + DY_BYTES);
+    tma_load_3d(stages[s], &x_map, x0 - p.pl - p.off, y0 - p.pt, plane, &full[s]);
+    tma_load_3d(stages[s] + X_BYTES, &dy_map, x0, y0, plane, &full[s]);
+    ++asked;
+    if (++tx == p.tiles_x) {
+      tx = 0;
+      if (++ty == p.tiles_y) { ty = 0; ++n; }
+    }
+  };
+  if (threadIdx.x == 0) {
+    if (steps > 0) ask(0);
+    if (steps > 1) ask(1);
+  }
+  float acc[K][K];
+#pragma unroll
+  for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+    for (int kx = 0; kx < K; ++kx) acc[ky][kx] = 0.f;
+  bool gave_up = false;
+  for (int it = 0; it < steps; ++it) {
+    const int s = it & 1;
+    if (!gave_up) {
+      if (mbar_wait_bounded(&full[s], (it >> 1) & 1)) {
+        landed0 += 1 - s;
+        landed1 += s;
+      } else {
+        gave_up = true;
+        atomicOr(error_flag, 2);
+      }
+    }
+    const unsigned char *xs = stages[s];
+    const unsigned char *gs = stages[s] + X_BYTES;
+    float g[TILE_R];
+#pragma unroll
+    for (int o = 0; o < TILE_R; ++o) g[o] = smem_elem<T>(gs, (tr * TILE_R + o) * TW + tc);
+    const int first = (tr * TILE_R) * G::BW + p.off + tc;
+#pragma unroll
+    for (int ir = 0; ir < G::IR; ++ir) {
+      float v[K];
+#pragma unroll
+      for (int kx = 0; kx < K; ++kx) v[kx] = smem_elem<T>(xs, first + ir * G::BW + kx);
+#pragma unroll
+      for (int o = 0; o < TILE_R; ++o) {
+        const int ky = ir - o;
+        if (ky >= 0 && ky < K) {
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) acc[ky][kx] = fmaf(g[o], v[kx], acc[ky][kx]);
+        }
+      }
+    }
+    __syncthreads();  // every thread has read stage s: it may be refilled
+    if (threadIdx.x == 0 && !gave_up && asked < steps) ask(s);
+  }
+  if (threadIdx.x == 0 && gave_up) {
+    const int asked0 = (asked + 1) / 2, asked1 = asked / 2;
+    while (landed0 < asked0 && mbar_wait_bounded(&full[0], landed0 & 1)) ++landed0;
+    while (landed1 < asked1 && mbar_wait_bounded(&full[1], landed1 & 1)) ++landed1;
+  }
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+  for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+    for (int kx = 0; kx < K; ++kx) {
+      const float v = warp_sum(acc[ky][kx]);
+      if (lane == 0) red[wid][ky * K + kx] = v;
+    }
+  __syncthreads();
+  if (threadIdx.x < KK) {
+    float sum = 0.f;
+#pragma unroll
+    for (int q = 0; q < TILE_THREADS / 32; ++q) sum += red[q][threadIdx.x];
+    partial[((size_t)c * p.SL + slice) * KK + threadIdx.x] = sum;
+  }
+}
+
 }  // namespace dwb

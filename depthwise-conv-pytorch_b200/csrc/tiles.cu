@@ -10,6 +10,9 @@ namespace dwb {
 // tiles_tma.cu: the stride-1 kernels whose input tile arrives by one tensor copy.
 template <typename T>
 int tiles_tma_conv(const T *in, const T *w, T *out, const TileParams &p, int K, int tw, cudaStream_t st);
+template <typename T>
+int tiles_tma_filter(const T *x, const T *dy, float *partial, const TileFilterParams &p, int K, int tw,
+                     int bound, cudaStream_t st, int *slices_used);
 
 namespace {
 
@@ -104,36 +107,6 @@ int conv_dispatch(const T *in, const T *w, T *out, const TileParams &p, int K, i
   }
 }
 
-// Resident CTAs of a kernel on the whole device (asked once per instantiation).
-template <typename Kernel> int resident_ctas(Kernel kernel) {
-  static std::atomic<int> cached{0};
-  int v = cached.load(std::memory_order_relaxed);
-  if (v == 0) {
-    int per_sm = 0, dev = 0, sms = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, TILE_THREADS, 0) != cudaSuccess ||
-        cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return 148;
-    }
-    v = per_sm * sms;
-    if (v < 1) v = 1;
-    cached.store(v, std::memory_order_relaxed);
-  }
-  return v;
-}
-
-// Slices per channel: as many as give every CTA a place on the device at once (one wave of
-// CTAs with equal tile counts), within the bound the workspace was sized for.
-template <typename Kernel>
-int filter_slices_for(Kernel kernel, const TileFilterParams &p, int bound) {
-  int S = resident_ctas(kernel) / p.C;
-  if (S > bound) S = bound;
-  const long long total = (long long)p.N * p.tiles_x * p.tiles_y;
-  if (S > total) S = (int)total;
-  return S < 1 ? 1 : S;
-}
-
 template <typename T, int K, int S, int TW>
 int launch_filter(const T *x, const T *dy, float *partial, TileFilterParams p, int bound, cudaStream_t st) {
   constexpr int TH = TileGeo<T, K, S, TW>::TH;
@@ -144,6 +117,12 @@ int launch_filter(const T *x, const T *dy, float *partial, TileFilterParams p, i
   // the wider staged rows of the 16-byte form must still fit the static shared memory of a CTA
   constexpr bool fits =
       (GV::IH * GV::PITCH + GV::TH * TW + TILE_THREADS / 32 * K * K) * sizeof(float) <= 48 * 1024;
+  if constexpr (S == 1) {
+    if (rows_aligned16(x, p.W) && rows_aligned16(dy, p.Wo) && !tiles_tma_off()) {
+      int used = 0;
+      if (tiles_tma_filter<T>(x, dy, partial, p, K, TW, bound, st, &used) == ROWS_SERVED) return used;
+    }
+  }
   if constexpr (fits) {
     if (rows_aligned16(x, p.W) && rows_aligned16(dy, p.Wo)) {
       p.off = stage_off<T>(p.pl);

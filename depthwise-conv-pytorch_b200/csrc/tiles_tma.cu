@@ -99,7 +99,56 @@ int launch_tw(const T *in, const T *w, T *out, const TileParams &p, int tw, cuda
   return tw == 32 ? launch<T, K, 32>(in, w, out, p, st) : launch<T, K, 64>(in, w, out, p, st);
 }
 
+template <typename T, int K, int TW>
+int launch_filter(const T *x, const T *dy, float *partial, TileFilterParams p, int bound, cudaStream_t st,
+                  int *used) {
+  using G = TileTmaGeo<T, K, TW>;
+  int *flag = error_flag_ptr();
+  if (flag == nullptr) return ROWS_DECLINED;
+  p.off = ((-p.pl) % G::V + G::V) % G::V;
+  if ((p.pl + p.off) % G::V != 0) return ROWS_DECLINED;
+  alignas(64) CUtensorMap x_map, dy_map;
+  if (!encode_planes<T>(&x_map, x, p.W, p.H, p.N * p.C, G::BW, G::IH)) return ROWS_DECLINED;
+  if (!encode_planes<T>(&dy_map, dy, p.Wo, p.Ho, p.N * p.C, TW, G::TH)) return ROWS_DECLINED;
+  p.tiles_x = ceil_div(p.Wo, TW);
+  p.tiles_y = ceil_div(p.Ho, G::TH);
+  p.SL = filter_slices_for(tile_tma_filter_kernel<T, K, TW>, p, bound);
+  tile_tma_filter_kernel<T, K, TW><<<p.C * p.SL, TILE_THREADS, 0, st>>>(x_map, dy_map, partial, p, flag);
+  *used = p.SL;
+  return ROWS_SERVED;
+}
+
 }  // namespace
+
+// First pass of the stride-1 filter gradient staged by tensor copies (x and dy rows on 16-byte
+// boundaries); `bound` is the slice count the workspace was sized for, *slices_used what was
+// launched.
+template <typename T>
+int tiles_tma_filter(const T *x, const T *dy, float *partial, const TileFilterParams &p, int K, int tw,
+                     int bound, cudaStream_t st, int *slices_used) {
+  constexpr int V = 16 / (int)sizeof(T);
+  if (p.W % V != 0 || p.Wo % V != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(dy) & 15) != 0)
+    return ROWS_DECLINED;
+  if ((long long)p.N * p.C > (1 << 30) || (long long)p.W * p.H * (long long)sizeof(T) >= (1ll << 40))
+    return ROWS_DECLINED;
+  switch (K * 100 + tw) {
+    case 332: return launch_filter<T, 3, 32>(x, dy, partial, p, bound, st, slices_used);
+    case 364: return launch_filter<T, 3, 64>(x, dy, partial, p, bound, st, slices_used);
+    case 532: return launch_filter<T, 5, 32>(x, dy, partial, p, bound, st, slices_used);
+    case 564: return launch_filter<T, 5, 64>(x, dy, partial, p, bound, st, slices_used);
+    case 732: return launch_filter<T, 7, 32>(x, dy, partial, p, bound, st, slices_used);
+    case 764: return launch_filter<T, 7, 64>(x, dy, partial, p, bound, st, slices_used);
+    default: return ROWS_DECLINED;
+  }
+}
+
+template int tiles_tma_filter<float>(const float *, const float *, float *, const TileFilterParams &, int,
+                                     int, int, cudaStream_t, int *);
+template int tiles_tma_filter<__half>(const __half *, const __half *, float *, const TileFilterParams &,
+                                      int, int, int, cudaStream_t, int *);
+template int tiles_tma_filter<__nv_bfloat16>(const __nv_bfloat16 *, const __nv_bfloat16 *, float *,
+                                             const TileFilterParams &, int, int, int, cudaStream_t, int *);
 
 // Stride-1 correlation of `in` (rows on 16-byte boundaries) staged by tensor copies; `tw` is
 // the tile width the caller chose (32 or 64).  ROWS_DECLINED when this form cannot run (no
