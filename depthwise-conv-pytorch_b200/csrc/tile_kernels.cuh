@@ -24,10 +24,9 @@
 // bit-identical to it and to the other families.  No bulk copies, no pipeline: latency is
 // hidden by several resident CTAs per SM.
 //
-// Backward-input at stride 2 is the reference's own formulation (torch_dwconv/dwconv.py:57-64,
-// dwconv_kernel.cu:107-114): dy is staged with a zero between neighbouring elements (up-sampling
-// by the stride happens while copying into shared memory) and correlated at stride 1 with the
-// flipped filter; the inserted zeros add nothing, so the sum is the same as the polyphase form's.
+// Backward-input at stride 2 has a kernel of its own (tile_bwd2_kernel below): the reference's
+// formulation (dy up-sampled with zeros, correlated at stride 1 with the flipped filter,
+// torch_dwconv/dwconv.py:57-64) with the products by the inserted zeros left out.
 #pragma once
 
 #include <atomic>
@@ -139,10 +138,9 @@ __device__ __forceinline__ void tile_stage_vec(float *sm, const T *__restrict__ 
   }
 }
 
-// Copies the input tile whose first element is (gy0, gx0) of `plane` into shared memory.
-// UP > 1: (gy, gx) address the map up-sampled by UP with zeros in between ((Hin-1)*UP+1 rows);
-// only coordinates that are multiples of UP hold data.
-template <typename T, int S, int IH, int IW, int HALF, int PITCH, int UP = 1>
+// Copies the input tile whose first element is (gy0, gx0) of `plane` into shared memory,
+// element by element with a bounds test each (any alignment).
+template <typename T, int S, int IH, int IW, int HALF, int PITCH>
 __device__ __forceinline__ void tile_stage(float *sm, const T *__restrict__ plane, int Hin, int Win,
                                            int gy0, int gx0) {
   constexpr int TOTAL = IH * IW;
@@ -162,14 +160,8 @@ __device__ __forceinline__ void tile_stage(float *sm, const T *__restrict__ plan
       ix += DX; iy += DY;
       if (ix >= IW) { ix -= IW; ++iy; }
       v[u] = 0.f;
-      if (UP == 1) {
-        if (idx < TOTAL && (unsigned)gy < (unsigned)Hin && (unsigned)gx < (unsigned)Win)
-          v[u] = Elem<T>::ld(plane + (size_t)gy * Win + gx);
-      } else {
-        const int sy = gy / UP, sx = gx / UP;  // gy, gx >= 0 is checked below
-        if (idx < TOTAL && gy >= 0 && gx >= 0 && sy * UP == gy && sx * UP == gx && sy < Hin && sx < Win)
-          v[u] = Elem<T>::ld(plane + (size_t)sy * Win + sx);
-      }
+      if (idx < TOTAL && (unsigned)gy < (unsigned)Hin && (unsigned)gx < (unsigned)Win)
+        v[u] = Elem<T>::ld(plane + (size_t)gy * Win + gx);
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)
@@ -177,15 +169,13 @@ __device__ __forceinline__ void tile_stage(float *sm, const T *__restrict__ plan
   }
 }
 
-// out[oy][ox] = sum over (ky, kx) of in[oy*S - pt + ky][ox*S - pl + kx] * tap[ky][kx], `in` being
-// the map up-sampled by UP.
-template <typename T, int K, int S, int TW, int UP = 1, int VEC = 0>
+// out[oy][ox] = sum over (ky, kx) of in[oy*S - pt + ky][ox*S - pl + kx] * tap[ky][kx].
+template <typename T, int K, int S, int TW, int VEC = 0>
 __global__ void __launch_bounds__(TILE_THREADS)
 tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restrict__ out,
                  const TileParams p) {
   using G = TileGeo<T, K, S, TW, VEC>;
   constexpr int KK = K * K;
-  static_assert(VEC == 0 || UP == 1, "the up-sampled gradient is staged element by element");
   __shared__ __align__(16) float sm[G::IH * G::PITCH];
   // position, inside a staged row, of the K columns under this thread's output column
   int cpos[K];
@@ -209,7 +199,7 @@ tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restric
                                                              p.Win, y0 * S - p.pt,
                                                              x0 * S - p.pl - p.off);
     else
-      tile_stage<T, S, G::IH, G::IW, G::HALF, G::PITCH, UP>(sm, in + (size_t)plane * plane_in, p.Hin,
+      tile_stage<T, S, G::IH, G::IW, G::HALF, G::PITCH>(sm, in + (size_t)plane * plane_in, p.Hin,
                                                             p.Win, y0 * S - p.pt, x0 * S - p.pl);
     float tap[K][K];
     {
@@ -252,6 +242,113 @@ tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restric
 #pragma unroll
       for (int o = 0; o < TILE_R; ++o) {
         if (o < rows) *op = Elem<T>::from_acc(acc[o]);
+        op += p.Wout;
+      }
+    }
+    chan += chan_step;
+    if (chan >= p.C) chan -= p.C;
+  }
+}
+
+// Backward-input at stride 2, polyphase.  The transposed operation is the stride-1 correlation of
+// dy, up-sampled by 2 with zeros in between, with the flipped filter (torch_dwconv/dwconv.py:57-64,
+// dwconv_kernel.cu:107-114): out[oy][ox] = sum over (ky, kx) of U[oy - pt + ky][ox - pl + kx] *
+// wf[ky][kx], U[2a][2b] = dy[a][b] and zero elsewhere.  Three quarters of those products are with
+// the inserted zeros; this kernel stages dy as it is (dense) and issues only the others, in the
+// same ky-major / kx-minor order, so the sums keep their bits.  For an output column only the kx
+// of one parity meet data: a thread picks its ceil(K/2) taps per filter row once per plane
+// (`tsel`); for an output row only the ky of one parity do, and which is a compile-time fact once
+// the parity of pt is a template argument.  Staged row d of a strip is dy row
+// floor((ys - pt) / 2) + d (ys = the strip's first output row, even), and then ky = 2d - P - o for
+// output row ys + o (P = pt & 1); columns likewise with pl.
+template <int K, int TW, int VEC>
+struct Bwd2Geo {
+  static constexpr int TH = TILE_THREADS / TW * TILE_R;       // output rows per tile
+  static constexpr int KH = (K + 1) / 2;                      // taps of one parity per filter row
+  static constexpr int ND = (K + TILE_R - 1) / 2 + 1;         // dy rows under one strip
+  static constexpr int IH = (TH / TILE_R - 1) * (TILE_R / 2) + ND;  // dy rows per tile
+  static constexpr int IW = TW / 2 + KH;                      // dy columns per tile
+  static constexpr int NCH = VEC ? (IW + 2 * VEC - 2) / VEC : 0;
+  static constexpr int PITCH = VEC ? NCH * VEC : IW;
+};
+
+template <typename T, int K, int TW, int VEC, bool PODD>
+__device__ __forceinline__ void bwd2_strip(const float *__restrict__ rows, int pitch, int col0,
+                                           const float (&tsel)[K][(K + 1) / 2], float (&acc)[TILE_R]) {
+  constexpr int KH = (K + 1) / 2;
+  constexpr int ND = Bwd2Geo<K, TW, VEC>::ND;
+  constexpr int P = PODD ? 1 : 0;
+#pragma unroll
+  for (int d = 0; d < ND; ++d) {
+    float v[KH];
+#pragma unroll
+    for (int j = 0; j < KH; ++j) v[j] = rows[d * pitch + col0 + j];
+#pragma unroll
+    for (int o = 0; o < TILE_R; ++o) {
+      const int ky = 2 * d - P - o;
+      if (ky >= 0 && ky < K) {
+#pragma unroll
+        for (int j = 0; j < KH; ++j) acc[o] = fmaf(v[j], tsel[ky][j], acc[o]);
+      }
+    }
+  }
+}
+
+// p: Hin x Win = dy, Hout x Wout = dx, pt / pl = k-1-padding, off as in TileParams for the dense
+// dy tile (its first column is floor((x0 - pl) / 2)).
+template <typename T, int K, int TW, int VEC = 0>
+__global__ void __launch_bounds__(TILE_THREADS)
+tile_bwd2_kernel(const T *__restrict__ dy, const T *__restrict__ w, T *__restrict__ out,
+                 const TileParams p) {
+  using G = Bwd2Geo<K, TW, VEC>;
+  constexpr int KK = K * K;
+  __shared__ __align__(16) float sm[G::IH * G::PITCH];
+  const int tc = threadIdx.x % TW, tr = threadIdx.x / TW;
+  const int ty = (int)blockIdx.x / p.tiles_x, tx = (int)blockIdx.x - ty * p.tiles_x;
+  const int y0 = ty * G::TH, x0 = tx * TW;  // first output of the tile (both even)
+  const int px = p.pl & 1;
+  const int qx = (px + tc) & 1;             // parity of the kx that meet data under this column
+  const int col0 = (VEC ? p.off : 0) + ((tc + qx + px) >> 1);
+  // floor((y0 - pt) / 2), floor((x0 - pl) / 2): first dy row / column of the tile
+  const int gy0 = (y0 - p.pt - (p.pt & 1)) / 2, gx0 = (x0 - p.pl - px) / 2;
+  const size_t plane_in = (size_t)p.Hin * p.Win, plane_out = (size_t)p.Hout * p.Wout;
+  int chan = (int)blockIdx.y % p.C;
+  const int chan_step = (int)gridDim.y % p.C;
+  for (int plane = blockIdx.y; plane < p.NC; plane += gridDim.y) {
+    __syncthreads();  // the previous tile's readers are done
+    if constexpr (VEC != 0)
+      tile_stage_vec<T, 1, G::IH, G::NCH, 0, G::PITCH>(sm, dy + (size_t)plane * plane_in, p.Hin, p.Win,
+                                                       gy0, gx0 - p.off);
+    else
+      tile_stage<T, 1, G::IH, G::IW, 0, G::PITCH>(sm, dy + (size_t)plane * plane_in, p.Hin, p.Win, gy0,
+                                                  gx0);
+    float tsel[K][G::KH];
+    {
+      const T *tp = w + (size_t)chan * KK;
+#pragma unroll
+      for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+        for (int j = 0; j < G::KH; ++j) {
+          const int kx = qx + 2 * j;  // flipped filter: wf[ky][kx] = w[K-1-ky][K-1-kx]
+          tsel[ky][j] = kx < K ? Elem<T>::ld(tp + (K - 1 - ky) * K + (K - 1 - kx)) : 0.f;
+        }
+    }
+    __syncthreads();
+    float acc[TILE_R];
+#pragma unroll
+    for (int o = 0; o < TILE_R; ++o) acc[o] = 0.f;
+    const float *rows = sm + (tr * (TILE_R / 2)) * G::PITCH;
+    if (p.pt & 1)
+      bwd2_strip<T, K, TW, VEC, true>(rows, G::PITCH, col0, tsel, acc);
+    else
+      bwd2_strip<T, K, TW, VEC, false>(rows, G::PITCH, col0, tsel, acc);
+    const int ox = x0 + tc;
+    if (ox < p.Wout) {
+      T *op = out + (size_t)plane * plane_out + (size_t)(y0 + tr * TILE_R) * p.Wout + ox;
+      const int nrows = p.Hout - (y0 + tr * TILE_R);
+#pragma unroll
+      for (int o = 0; o < TILE_R; ++o) {
+        if (o < nrows) *op = Elem<T>::from_acc(acc[o]);
         op += p.Wout;
       }
     }

@@ -56,7 +56,7 @@ template <typename T> inline int stage_off(int pl) {
   return ((-pl) % V + V) % V;
 }
 
-template <typename T, int K, int S, int TW, int UP = 1>
+template <typename T, int K, int S, int TW>
 void launch_conv(const T *in, const T *w, T *out, TileParams p, cudaStream_t st) {
   constexpr int TH = TileGeo<T, K, S, TW>::TH;
   constexpr int V = 16 / (int)sizeof(T);
@@ -71,7 +71,7 @@ void launch_conv(const T *in, const T *w, T *out, TileParams p, cudaStream_t st)
   if (gy < 1) gy = 1;
   if (gy > p.NC) gy = p.NC;
   const dim3 grid(per_plane, gy);
-  if constexpr (UP == 1) {
+  {
     if (rows_aligned16(in, p.Win)) {
       // stride 1: one tensor copy per tile; else (or if the driver offers no encoder) 16-byte
       // loads and stores through registers
@@ -79,19 +79,51 @@ void launch_conv(const T *in, const T *w, T *out, TileParams p, cudaStream_t st)
         if (!tiles_tma_off() && tiles_tma_conv<T>(in, w, out, p, K, TW, st) == ROWS_SERVED) return;
       }
       p.off = stage_off<T>(p.pl);
-      tile_conv_kernel<T, K, S, TW, 1, V><<<grid, TILE_THREADS, 0, st>>>(in, w, out, p);
+      tile_conv_kernel<T, K, S, TW, V><<<grid, TILE_THREADS, 0, st>>>(in, w, out, p);
       return;
     }
   }
-  tile_conv_kernel<T, K, S, TW, UP><<<grid, TILE_THREADS, 0, st>>>(in, w, out, p);
+  tile_conv_kernel<T, K, S, TW><<<grid, TILE_THREADS, 0, st>>>(in, w, out, p);
 }
 
-template <typename T, int K, int S, int UP = 1>
+template <typename T, int K, int S>
 void launch_conv_tw(const T *in, const T *w, T *out, const TileParams &p, cudaStream_t st) {
   if (pick_tw(p.Wout) == 32)
-    launch_conv<T, K, S, 32, UP>(in, w, out, p, st);
+    launch_conv<T, K, S, 32>(in, w, out, p, st);
   else
-    launch_conv<T, K, S, 64, UP>(in, w, out, p, st);
+    launch_conv<T, K, S, 64>(in, w, out, p, st);
+}
+
+// Stride-2 backward-input (polyphase kernel): p describes dy -> dx with pt / pl = k-1-padding.
+template <typename T, int K, int TW>
+void launch_bwd2(const T *dy, const T *w, T *dx, TileParams p, cudaStream_t st) {
+  constexpr int V = 16 / (int)sizeof(T);
+  constexpr int TH = Bwd2Geo<K, TW, 0>::TH;
+  p.tiles_x = ceil_div(p.Wout, TW);
+  p.tiles_y = ceil_div(p.Hout, TH);
+  p.ntiles = (long long)p.NC * p.tiles_x * p.tiles_y;
+  const int per_plane = p.tiles_x * p.tiles_y;
+  const int cap = 148 * 16;
+  int gy = cap / per_plane;
+  if (gy < 1) gy = 1;
+  if (gy > p.NC) gy = p.NC;
+  const dim3 grid(per_plane, gy);
+  if (rows_aligned16(dy, p.Win)) {
+    // the dense dy tile starts at column floor((x0 - pl) / 2); x0 / 2 is a multiple of the chunk
+    const int first = -((p.pl + (p.pl & 1)) / 2);
+    p.off = (first % V + V) % V;
+    tile_bwd2_kernel<T, K, TW, V><<<grid, TILE_THREADS, 0, st>>>(dy, w, dx, p);
+    return;
+  }
+  tile_bwd2_kernel<T, K, TW, 0><<<grid, TILE_THREADS, 0, st>>>(dy, w, dx, p);
+}
+
+template <typename T, int K>
+void launch_bwd2_tw(const T *dy, const T *w, T *dx, const TileParams &p, cudaStream_t st) {
+  if (pick_tw(p.Wout) == 32)
+    launch_bwd2<T, K, 32>(dy, w, dx, p, st);
+  else
+    launch_bwd2<T, K, 64>(dy, w, dx, p, st);
 }
 
 template <typename T>
@@ -175,9 +207,9 @@ int tiles_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStr
     p.pt = s.kh - 1 - s.ph; p.pl = s.kw - 1 - s.pw; p.flip = 1;
     if (s.sh == 1) return conv_dispatch<T>(dy, w, dx, p, s.kh, 1, st);
     switch (s.kh) {
-      case 3: launch_conv_tw<T, 3, 1, 2>(dy, w, dx, p, st); return ROWS_SERVED;
-      case 5: launch_conv_tw<T, 5, 1, 2>(dy, w, dx, p, st); return ROWS_SERVED;
-      case 7: launch_conv_tw<T, 7, 1, 2>(dy, w, dx, p, st); return ROWS_SERVED;
+      case 3: launch_bwd2_tw<T, 3>(dy, w, dx, p, st); return ROWS_SERVED;
+      case 5: launch_bwd2_tw<T, 5>(dy, w, dx, p, st); return ROWS_SERVED;
+      case 7: launch_bwd2_tw<T, 7>(dy, w, dx, p, st); return ROWS_SERVED;
       default: return ROWS_DECLINED;
     }
   }
