@@ -4,6 +4,13 @@
 
 namespace dwb {
 
+// nhwc_tma.cu: the same operators with their tiles brought in by tensor copies.
+template <typename T>
+int nhwc_tma_conv(const T *in, const T *w, T *out, const NhwcParams &p, int K, int S, cudaStream_t st);
+template <typename T>
+int nhwc_tma_filter(const T *x, const T *dy, float *partial, const NhwcFilterParams &p, int K, int S,
+                    cudaStream_t st);
+
 namespace {
 
 template <typename T> struct NhwcDtype { static constexpr bool ok = false; };
@@ -40,12 +47,15 @@ void launch_filter(const T *x, const T *dy, float *partial, NhwcFilterParams p, 
 }  // namespace
 
 // Slices of the (image, tile) list per block of 32 channels: about four CTAs per SM in all,
-// never more slices than images (a slice is at least one image's worth of tiles on average).
+// never more slices than tiles.
 int nhwc_filter_slices(const Shape &s) {
+  if (!nhwc_filter_ok(s)) return 1;
   const int cblocks = ceil_div(s.C, NHWC_CB);
-  int SL = ceil_div(4 * 148, cblocks);
-  if (SL > s.N) SL = s.N;
-  return SL < 1 ? 1 : SL;
+  const int R = nhwc_rows(s.kh, s.sh, true), TW = s.sh == 1 ? 16 : 8;
+  const long long total = (long long)s.N * ceil_div(s.Ho, R) * ceil_div(s.Wo, TW);
+  long long SL = ceil_div(4 * 148, cblocks);
+  if (SL > total) SL = total;
+  return SL < 1 ? 1 : (int)SL;
 }
 
 template <typename T>
@@ -57,6 +67,7 @@ int nhwc_forward(const T *x, const T *w, T *y, const Shape &s, const EpilogueArg
     NhwcParams p{};
     p.N = s.N; p.C = s.C; p.Hin = s.H; p.Win = s.W; p.Hout = s.Ho; p.Wout = s.Wo;
     p.pt = s.ph; p.pl = s.pw; p.flip = 0; p.ep = ep;
+    if (nhwc_tma_conv<T>(x, w, y, p, s.kh, s.sh, st) == ROWS_SERVED) return ROWS_SERVED;
     switch (s.kh * 10 + s.sh) {
       case 31: launch_conv<T, 3, 1, 1>(x, w, y, p, st); break;
       case 51: launch_conv<T, 5, 1, 1>(x, w, y, p, st); break;
@@ -82,6 +93,7 @@ int nhwc_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStre
     p.N = s.N; p.C = s.C; p.Hin = s.Ho; p.Win = s.Wo; p.Hout = s.H; p.Wout = s.W;
     p.pt = s.kh - 1 - s.ph; p.pl = s.kw - 1 - s.pw; p.flip = 1;
     p.ep = EpilogueArgs{nullptr, nullptr, 0, 0};
+    if (s.sh == 1 && nhwc_tma_conv<T>(dy, w, dx, p, s.kh, 1, st) == ROWS_SERVED) return ROWS_SERVED;
     switch (s.kh * 10 + s.sh) {
       case 31: launch_conv<T, 3, 1, 1>(dy, w, dx, p, st); break;
       case 51: launch_conv<T, 5, 1, 1>(dy, w, dx, p, st); break;
@@ -107,6 +119,7 @@ int nhwc_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *parti
     p.N = s.N; p.C = s.C; p.H = s.H; p.W = s.W; p.Ho = s.Ho; p.Wo = s.Wo;
     p.pt = s.ph; p.pl = s.pw; p.SL = nhwc_filter_slices(s);
     *slices_out = p.SL;
+    if (nhwc_tma_filter<T>(x, dy, partial, p, s.kh, s.sh, st) == ROWS_SERVED) return ROWS_SERVED;
     switch (s.kh * 10 + s.sh) {
       case 31: launch_filter<T, 3, 1>(x, dy, partial, p, st); break;
       case 51: launch_filter<T, 5, 1>(x, dy, partial, p, st); break;

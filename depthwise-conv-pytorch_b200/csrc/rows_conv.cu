@@ -60,10 +60,11 @@ int rows_debug_conv_plan(int op, int esize, const Shape &s, int a16, int *out) {
 
 int rows_conv_epi_take_error();  // rows_conv_epi.cu
 int tiles_tma_take_error();      // tiles_tma.cu
+int nhwc_tma_take_error();       // nhwc_tma.cu
 
 int rows_conv_take_error() {
   return conv_take_error_here() | rows_conv_epi_take_error() | rows_bigk_take_error() |
-         tiles_tma_take_error();
+         tiles_tma_take_error() | nhwc_tma_take_error();
 }
 
 template int rows_forward<float>(const float *, const float *, float *, const Shape &, cudaStream_t);

@@ -463,7 +463,9 @@ tile_filter_kernel(const T *__restrict__ x, const T *__restrict__ dy, float *__r
 }
 
 // Resident CTAs of a kernel on the whole device (asked once per instantiation).
-template <typename Kernel> inline int resident_ctas(Kernel kernel) {
+// (The kernel is a template ARGUMENT: kernels of one signature share a function type, and a
+// cache per type would be shared among them.)
+template <auto kernel> inline int resident_ctas() {
   static std::atomic<int> cached{0};
   int v = cached.load(std::memory_order_relaxed);
   if (v == 0) {
@@ -483,9 +485,9 @@ template <typename Kernel> inline int resident_ctas(Kernel kernel) {
 
 // Slices per channel: as many as give every CTA a place on the device at once (one wave of
 // CTAs with equal tile counts), within the bound the workspace was sized for.
-template <typename Kernel>
-inline int filter_slices_for(Kernel kernel, const TileFilterParams &p, int bound) {
-  int S = resident_ctas(kernel) / p.C;
+template <auto kernel>
+inline int filter_slices_for(const TileFilterParams &p, int bound) {
+  int S = resident_ctas<kernel>() / p.C;
   if (S > bound) S = bound;
   const long long total = (long long)p.N * p.tiles_x * p.tiles_y;
   if (S > total) S = (int)total;

@@ -158,12 +158,12 @@ int launch_filter(const T *x, const T *dy, float *partial, TileFilterParams p, i
   if constexpr (fits) {
     if (rows_aligned16(x, p.W) && rows_aligned16(dy, p.Wo)) {
       p.off = stage_off<T>(p.pl);
-      p.SL = filter_slices_for(tile_filter_kernel<T, K, S, TW, V>, p, bound);
+      p.SL = filter_slices_for<tile_filter_kernel<T, K, S, TW, V>>(p, bound);
       tile_filter_kernel<T, K, S, TW, V><<<p.C * p.SL, TILE_THREADS, 0, st>>>(x, dy, partial, p);
       return p.SL;
     }
   }
-  p.SL = filter_slices_for(tile_filter_kernel<T, K, S, TW, 0>, p, bound);
+  p.SL = filter_slices_for<tile_filter_kernel<T, K, S, TW, 0>>(p, bound);
   tile_filter_kernel<T, K, S, TW><<<p.C * p.SL, TILE_THREADS, 0, st>>>(x, dy, partial, p);
   return p.SL;
 }

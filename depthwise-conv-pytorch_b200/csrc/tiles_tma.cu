@@ -1,6 +1,7 @@
 // Tiles family, tensor-copy staged kernels: tensor-map encoding and launches
 // (kernels: tile_tma_kernels.cuh).
 #include "tile_tma_kernels.cuh"
+#include "tensor_map.cuh"
 
 #include <atomic>
 
@@ -9,30 +10,6 @@ namespace dwb {
 namespace {
 
 __device__ int g_tiles_tma_error_flag;
-
-// cuTensorMapEncodeTiled, looked up in the driver at run time (the library does not link
-// libcuda).  Null when the driver has none: the callers then use the other staging forms.
-using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                 const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                 const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encoder() {
-  static std::atomic<int> state{0};  // 0 not asked yet, 1 found, 2 absent
-  static std::atomic<void *> fn{nullptr};
-  int s = state.load(std::memory_order_acquire);
-  if (s == 0) {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
-    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
-    if (e != cudaSuccess) (void)cudaGetLastError();
-    const bool ok = e == cudaSuccess && q == cudaDriverEntryPointSuccess && p != nullptr;
-    fn.store(ok ? p : nullptr, std::memory_order_relaxed);
-    s = ok ? 1 : 2;
-    state.store(s, std::memory_order_release);
-  }
-  return s == 1 ? reinterpret_cast<EncodeTiled>(fn.load(std::memory_order_relaxed)) : nullptr;
-}
 
 int *error_flag_ptr() {
   static std::atomic<int *> cached{nullptr};
@@ -47,26 +24,13 @@ int *error_flag_ptr() {
   return p;
 }
 
-template <typename T> struct MapType;
-template <> struct MapType<float> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; };
-template <> struct MapType<__half> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; };
-template <> struct MapType<__nv_bfloat16> {
-  static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-};
-
-// The maps [planes][H][W] as a (W, H, planes) tensor read in boxes of (bw, bh, 1) elements;
-// what a box holds outside the tensor reads as zero.
+// The maps [planes][H][W] as a (W, H, planes) tensor read in boxes of (bw, bh, 1) elements.
 template <typename T>
 bool encode_planes(CUtensorMap *map, const T *base, int W, int H, int planes, int bw, int bh) {
-  EncodeTiled enc = encoder();
-  if (enc == nullptr) return false;
   const cuuint64_t dims[3] = {(cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)planes};
   const cuuint64_t strides[2] = {(cuuint64_t)W * sizeof(T), (cuuint64_t)W * H * sizeof(T)};
   const cuuint32_t box[3] = {(cuuint32_t)bw, (cuuint32_t)bh, 1u};
-  const cuuint32_t elem[3] = {1u, 1u, 1u};
-  return enc(map, MapType<T>::v, 3, const_cast<T *>(base), dims, strides, box, elem,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode_tensor_map<T>(map, base, 3, dims, strides, box);
 }
 
 template <typename T, int K, int TW>
@@ -112,7 +76,7 @@ int launch_filter(const T *x, const T *dy, float *partial, TileFilterParams p, i
   if (!encode_planes<T>(&dy_map, dy, p.Wo, p.Ho, p.N * p.C, TW, G::TH)) return ROWS_DECLINED;
   p.tiles_x = ceil_div(p.Wo, TW);
   p.tiles_y = ceil_div(p.Ho, G::TH);
-  p.SL = filter_slices_for(tile_tma_filter_kernel<T, K, TW>, p, bound);
+  p.SL = filter_slices_for<tile_tma_filter_kernel<T, K, TW>>(p, bound);
   tile_tma_filter_kernel<T, K, TW><<<p.C * p.SL, TILE_THREADS, 0, st>>>(x_map, dy_map, partial, p, flag);
   *used = p.SL;
   return ROWS_SERVED;

@@ -16,6 +16,9 @@ CASES = [
     (2, 32, 14, 14, 3, 1, 1), (3, 40, 28, 28, 3, 2, 1), (2, 7, 33, 35, 5, 1, 2), (1, 96, 56, 56, 5, 2, 2),
     (2, 65, 17, 19, 7, 1, 3), (1, 33, 30, 41, 7, 2, 3), (2, 16, 20, 20, 3, 1, 0), (1, 48, 21, 21, 5, 2, 0),
     (1, 3, 64, 64, 3, 1, (2, 0)), (4, 160, 7, 7, 3, 1, 1),
+    # enough tiles per CTA for the two-stage tensor-copy pipeline to wrap around (several images
+    # per CTA in the forward, several steps per slice in the filter gradient)
+    (5, 128, 112, 112, 3, 1, 1), (5, 64, 112, 112, 5, 2, 2), (40, 32, 56, 56, 7, 1, 3), (3, 24, 120, 72, 5, 1, 0),
 ]
 
 
@@ -45,6 +48,7 @@ def test_channels_last_through_the_c_abi(cfg, dtn):
     assert torch.equal(y.cpu(), oracle.forward_seq(x, w, s, p))
     assert torch.equal(dx.cpu(), oracle.backward_input_seq(dy, w, (H, W), s, p))
     assert_dw_close(dw, oracle.backward_filter(x, dy, (k, k), s, p), dt, "NHWC dW")
+    assert L.dwconv_b200_device_status() == 0, "a bounded wait expired in a kernel"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16], ids=["f32", "f16", "bf16"])

@@ -629,6 +629,10 @@ def test_exchange_calls_back_to_back(shape, k, s, p, dtype):
     ((2, 4, 20, 17), (5, 5), 2, 2),
     ((2, 3, 12, 12), (3, 5), (1, 2), (1, 2)),
     ((1, 5, 33, 33), (7, 7), 1, 3),
+    # rows on 16-byte boundaries: the tile kernels' tensor-copy (stride 1) and 16-byte staged /
+    # polyphase (stride 2) forms
+    ((2, 4, 24, 40), (5, 5), 1, 2),
+    ((2, 3, 40, 48), (3, 3), 2, 1),
 ])
 def test_bfloat16_against_oracle(shape, k, s, p):
     """bfloat16 (not a reference dtype): fp32 accumulation, one rounding at the end, compared
