@@ -88,6 +88,18 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Grid shaping for kernels whose CTAs keep a tile position and walk the planes (or images)
+// g-th by g-th: how many CTAs share one of `positions` positions over `units` planes, on a device
+// that holds `resident` CTAs of the kernel at once.  One full wave of long-lived CTAs when that
+// fills at least 85 % of the device; otherwise about four waves of shorter-lived ones, so that
+// no large part of the device idles behind a fixed assignment.
+inline int walk_groups(long long resident, long long positions, long long units) {
+  long long g = resident / positions;
+  if (g < 1 || g * positions * 100 < resident * 85) g = (4 * resident + positions - 1) / positions;
+  if (g > units) g = units;
+  return g < 1 ? 1 : (int)g;
+}
 __host__ __device__ __forceinline__ long long ceil_div_ll(long long a, long long b) {
   return (a + b - 1) / b;
 }

@@ -8,6 +8,8 @@ namespace dwb {
 template <typename T>
 int nhwc_tma_conv(const T *in, const T *w, T *out, const NhwcParams &p, int K, int S, cudaStream_t st);
 template <typename T>
+int nhwc_tma_bwd2(const T *dy, const T *w, T *dx, const NhwcParams &p, int K, cudaStream_t st);
+template <typename T>
 int nhwc_tma_filter(const T *x, const T *dy, float *partial, const NhwcFilterParams &p, int K, int S,
                     cudaStream_t st);
 
@@ -94,6 +96,7 @@ int nhwc_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStre
     p.pt = s.kh - 1 - s.ph; p.pl = s.kw - 1 - s.pw; p.flip = 1;
     p.ep = EpilogueArgs{nullptr, nullptr, 0, 0};
     if (s.sh == 1 && nhwc_tma_conv<T>(dy, w, dx, p, s.kh, 1, st) == ROWS_SERVED) return ROWS_SERVED;
+    if (s.sh == 2 && nhwc_tma_bwd2<T>(dy, w, dx, p, s.kh, st) == ROWS_SERVED) return ROWS_SERVED;
     switch (s.kh * 10 + s.sh) {
       case 31: launch_conv<T, 3, 1, 1>(dy, w, dx, p, st); break;
       case 51: launch_conv<T, 5, 1, 1>(dy, w, dx, p, st); break;

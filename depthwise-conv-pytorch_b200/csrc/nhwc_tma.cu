@@ -78,12 +78,29 @@ int launch_conv(const T *in, const T *w, T *out, NhwcParams p, cudaStream_t st) 
   const long long per_img = (long long)p.tiles_x * p.tiles_y * p.cblocks;
   if (per_img > (1ll << 30)) return ROWS_DECLINED;
   p.ntiles = per_img * p.N;
-  // as many CTAs as the device holds at once; each walks its share of the images
-  long long gy = resident / per_img;
-  if (gy < 1) gy = 1;
-  if (gy > p.N) gy = p.N;
+  const int gy = walk_groups(resident, per_img, p.N);  // each CTA walks its share of the images
   nhwc_tma_conv_kernel<T, K, S><<<dim3((unsigned)per_img, (unsigned)gy), G::THREADS, TG::SMEM_BYTES, st>>>(
       map, w, out, p, flag);
+  return ROWS_SERVED;
+}
+
+template <typename T, int K>
+int launch_bwd2(const T *dy, const T *w, T *dx, NhwcParams p, cudaStream_t st) {
+  using G = NhwcBwd2Geo<K>;
+  int *flag = error_flag_ptr();
+  if (flag == nullptr) return ROWS_DECLINED;
+  const int resident = prepare<nhwc_tma_bwd2_kernel<T, K>>(G::THREADS, 0);
+  if (resident < 1) return ROWS_DECLINED;
+  alignas(64) CUtensorMap map;
+  if (!encode_nhwc<T>(&map, dy, p.C, p.Win, p.Hin, p.N, G::IW, G::ND)) return ROWS_DECLINED;
+  p.tiles_x = ceil_div(p.Wout, G::TW);
+  p.tiles_y = ceil_div(p.Hout, G::R);
+  p.cblocks = ceil_div(p.C, NHWC_CB);
+  const long long per_img = (long long)p.tiles_x * p.tiles_y * p.cblocks;
+  if (per_img > (1ll << 30)) return ROWS_DECLINED;
+  p.ntiles = per_img * p.N;
+  const int gy = walk_groups(resident, per_img, p.N);
+  nhwc_tma_bwd2_kernel<T, K><<<dim3((unsigned)per_img, (unsigned)gy), G::THREADS, 0, st>>>(map, w, dx, p, flag);
   return ROWS_SERVED;
 }
 
@@ -123,6 +140,18 @@ int nhwc_tma_conv(const T *in, const T *w, T *out, const NhwcParams &p, int K, i
   }
 }
 
+// Stride-2 backward-input (polyphase): p describes dy -> dx with pt / pl = k-1-padding.
+template <typename T>
+int nhwc_tma_bwd2(const T *dy, const T *w, T *dx, const NhwcParams &p, int K, cudaStream_t st) {
+  if (!tensor_ok(dy, p.C, p.Win, p.Hin)) return ROWS_DECLINED;
+  switch (K) {
+    case 3: return launch_bwd2<T, 3>(dy, w, dx, p, st);
+    case 5: return launch_bwd2<T, 5>(dy, w, dx, p, st);
+    case 7: return launch_bwd2<T, 7>(dy, w, dx, p, st);
+    default: return ROWS_DECLINED;
+  }
+}
+
 // First pass of the filter gradient with p.SL slices per channel block.
 template <typename T>
 int nhwc_tma_filter(const T *x, const T *dy, float *partial, const NhwcFilterParams &p, int K, int S,
@@ -141,6 +170,7 @@ int nhwc_tma_filter(const T *x, const T *dy, float *partial, const NhwcFilterPar
 
 #define DWB_NHWC_TMA_INSTANTIATE(T)                                                               \
   template int nhwc_tma_conv<T>(const T *, const T *, T *, const NhwcParams &, int, int, cudaStream_t); \
+  template int nhwc_tma_bwd2<T>(const T *, const T *, T *, const NhwcParams &, int, cudaStream_t);      \
   template int nhwc_tma_filter<T>(const T *, const T *, float *, const NhwcFilterParams &, int, int,    \
                                   cudaStream_t);
 DWB_NHWC_TMA_INSTANTIATE(float)

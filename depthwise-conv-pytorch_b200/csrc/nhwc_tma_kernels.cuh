@@ -161,6 +161,141 @@ nhwc_tma_conv_kernel(const __grid_constant__ CUtensorMap in_map, const T *__rest
   }
 }
 
+// Backward-input at stride 2, polyphase (the arithmetic of tile_bwd2_kernel in tile_kernels.cuh,
+// with lane = channel): dy is fetched as it is (a dense box of (32 channels, TW/2 + ceil(K/2)
+// columns, ND rows)), and only the products that meet data are issued, in ky-major / kx-minor
+// order.  The output column, and with it the parity of the kx that meet data, is the same for all
+// lanes of a warp.  A tile is 8 rows x 16 columns of dx; staged row d is dy row
+// floor((y0 - pt) / 2) + d, and ky = 2d - P - o for output row y0 + o (P = pt & 1).
+template <int K> struct NhwcBwd2Geo {
+  static constexpr int R = 8, TW = 16;
+  static constexpr int THREADS = NHWC_CB * TW;
+  static constexpr int KH = (K + 1) / 2;
+  static constexpr int ND = (K + R - 1) / 2 + 1;  // dy rows under a tile
+  static constexpr int IW = TW / 2 + KH;          // dy columns under a tile
+};
+
+template <typename T, int K, bool PODD>
+__device__ __forceinline__ void nhwc_bwd2_rows(const unsigned char *stage, int col0, int lane,
+                                               const float (&tsel)[K][(K + 1) / 2], float (&acc)[8]) {
+  using G = NhwcBwd2Geo<K>;
+  constexpr int P = PODD ? 1 : 0;
+#pragma unroll
+  for (int d = 0; d < G::ND; ++d) {
+    float v[G::KH];
+#pragma unroll
+    for (int j = 0; j < G::KH; ++j) v[j] = nhwc_smem_elem<T>(stage, (d * G::IW + col0 + j) * NHWC_CB + lane);
+#pragma unroll
+    for (int o = 0; o < G::R; ++o) {
+      const int ky = 2 * d - P - o;
+      if (ky >= 0 && ky < K) {
+#pragma unroll
+        for (int j = 0; j < G::KH; ++j) acc[o] = fmaf(v[j], tsel[ky][j], acc[o]);
+      }
+    }
+  }
+}
+
+// p: Hin x Win = dy, Hout x Wout = dx, pt / pl = k-1-padding.
+template <typename T, int K>
+__global__ void __launch_bounds__(NhwcBwd2Geo<K>::THREADS)
+nhwc_tma_bwd2_kernel(const __grid_constant__ CUtensorMap dy_map, const T *__restrict__ w,
+                     T *__restrict__ out, const NhwcParams p, int *error_flag) {
+  using G = NhwcBwd2Geo<K>;
+  constexpr int KK = K * K;
+  constexpr int BOX_BYTES = G::ND * G::IW * NHWC_CB * (int)sizeof(T);
+  constexpr int STAGE_BYTES = (BOX_BYTES + 127) / 128 * 128;
+  static_assert(2 * STAGE_BYTES + 64 <= 48 * 1024, "two stages must fit static shared memory");
+  __shared__ __align__(128) unsigned char stages[2][STAGE_BYTES];
+  __shared__ uint64_t full[2];
+  const int lane = threadIdx.x & 31;
+  const int col = threadIdx.x >> 5;  // output column inside the tile
+  int rest = blockIdx.x;
+  const int cb = rest % p.cblocks;
+  rest /= p.cblocks;
+  const int ty = rest / p.tiles_x, tx = rest - ty * p.tiles_x;
+  const int y0 = ty * G::R, x0 = tx * G::TW, c0 = cb * NHWC_CB;  // y0, x0 even
+  const int c = c0 + lane;
+  const int px = p.pl & 1;
+  const int qx = (px + col) & 1;  // parity of the kx that meet data under this column
+  const int col0 = (col + qx + px) >> 1;
+  const int gy0 = (y0 - p.pt - (p.pt & 1)) / 2, gx0 = (x0 - p.pl - px) / 2;  // floor((y0-pt)/2), ...
+  const int step = gridDim.y;
+  if (threadIdx.x == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  int asked0 = 0, asked1 = 0, landed0 = 0, landed1 = 0;
+  if (threadIdx.x == 0) {
+    if ((int)blockIdx.y < p.N) {
+      mbar_arrive_expect_tx(&full[0], BOX_BYTES);
+      tma_load_4d(stages[0], &dy_map, c0, gx0, gy0, blockIdx.y, &full[0]);
+      asked0 = 1;
+    }
+    if ((int)blockIdx.y + step < p.N) {
+      mbar_arrive_expect_tx(&full[1], BOX_BYTES);
+      tma_load_4d(stages[1], &dy_map, c0, gx0, gy0, blockIdx.y + step, &full[1]);
+      asked1 = 1;
+    }
+  }
+  float tsel[K][G::KH];
+#pragma unroll
+  for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+    for (int j = 0; j < G::KH; ++j) {
+      const int kx = qx + 2 * j;  // flipped filter: wf[ky][kx] = w[K-1-ky][K-1-kx]
+      tsel[ky][j] = (kx < K && c < p.C) ? Elem<T>::ld(w + (size_t)c * KK + (K - 1 - ky) * K + (K - 1 - kx)) : 0.f;
+    }
+  bool gave_up = false;
+  int it = 0;
+  for (int n = blockIdx.y; n < p.N; n += step, ++it) {
+    const int s = it & 1;
+    if (!gave_up) {
+      if (mbar_wait_bounded(&full[s], (it >> 1) & 1)) {
+        landed0 += 1 - s;
+        landed1 += s;
+      } else {
+        gave_up = true;
+        atomicOr(error_flag, 1);
+      }
+    }
+    float acc[G::R];
+#pragma unroll
+    for (int o = 0; o < G::R; ++o) acc[o] = 0.f;
+    if (p.pt & 1)
+      nhwc_bwd2_rows<T, K, true>(stages[s], col0, lane, tsel, acc);
+    else
+      nhwc_bwd2_rows<T, K, false>(stages[s], col0, lane, tsel, acc);
+    const int ox = x0 + col;
+    if (ox < p.Wout && c < p.C) {
+      T *op = out + (((size_t)n * p.Hout + y0) * p.Wout + ox) * p.C + c;
+      const size_t row_stride = (size_t)p.Wout * p.C;
+      const int rows = p.Hout - y0;
+#pragma unroll
+      for (int o = 0; o < G::R; ++o) {
+        if (o < rows) *op = Elem<T>::from_acc(acc[o]);
+        op += row_stride;
+      }
+    }
+    __syncthreads();  // every thread has read stage s: it may be refilled
+    if (threadIdx.x == 0 && !gave_up) {
+      const int next = n + 2 * step;
+      if (next < p.N) {
+        mbar_arrive_expect_tx(&full[s], BOX_BYTES);
+        tma_load_4d(stages[s], &dy_map, c0, gx0, gy0, next, &full[s]);
+        asked0 += 1 - s;
+        asked1 += s;
+      }
+    }
+  }
+  if (threadIdx.x == 0 && gave_up) {
+    while (landed0 < asked0 && mbar_wait_bounded(&full[0], landed0 & 1)) ++landed0;
+    while (landed1 < asked1 && mbar_wait_bounded(&full[1], landed1 & 1)) ++landed1;
+  }
+}
+
 // Filter gradient, first pass: as nhwc_filter_kernel (block (channel block, slice) walks its
 // share of the (image, tile) list, thread (channel, dy column) keeps K*K sums, the columns are
 // added in order at the end), with the x tile and the dy tile of every step brought in by one

@@ -19,6 +19,9 @@ CASES = [
     # enough tiles per CTA for the two-stage tensor-copy pipeline to wrap around (several images
     # per CTA in the forward, several steps per slice in the filter gradient)
     (5, 128, 112, 112, 3, 1, 1), (5, 64, 112, 112, 5, 2, 2), (40, 32, 56, 56, 7, 1, 3), (3, 24, 120, 72, 5, 1, 0),
+    # stride 2 with every filter size and paddings of both parities (the polyphase backward-input)
+    (2, 16, 30, 41, 7, 2, 3), (2, 8, 33, 35, 3, 2, 0), (1, 24, 20, 20, 5, 2, (1, 2)), (3, 32, 28, 28, 7, 2, (2, 5)),
+    (2, 40, 17, 16, 3, 2, 2),
 ]
 
 
