@@ -782,28 +782,79 @@ def gpu_arm(args, layers):
 def time_api(layers, reps):
     """CUDA-event timing of the public Python API (``depthwise_conv2d`` forward, and forward +
     ``backward``) on arbitrary layers, the way ``oracle/ref_cuda.py --time`` times the reference's
-    CUDA route: rotating buffer sets larger than L2, 3 warm-up calls.  Prints one JSON object."""
+    CUDA route: rotating buffer sets larger than L2, 3 warm-up calls; and of the three operators
+    through the C entry points (``ops_ms``).  A layer is [N, C, H, (W,) k, stride, padding, dtype]
+    with an optional last element "nhwc" for channels-last tensors.  Prints one JSON object."""
     import torch
     import dwconv_b200
     from dwconv_b200 import _lib
     dts = {"f32": torch.float32, "f16": torch.float16}
     res = []
     for layer in layers:
-        if len(layer) == 8:
-            N, C, H, W, k, s, p, dt = layer
+        layer = list(layer)
+        nhwc = layer[-1] == "nhwc"  # optional last element: channels-last tensors
+        spec = layer[:-1] if nhwc else layer
+        if len(spec) == 8:
+            N, C, H, W, k, s, p, dt = spec
         else:
-            N, C, H, k, s, p, dt = layer
+            N, C, H, k, s, p, dt = spec
             W = H
+        fmt = torch.channels_last if nhwc else torch.contiguous_format
         ho, wo = out_hw(H, k, s, p), out_hw(W, k, s, p)
         per_set = 2 * N * C * (H * W + ho * wo) * ESIZE[dt]
         n_sets = max(2, min(8, int(2 * L2_BYTES // per_set) + 2))
         sets = []
         for si in range(n_sets):
             g = torch.Generator(device="cuda").manual_seed(si)
-            x = torch.randn((N, C, H, W), generator=g, device="cuda").to(dts[dt]).requires_grad_(True)
+            x = torch.randn((N, C, H, W), generator=g, device="cuda").to(dts[dt]).contiguous(
+                memory_format=fmt).requires_grad_(True)
             w = (torch.randn((C, 1, k, k), generator=g, device="cuda") / k).to(dts[dt]).requires_grad_(True)
-            dy = torch.randn((N, C, ho, wo), generator=g, device="cuda").to(dts[dt])
+            dy = torch.randn((N, C, ho, wo), generator=g, device="cuda").to(dts[dt]).contiguous(
+                memory_format=fmt)
             sets.append((x, w, dy))
+
+        # the three operators through the C entry points (no Python layer, no allocation)
+        shape = _lib.Shape(N, C, H, W, k, k, s, s, p, p, ho, wo)
+        code = {"f32": _lib.F32, "f16": _lib.F16}[dt]
+        L = _lib.lib
+        ys = [torch.empty_like(t[2]) for t in sets]
+        dxs = [torch.empty_like(t[0]) for t in sets]
+        ws_bytes = int(L.dwconv_b200_backward_filter_workspace_bytes(code, shape))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+        dw = torch.empty((C, 1, k, k), dtype=dts[dt], device="cuda")
+        st = torch.cuda.current_stream().cuda_stream
+
+        def op_forward(i):
+            x, w, dy = sets[i % n_sets]
+            if nhwc:
+                return L.dwconv_b200_forward_nhwc(x.data_ptr(), w.data_ptr(), ys[i % n_sets].data_ptr(), code,
+                                                  shape, None, st)
+            return L.dwconv_b200_forward(x.data_ptr(), w.data_ptr(), ys[i % n_sets].data_ptr(), code, shape, st)
+
+        def op_backward_input(i):
+            x, w, dy = sets[i % n_sets]
+            f = L.dwconv_b200_backward_input_nhwc if nhwc else L.dwconv_b200_backward_input
+            return f(dy.data_ptr(), w.data_ptr(), dxs[i % n_sets].data_ptr(), code, shape, st)
+
+        def op_backward_filter(i):
+            x, w, dy = sets[i % n_sets]
+            f = L.dwconv_b200_backward_filter_nhwc if nhwc else L.dwconv_b200_backward_filter
+            return f(x.data_ptr(), dy.data_ptr(), dw.data_ptr(), ws.data_ptr(), ws_bytes, code, shape, st)
+
+        ops = {}
+        for name, fn in (("forward", op_forward), ("backward_input", op_backward_input),
+                         ("backward_filter", op_backward_filter)):
+            for i in range(3):
+                _lib.check(fn(i), name)
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for i in range(reps):
+                fn(i)
+            z.record()
+            torch.cuda.synchronize()
+            ops[name] = round(a.elapsed_time(z) / reps, 5)
+        del ys, dxs
 
         def fwd(i):
             x, w, dy = sets[i % n_sets]
@@ -830,7 +881,9 @@ def time_api(layers, reps):
             times[name] = a.elapsed_time(z) / reps
         res.append({"layer": list(layer), "forward_ms": round(times["forward"], 5),
                     "forward_backward_ms": round(times["forward_backward"], 5),
-                    "kernel_family": {1: "direct", 2: "rows"}.get(_lib.lib.dwconv_b200_last_path()),
+                    "ops_ms": ops, "layout": "nhwc" if nhwc else "nchw",
+                    "kernel_family": "nhwc" if nhwc else {1: "direct", 2: "rows", 3: "tiles"}.get(
+                        _lib.lib.dwconv_b200_last_path()),
                     "buffer_sets": n_sets})
         del sets
         torch.cuda.empty_cache()
