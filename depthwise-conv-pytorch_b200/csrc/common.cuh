@@ -39,6 +39,24 @@ template <> struct Elem<double> {
   static __device__ __forceinline__ double from_acc(double v) { return v; }
 };
 
+// acc + a * b with ONE rounding, a and b in the tensors' storage type.  For the 16-bit types
+// this is the mixed-precision multiply-add of sm_100 (fma.rn.f32.f16 / .bf16): the product of
+// two 11-bit (8-bit) significands is exact in fp32, so the result equals
+// fmaf(float(a), float(b), acc) bit for bit, without the two conversions.
+__device__ __forceinline__ float fma_mix(float a, float b, float acc) { return fmaf(a, b, acc); }
+__device__ __forceinline__ float fma_mix(__half a, __half b, float acc) {
+  float d;
+  asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(__half_as_ushort(a)), "h"(__half_as_ushort(b)), "f"(acc));
+  return d;
+}
+__device__ __forceinline__ float fma_mix(__nv_bfloat16 a, __nv_bfloat16 b, float acc) {
+  float d;
+  asm("fma.rn.f32.bf16 %0, %1, %2, %3;"
+      : "=f"(d)
+      : "h"(__bfloat16_as_ushort(a)), "h"(__bfloat16_as_ushort(b)), "f"(acc));
+  return d;
+}
+
 // One fused multiply-add, never split by the compiler.
 __device__ __forceinline__ float fma_acc(float a, float b, float c) { return fmaf(a, b, c); }
 __device__ __forceinline__ double fma_acc(double a, double b, double c) { return fma(a, b, c); }

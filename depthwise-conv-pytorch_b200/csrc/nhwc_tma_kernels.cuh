@@ -48,8 +48,10 @@ template <typename T> __device__ __forceinline__ float nhwc_smem_elem(const unsi
 
 // Forward (any stride the family has) and stride-1 backward-input (flip).  Grid: x = (tile row,
 // tile column, channel block), channel blocks innermost; y = first image.
+// (Two CTAs per SM as the register target at stride 1, 512 threads: left to itself the compiler
+// aims at four and spills.)
 template <typename T, int K, int S>
-__global__ void __launch_bounds__(NhwcGeo<K, S>::THREADS)
+__global__ void __launch_bounds__(NhwcGeo<K, S>::THREADS, (S == 1 && K < 7) ? 2 : 1)
 nhwc_tma_conv_kernel(const __grid_constant__ CUtensorMap in_map, const T *__restrict__ w,
                      T *__restrict__ out, const NhwcParams p, int *error_flag) {
   using G = NhwcGeo<K, S>;
@@ -87,13 +89,14 @@ nhwc_tma_conv_kernel(const __grid_constant__ CUtensorMap in_map, const T *__rest
     }
   }
   // the CTA's channels do not change: taps and epilogue coefficients are loaded once
-  float tap[K][K];
+  // (taps and staged values stay in the storage type: fma_mix multiplies them as they are)
+  T tap[K][K];
 #pragma unroll
   for (int ky = 0; ky < K; ++ky)
 #pragma unroll
     for (int kx = 0; kx < K; ++kx)
-      tap[ky][kx] = c < p.C ? Elem<T>::ld(w + (size_t)c * KK + (p.flip ? KK - 1 - (ky * K + kx) : ky * K + kx))
-                            : 0.f;
+      tap[ky][kx] = c < p.C ? __ldg(w + (size_t)c * KK + (p.flip ? KK - 1 - (ky * K + kx) : ky * K + kx))
+                            : Elem<T>::from_acc(0.f);
   float sc = 1.f, bi = 0.f;
   if (p.ep.on && c < p.C) epilogue_coeffs<T>(p.ep, c, sc, bi);
   bool gave_up = false;
@@ -115,16 +118,16 @@ nhwc_tma_conv_kernel(const __grid_constant__ CUtensorMap in_map, const T *__rest
     for (int o = 0; o < G::R; ++o) acc[o] = 0.f;
 #pragma unroll
     for (int ir = 0; ir < G::IH; ++ir) {
-      float v[K];
+      T v[K];
 #pragma unroll
       for (int kx = 0; kx < K; ++kx)
-        v[kx] = nhwc_smem_elem<T>(stage, (ir * G::IW + col * S + kx) * NHWC_CB + lane);
+        v[kx] = reinterpret_cast<const T *>(stage)[(ir * G::IW + col * S + kx) * NHWC_CB + lane];
 #pragma unroll
       for (int o = 0; o < G::R; ++o) {
         const int ky = ir - o * S;
         if (ky >= 0 && ky < K) {
 #pragma unroll
-          for (int kx = 0; kx < K; ++kx) acc[o] = fmaf(v[kx], tap[ky][kx], acc[o]);
+          for (int kx = 0; kx < K; ++kx) acc[o] = fma_mix(v[kx], tap[ky][kx], acc[o]);
         }
       }
     }
@@ -198,7 +201,7 @@ __device__ __forceinline__ void nhwc_bwd2_rows(const unsigned char *stage, int c
 
 // p: Hin x Win = dy, Hout x Wout = dx, pt / pl = k-1-padding.
 template <typename T, int K>
-__global__ void __launch_bounds__(NhwcBwd2Geo<K>::THREADS)
+__global__ void __launch_bounds__(NhwcBwd2Geo<K>::THREADS, 2)
 nhwc_tma_bwd2_kernel(const __grid_constant__ CUtensorMap dy_map, const T *__restrict__ w,
                      T *__restrict__ out, const NhwcParams p, int *error_flag) {
   using G = NhwcBwd2Geo<K>;

@@ -170,8 +170,10 @@ __device__ __forceinline__ void tile_stage(float *sm, const T *__restrict__ plan
 }
 
 // out[oy][ox] = sum over (ky, kx) of in[oy*S - pt + ky][ox*S - pl + kx] * tap[ky][kx].
+// (Four CTAs per SM, two for 7x7, as the register target: left to itself the compiler aims at
+// eight, with 32 registers per thread.)
 template <typename T, int K, int S, int TW, int VEC = 0>
-__global__ void __launch_bounds__(TILE_THREADS)
+__global__ void __launch_bounds__(TILE_THREADS, K == 7 ? 2 : 4)
 tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restrict__ out,
                  const TileParams p) {
   using G = TileGeo<T, K, S, TW, VEC>;

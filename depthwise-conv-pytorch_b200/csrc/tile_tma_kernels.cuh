@@ -52,7 +52,7 @@ template <typename T> __device__ __forceinline__ float smem_elem(const unsigned 
 
 // Forward and (flip, other paddings) backward-input at stride 1.  p.off as in TileParams.
 template <typename T, int K, int TW>
-__global__ void __launch_bounds__(TILE_THREADS, K == 3 ? 6 : (K == 5 ? 4 : 3))
+__global__ void __launch_bounds__(TILE_THREADS, K == 7 ? 3 : 4)
 tile_tma_conv_kernel(const __grid_constant__ CUtensorMap in_map, const T *__restrict__ w,
                      T *__restrict__ out, const TileParams p, int *error_flag) {
   using G = TileTmaGeo<T, K, TW>;
@@ -92,14 +92,14 @@ tile_tma_conv_kernel(const __grid_constant__ CUtensorMap in_map, const T *__rest
   int it = 0;
   for (int plane = blockIdx.y; plane < p.NC; plane += step, ++it) {
     const int s = it & 1;
-    float tap[K][K];
+    T tap[K][K];  // taps and staged values stay in the storage type: fma_mix multiplies them as they are
     {
       const T *tp = w + (size_t)chan * KK;
 #pragma unroll
       for (int ky = 0; ky < K; ++ky)
 #pragma unroll
         for (int kx = 0; kx < K; ++kx)
-          tap[ky][kx] = Elem<T>::ld(tp + (p.flip ? KK - 1 - (ky * K + kx) : ky * K + kx));
+          tap[ky][kx] = __ldg(tp + (p.flip ? KK - 1 - (ky * K + kx) : ky * K + kx));
     }
     if (!gave_up) {
       if (mbar_wait_bounded(&full[s], (it >> 1) & 1)) {
@@ -117,15 +117,15 @@ tile_tma_conv_kernel(const __grid_constant__ CUtensorMap in_map, const T *__rest
     const int first = (tr * TILE_R) * G::BW + p.off + tc;
 #pragma unroll
     for (int ir = 0; ir < G::IR; ++ir) {
-      float v[K];
+      T v[K];
 #pragma unroll
-      for (int kx = 0; kx < K; ++kx) v[kx] = smem_elem<T>(stage, first + ir * G::BW + kx);
+      for (int kx = 0; kx < K; ++kx) v[kx] = reinterpret_cast<const T *>(stage)[first + ir * G::BW + kx];
 #pragma unroll
       for (int o = 0; o < TILE_R; ++o) {
         const int ky = ir - o;
         if (ky >= 0 && ky < K) {
 #pragma unroll
-          for (int kx = 0; kx < K; ++kx) acc[o] = fmaf(v[kx], tap[ky][kx], acc[o]);
+          for (int kx = 0; kx < K; ++kx) acc[o] = fma_mix(v[kx], tap[ky][kx], acc[o]);
         }
       }
     }
