@@ -305,7 +305,7 @@ nhwc_tma_bwd2_kernel(const __grid_constant__ CUtensorMap dy_map, const T *__rest
 // tensor copy each, two steps in flight.  dy pixels beyond the map's edge read as zero and add
 // nothing.
 template <typename T, int K, int S>
-__global__ void __launch_bounds__(NhwcGeo<K, S, true>::THREADS)
+__global__ void __launch_bounds__(NhwcGeo<K, S, true>::THREADS, (S == 1 && K < 7) ? 2 : 1)
 nhwc_tma_filter_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap dy_map,
                        float *__restrict__ partial, const NhwcFilterParams p, int *error_flag) {
   using G = NhwcGeo<K, S, true>;

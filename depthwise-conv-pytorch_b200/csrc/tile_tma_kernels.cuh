@@ -52,7 +52,7 @@ template <typename T> __device__ __forceinline__ float smem_elem(const unsigned 
 
 // Forward and (flip, other paddings) backward-input at stride 1.  p.off as in TileParams.
 template <typename T, int K, int TW>
-__global__ void __launch_bounds__(TILE_THREADS, K == 7 ? 3 : 4)
+__global__ void __launch_bounds__(TILE_THREADS, K == 3 ? 6 : (K == 5 ? 4 : 3))
 tile_tma_conv_kernel(const __grid_constant__ CUtensorMap in_map, const T *__restrict__ w,
                      T *__restrict__ out, const TileParams p, int *error_flag) {
   using G = TileTmaGeo<T, K, TW>;

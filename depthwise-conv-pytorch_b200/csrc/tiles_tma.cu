@@ -50,7 +50,7 @@ int launch(const T *in, const T *w, T *out, TileParams p, cudaStream_t st) {
   const int per_plane = p.tiles_x * p.tiles_y;
   // as many CTAs as the device holds at once (the kernel's launch bounds); each walks its share
   // of the planes, its two stages overlapping copy and arithmetic
-  const int gy = walk_groups(148 * (K == 7 ? 3 : 4), per_plane, p.NC);
+  const int gy = walk_groups(148 * (K == 3 ? 6 : (K == 5 ? 4 : 3)), per_plane, p.NC);
   tile_tma_conv_kernel<T, K, TW><<<dim3(per_plane, gy), TILE_THREADS, 0, st>>>(map, w, out, p, flag);
   return ROWS_SERVED;
 }
