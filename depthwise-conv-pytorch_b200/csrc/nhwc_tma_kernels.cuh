@@ -42,10 +42,6 @@ __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, i
       : "memory");
 }
 
-template <typename T> __device__ __forceinline__ float nhwc_smem_elem(const unsigned char *stage, int idx) {
-  return Elem<T>::to_acc(reinterpret_cast<const T *>(stage)[idx]);
-}
-
 // Forward (any stride the family has) and stride-1 backward-input (flip).  Grid: x = (tile row,
 // tile column, channel block), channel blocks innermost; y = first image.
 // (Two CTAs per SM as the register target at stride 1, 512 threads: left to itself the compiler
@@ -180,20 +176,21 @@ template <int K> struct NhwcBwd2Geo {
 
 template <typename T, int K, bool PODD>
 __device__ __forceinline__ void nhwc_bwd2_rows(const unsigned char *stage, int col0, int lane,
-                                               const float (&tsel)[K][(K + 1) / 2], float (&acc)[8]) {
+                                               const T (&tsel)[K][(K + 1) / 2], float (&acc)[8]) {
   using G = NhwcBwd2Geo<K>;
   constexpr int P = PODD ? 1 : 0;
 #pragma unroll
   for (int d = 0; d < G::ND; ++d) {
-    float v[G::KH];
+    T v[G::KH];
 #pragma unroll
-    for (int j = 0; j < G::KH; ++j) v[j] = nhwc_smem_elem<T>(stage, (d * G::IW + col0 + j) * NHWC_CB + lane);
+    for (int j = 0; j < G::KH; ++j)
+      v[j] = reinterpret_cast<const T *>(stage)[(d * G::IW + col0 + j) * NHWC_CB + lane];
 #pragma unroll
     for (int o = 0; o < G::R; ++o) {
       const int ky = 2 * d - P - o;
       if (ky >= 0 && ky < K) {
 #pragma unroll
-        for (int j = 0; j < G::KH; ++j) acc[o] = fmaf(v[j], tsel[ky][j], acc[o]);
+        for (int j = 0; j < G::KH; ++j) acc[o] = fma_mix(v[j], tsel[ky][j], acc[o]);
       }
     }
   }
@@ -243,13 +240,14 @@ nhwc_tma_bwd2_kernel(const __grid_constant__ CUtensorMap dy_map, const T *__rest
       asked1 = 1;
     }
   }
-  float tsel[K][G::KH];
+  T tsel[K][G::KH];
 #pragma unroll
   for (int ky = 0; ky < K; ++ky)
 #pragma unroll
     for (int j = 0; j < G::KH; ++j) {
       const int kx = qx + 2 * j;  // flipped filter: wf[ky][kx] = w[K-1-ky][K-1-kx]
-      tsel[ky][j] = (kx < K && c < p.C) ? Elem<T>::ld(w + (size_t)c * KK + (K - 1 - ky) * K + (K - 1 - kx)) : 0.f;
+      tsel[ky][j] = (kx < K && c < p.C) ? __ldg(w + (size_t)c * KK + (K - 1 - ky) * K + (K - 1 - kx))
+                                        : Elem<T>::from_acc(0.f);
     }
   bool gave_up = false;
   int it = 0;
@@ -370,21 +368,21 @@ nhwc_tma_filter_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_c
     }
     const unsigned char *sx = nhwc_smem + s * TG::STAGE_BYTES;
     const unsigned char *sdy = sx + TG::X_SLOT;
-    float g[G::R];
+    T g[G::R];
 #pragma unroll
-    for (int o = 0; o < G::R; ++o) g[o] = nhwc_smem_elem<T>(sdy, (o * G::TW + col) * NHWC_CB + lane);
+    for (int o = 0; o < G::R; ++o) g[o] = reinterpret_cast<const T *>(sdy)[(o * G::TW + col) * NHWC_CB + lane];
 #pragma unroll
     for (int ir = 0; ir < G::IH; ++ir) {
-      float v[K];
+      T v[K];
 #pragma unroll
       for (int kx = 0; kx < K; ++kx)
-        v[kx] = nhwc_smem_elem<T>(sx, (ir * G::IW + col * S + kx) * NHWC_CB + lane);
+        v[kx] = reinterpret_cast<const T *>(sx)[(ir * G::IW + col * S + kx) * NHWC_CB + lane];
 #pragma unroll
       for (int o = 0; o < G::R; ++o) {
         const int ky = ir - o * S;
         if (ky >= 0 && ky < K) {
 #pragma unroll
-          for (int kx = 0; kx < K; ++kx) acc[ky][kx] = fmaf(g[o], v[kx], acc[ky][kx]);
+          for (int kx = 0; kx < K; ++kx) acc[ky][kx] = fma_mix(g[o], v[kx], acc[ky][kx]);
         }
       }
     }

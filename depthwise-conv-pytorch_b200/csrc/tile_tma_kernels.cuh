@@ -46,10 +46,6 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, i
       : "memory");
 }
 
-template <typename T> __device__ __forceinline__ float smem_elem(const unsigned char *stage, int idx) {
-  return Elem<T>::to_acc(reinterpret_cast<const T *>(stage)[idx]);
-}
-
 // Forward and (flip, other paddings) backward-input at stride 1.  p.off as in TileParams.
 template <typename T, int K, int TW>
 __global__ void __launch_bounds__(TILE_THREADS, K == 3 ? 6 : (K == 5 ? 4 : 3))
@@ -239,21 +235,21 @@ tile_tma_filter_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_c
     }
     const unsigned char *xs = stages[s];
     const unsigned char *gs = stages[s] + X_BYTES;
-    float g[TILE_R];
+    T g[TILE_R];
 #pragma unroll
-    for (int o = 0; o < TILE_R; ++o) g[o] = smem_elem<T>(gs, (tr * TILE_R + o) * TW + tc);
+    for (int o = 0; o < TILE_R; ++o) g[o] = reinterpret_cast<const T *>(gs)[(tr * TILE_R + o) * TW + tc];
     const int first = (tr * TILE_R) * G::BW + p.off + tc;
 #pragma unroll
     for (int ir = 0; ir < G::IR; ++ir) {
-      float v[K];
+      T v[K];
 #pragma unroll
-      for (int kx = 0; kx < K; ++kx) v[kx] = smem_elem<T>(xs, first + ir * G::BW + kx);
+      for (int kx = 0; kx < K; ++kx) v[kx] = reinterpret_cast<const T *>(xs)[first + ir * G::BW + kx];
 #pragma unroll
       for (int o = 0; o < TILE_R; ++o) {
         const int ky = ir - o;
         if (ky >= 0 && ky < K) {
 #pragma unroll
-          for (int kx = 0; kx < K; ++kx) acc[ky][kx] = fmaf(g[o], v[kx], acc[ky][kx]);
+          for (int kx = 0; kx < K; ++kx) acc[ky][kx] = fma_mix(g[o], v[kx], acc[ky][kx]);
         }
       }
     }
