@@ -16,8 +16,9 @@ closes the step).  Rank 0 prints ONE JSON line:
                  (the unfused definition, whether or not the backward is fused);
 * ``e2e``        the same metric through the public Python API with pinned HOST buffers:
                  host->device copies of x, w, dy and device->host copies of y, dx, dW inside
-                 the timed region; ``copy_ceiling_ms`` beside it is the same bytes moved both
-                 ways at once with no kernel at all;
+                 the timed region, every step, two consecutive steps in flight at a time
+                 (``HostMapsPipeline``; ``serial_ms_per_step``: one at a time); ``copy_ceiling_ms``
+                 beside it is the same bytes moved both ways at once with no kernel at all;
 * ``roofline``   the slowest kernel of the step, timed alone with CUDA events, its own
                  algorithmic bytes against the measured HBM copy bandwidth (MEASURED_PEAKS.json);
 * ``cpu_baseline`` the reference's CPU route timed on this machine's host cores (rank 0, N = 1);
@@ -630,6 +631,8 @@ def gpu_arm(args, layers):
 
     # ---- e2e: public Python API, pinned host buffers, copies inside the timed region ----
     host = []
+    depth = 1 if args.no_e2e else max(1, args.e2e_depth)
+    more_hosts = [[] for _ in range(depth - 1)]
     for (N, C, H, k, s, p, dt) in layers:
         g = torch.Generator().manual_seed(77)
         ho = out_hw(H, k, s, p)
@@ -639,16 +642,35 @@ def gpu_arm(args, layers):
         outs = [torch.empty_like(hdy).pin_memory(), torch.empty_like(hx).pin_memory(),
                 torch.empty_like(hw_).pin_memory()]
         host.append((hx, hw_, hdy, outs, s, p))
+        # further sets of host buffers: the steps in flight at a time each have their own
+        for extra in more_hosts:
+            extra.append((hx.clone().pin_memory(), hw_, hdy.clone().pin_memory(),
+                          [torch.empty_like(o).pin_memory() for o in outs], s, p))
     h2d = sum(t.numel() * t.element_size() for h in host for t in h[:3])
     d2h = sum(t.numel() * t.element_size() for h in host for t in h[3])
 
+    # Every step reads its inputs from pinned host memory and leaves its results there.  `depth`
+    # steps (default 2) are in flight at a time (HostMapsPipeline: the uploads of step i+1 run
+    # under the downloads of step i, each step on host buffers of its own); `serial_ms_per_step`
+    # is the same with one step at a time.
     pipes = [] if args.no_e2e else [
+        dwconv_b200.HostMapsPipeline(hx.shape, hw_.shape[2], s, p, depth=depth, dtype=hx.dtype, device=dev,
+                                     all_reduce=world > 1, chunk_images=args.e2e_chunk)
+        for hx, hw_, hdy, outs, s, p in host]
+    serial_pipes = [] if args.no_e2e else [
         dwconv_b200.HostMapsStep(hx.shape, hw_.shape[2], s, p, dtype=hx.dtype, device=dev,
                                  all_reduce=world > 1)
         for hx, hw_, hdy, outs, s, p in host]
+    e2e_count = [0]
 
     def e2e_step():
-        for pipe, (hx, hw_, hdy, outs, s, p) in zip(pipes, host):
+        bufs = ([host] + more_hosts)[e2e_count[0] % depth]
+        e2e_count[0] += 1
+        for pipe, (hx, hw_, hdy, outs, s, p) in zip(pipes, bufs):
+            pipe.run(hx, hw_, hdy, outs[0], outs[1], outs[2])
+
+    def e2e_step_serial():
+        for pipe, (hx, hw_, hdy, outs, s, p) in zip(serial_pipes, host):
             pipe.run(hx, hw_, hdy, outs[0], outs[1], outs[2])
 
     def max_over_ranks(v):
@@ -658,9 +680,21 @@ def gpu_arm(args, layers):
             return float(t.item())
         return v
 
-    e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 20))
-    for _ in range(3 if e2e_steps else 0):
+    e2e_steps = 0 if args.no_e2e else max(4, min(args.steps, 20))
+    serial_s = None
+    if e2e_steps:
+        for _ in range(3):
+            e2e_step_serial()
+        torch.cuda.synchronize()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step_serial()
+        torch.cuda.synchronize()
+        serial_s = max_over_ranks((time.perf_counter() - t0) / e2e_steps)
+    for _ in range(3 * depth if e2e_steps else 0):  # each step object: eager, record, replay
         e2e_step()
+    torch.cuda.synchronize()
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
@@ -755,9 +789,13 @@ def gpu_arm(args, layers):
                 "value": round(e2e_val, 3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 4),
                 "copy_ceiling_ms": round(ceiling_s * 1e3, 4),
-                "api": "dwconv_b200.HostMapsStep.run: pinned host x, w, dy -> pinned host y, dx, dw; "
-                       f"batch cut into chunks of {pipes[0].chunk} images, upload / kernels / "
-                       "download on three streams",
+                "steps_in_flight": depth, "serial_ms_per_step": round(serial_s * 1e3, 4),
+                "api": "dwconv_b200.HostMapsPipeline.run: pinned host x, w, dy -> pinned host y, dx, dw, "
+                       "every step; a step's batch is cut into chunks of "
+                       f"{pipes[0].steps[0].chunk} images (upload / kernels / download on three streams) and "
+                       f"{depth} consecutive steps overlap, each on host buffers of its own; "
+                       f"serial_ms_per_step: one step at a time (HostMapsStep.run, chunks of "
+                       f"{serial_pipes[0].chunk} images)",
                 "gpu_launches_per_step": sum(p.launches_per_run for p in pipes)},
             "stack": stack_entry,
             "strong": strong,
@@ -904,6 +942,10 @@ def main():
                     help="backward-input and backward-filter as separate operators")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
+    ap.add_argument("--e2e-chunk", type=int, default=None,
+                    help="images per chunk in the host-buffer leg (default: HostMapsStep's choice)")
+    ap.add_argument("--e2e-depth", type=int, default=2,
+                    help="steps in flight at a time in the host-buffer leg (HostMapsPipeline depth)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the stack and strong-scaling legs (profiling)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)

@@ -54,3 +54,35 @@ def test_host_step_rejects_pageable_and_wrong_shape():
     step.run(x, w, dy, y, dx, dw)
     step.synchronize()
     assert float(y.abs().max()) == 0.0
+
+
+def test_host_pipeline_overlaps_steps_and_keeps_their_results_apart():
+    """HostMapsPipeline: consecutive steps on alternating HostMapsStep objects and streams.  Six
+    steps with different inputs, two in flight at a time, each with its own host buffers: every
+    step's results equal the one-call path's on that step's inputs."""
+    shape, k, s, p, dtype = (12, 16, 28, 28), 3, 1, 1, torch.float32
+    N, C, H, W = shape
+    pipe = dwconv_b200.HostMapsPipeline(shape, k, s, p, depth=2, dtype=dtype, device="cuda:0",
+                                        chunk_images=4)
+    g = torch.Generator().manual_seed(11)
+    steps = []
+    for i in range(6):
+        x = torch.randn(shape, generator=g).pin_memory()
+        w = (torch.randn((C, 1, k, k), generator=g) / k).pin_memory()
+        dy = torch.randn(pipe.y_shape, generator=g).pin_memory()
+        outs = [torch.full(pipe.y_shape, float("nan")).pin_memory(),
+                torch.full(shape, float("nan")).pin_memory(),
+                torch.full((C, 1, k, k), float("nan")).pin_memory()]
+        steps.append((x, w, dy, outs))
+    events = [pipe.run(x, w, dy, *outs) for x, w, dy, outs in steps]
+    for ev, (x, w, dy, (y, dx, dw)) in zip(events, steps):
+        pipe.wait(ev)
+        xd, wd = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+        yd = dwconv_b200.depthwise_conv2d(xd, wd, None, s, p)
+        yd.backward(dy.cuda())
+        assert torch.equal(y, yd.detach().cpu())
+        assert torch.equal(dx, xd.grad.cpu())
+        ref = wd.grad.double().cpu()
+        assert (dw.double() - ref).abs().max().item() <= 1e-4 * max(1.0, ref.abs().max().item())
+    pipe.synchronize()
+    assert dwconv_b200._lib.lib.dwconv_b200_device_status() == 0
