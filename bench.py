@@ -84,7 +84,7 @@ DESCR = {
 }
 # strong scaling (fixed global batch, divided over the ranks): workload -> global batch
 STRONG = {"c4a": 64, "c5k3": 256}
-ESIZE = {"f32": 4, "f16": 2, "f64": 8}
+ESIZE = {"f32": 4, "f16": 2, "bf16": 2, "f64": 8}
 METRIC = "dwconv_fwd_bwd_achieved_hbm_gbps"
 UNIT = "GB/s"
 L2_BYTES = 126e6
@@ -826,7 +826,7 @@ def time_api(layers, reps):
     import torch
     import dwconv_b200
     from dwconv_b200 import _lib
-    dts = {"f32": torch.float32, "f16": torch.float16}
+    dts = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
     res = []
     for layer in layers:
         layer = list(layer)
@@ -853,7 +853,7 @@ def time_api(layers, reps):
 
         # the three operators through the C entry points (no Python layer, no allocation)
         shape = _lib.Shape(N, C, H, W, k, k, s, s, p, p, ho, wo)
-        code = {"f32": _lib.F32, "f16": _lib.F16}[dt]
+        code = {"f32": _lib.F32, "f16": _lib.F16, "bf16": _lib.BF16}[dt]
         L = _lib.lib
         ys = [torch.empty_like(t[2]) for t in sets]
         dxs = [torch.empty_like(t[0]) for t in sets]

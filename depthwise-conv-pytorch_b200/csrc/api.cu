@@ -16,8 +16,8 @@ using namespace dwb;
 
 namespace {
 
-// The rows family is compiled for fp32 and fp16; everything else runs on the direct family.
-template <typename T> constexpr bool kRowsCompiled = !std::is_same<T, __nv_bfloat16>::value;
+// The rows family is compiled for fp32, fp16 and bf16; fp64 declines there and runs on the direct family.
+template <typename T> constexpr bool kRowsCompiled = true;  // every type is instantiated (fp64 declines)
 
 std::atomic<int> g_forced_path{DWCONV_B200_PATH_AUTO};
 thread_local int t_last_path = DWCONV_B200_PATH_AUTO;

@@ -26,7 +26,7 @@ template <> struct Elem<__half> {
   static __device__ __forceinline__ float to_acc(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_acc(float v) { return __float2half_rn(v); }
 };
-template <> struct Elem<__nv_bfloat16> {  // served by the direct family only
+template <> struct Elem<__nv_bfloat16> {  // not a reference dtype; fp32 accumulation, every family
   using acc_t = float;
   static __device__ __forceinline__ float ld(const __nv_bfloat16 *p) { return __bfloat162float(__ldg(p)); }
   static __device__ __forceinline__ float to_acc(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -56,6 +56,36 @@ __device__ __forceinline__ float fma_mix(__nv_bfloat16 a, __nv_bfloat16 b, float
       : "h"(__bfloat16_as_ushort(a)), "h"(__bfloat16_as_ushort(b)), "f"(acc));
   return d;
 }
+
+// Two 16-bit elements in one 32-bit word, and single elements as bit patterns: what the vector
+// loads and stores of the 16-bit kernels need, for fp16 and bf16 alike.
+template <typename T> struct Pack16;
+template <> struct Pack16<__half> {
+  static __device__ __forceinline__ float2 unpack(uint32_t r) {
+    return __half22float2(*reinterpret_cast<const __half2 *>(&r));
+  }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __half2 h = __halves2half2(__float2half_rn(a), __float2half_rn(b));
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+  static __device__ __forceinline__ float from_bits(unsigned short h) { return __half2float(__ushort_as_half(h)); }
+  static __device__ __forceinline__ unsigned short to_bits(float v) { return __half_as_ushort(__float2half_rn(v)); }
+};
+template <> struct Pack16<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 unpack(uint32_t r) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&r));
+  }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __nv_bfloat162 h = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+  static __device__ __forceinline__ float from_bits(unsigned short h) {
+    return __bfloat162float(__ushort_as_bfloat16(h));
+  }
+  static __device__ __forceinline__ unsigned short to_bits(float v) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  }
+};
 
 // One fused multiply-add, never split by the compiler.
 __device__ __forceinline__ float fma_acc(float a, float b, float c) { return fmaf(a, b, c); }

@@ -105,14 +105,10 @@ template <int W> struct RowIO<float, W> {
     }
   }
 };
-template <int W> struct RowIO<__half, W> {
-  static __device__ __forceinline__ float2 unpack(uint32_t r) {
-    return __half22float2(*reinterpret_cast<const __half2 *>(&r));
-  }
-  static __device__ __forceinline__ uint32_t pack(float a, float b) {
-    __half2 h = __halves2half2(__float2half_rn(a), __float2half_rn(b));
-    return *reinterpret_cast<uint32_t *>(&h);
-  }
+// 16-bit types (fp16, bf16), converted through Pack16<T>.
+template <typename T, int W> struct RowIO16 {
+  static __device__ __forceinline__ float2 unpack(uint32_t r) { return Pack16<T>::unpack(r); }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) { return Pack16<T>::pack(a, b); }
   static __device__ __forceinline__ void ld(uint32_t a, float (&v)[W]) {
     if constexpr (W % 4 == 0) {  // rows of a multiple of 8 bytes
 #pragma unroll
@@ -135,7 +131,7 @@ template <int W> struct RowIO<__half, W> {
       for (int i = 0; i < W; ++i) {
         unsigned short h;
         asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(a + 2u * i));
-        v[i] = __half2float(__ushort_as_half(h));
+        v[i] = Pack16<T>::from_bits(h);
       }
     }
   }
@@ -153,11 +149,14 @@ template <int W> struct RowIO<__half, W> {
     } else {
 #pragma unroll
       for (int i = 0; i < W; ++i)
-        asm volatile("st.shared.u16 [%0], %1;" ::"r"(a + 2u * i), "h"(__half_as_ushort(__float2half_rn(v[i])))
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(a + 2u * i), "h"(Pack16<T>::to_bits(v[i]))
                      : "memory");
     }
   }
 };
+
+template <int W> struct RowIO<__half, W> : RowIO16<__half, W> {};
+template <int W> struct RowIO<__nv_bfloat16, W> : RowIO16<__nv_bfloat16, W> {};
 
 template <typename T, int K, int W, int MINB>
 __global__ void __launch_bounds__(ROWS_THREADS, MINB)

@@ -200,6 +200,7 @@ int launch_backward(const BackwardPlan &f, cudaStream_t st) {
 template <typename T> struct RowsDtype { static constexpr bool ok = false; };
 template <> struct RowsDtype<float> { static constexpr bool ok = true; };
 template <> struct RowsDtype<__half> { static constexpr bool ok = true; };
+template <> struct RowsDtype<__nv_bfloat16> { static constexpr bool ok = true; };
 
 // ---- small maps: a lane owns a row (lanerow_backward.cuh) ----
 // Stride 1, padding k/2, maps 7, 14 or 28 columns wide and at most 32 rows high; fp32 and fp16.
@@ -357,9 +358,11 @@ int rows_backward_take_error() {
 
 template int rows_backward_slices<float>(const Shape &);
 template int rows_backward_slices<__half>(const Shape &);
+template int rows_backward_slices<__nv_bfloat16>(const Shape &);
 template int rows_backward_slices<double>(const Shape &);
 template int rows_backward<float>(const float *, const float *, const float *, float *, float *, const Shape &, cudaStream_t, int *, float *);
 template int rows_backward<__half>(const __half *, const __half *, const __half *, __half *, float *, const Shape &, cudaStream_t, int *, __half *);
+template int rows_backward<__nv_bfloat16>(const __nv_bfloat16 *, const __nv_bfloat16 *, const __nv_bfloat16 *, __nv_bfloat16 *, float *, const Shape &, cudaStream_t, int *, __nv_bfloat16 *);
 template int rows_backward<double>(const double *, const double *, const double *, double *, double *, const Shape &, cudaStream_t, int *, double *);
 
 // Tiling the fused backward pass would use, for inspection (same layout as the other plans).

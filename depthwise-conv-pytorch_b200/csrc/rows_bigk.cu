@@ -177,9 +177,12 @@ int rows_bigk_take_error() {
 
 template int rows_bigk_filter_slices<float>(const Shape &);
 template int rows_bigk_filter_slices<__half>(const Shape &);
+template int rows_bigk_filter_slices<__nv_bfloat16>(const Shape &);
 template int rows_bigk_filter<float>(const float *, const float *, float *, const Shape &, cudaStream_t, int *);
 template int rows_bigk_filter<__half>(const __half *, const __half *, float *, const Shape &, cudaStream_t, int *);
+template int rows_bigk_filter<__nv_bfloat16>(const __nv_bfloat16 *, const __nv_bfloat16 *, float *, const Shape &, cudaStream_t, int *);
 template int rows_bigk_conv<float>(const RowsParams &, int, cudaStream_t);
 template int rows_bigk_conv<__half>(const RowsParams &, int, cudaStream_t);
+template int rows_bigk_conv<__nv_bfloat16>(const RowsParams &, int, cudaStream_t);
 
 }  // namespace dwb

@@ -69,9 +69,11 @@ int rows_conv_take_error() {
 
 template int rows_forward<float>(const float *, const float *, float *, const Shape &, cudaStream_t);
 template int rows_forward<__half>(const __half *, const __half *, __half *, const Shape &, cudaStream_t);
+template int rows_forward<__nv_bfloat16>(const __nv_bfloat16 *, const __nv_bfloat16 *, __nv_bfloat16 *, const Shape &, cudaStream_t);
 template int rows_forward<double>(const double *, const double *, double *, const Shape &, cudaStream_t);
 template int rows_backward_input<float>(const float *, const float *, float *, const Shape &, cudaStream_t);
 template int rows_backward_input<__half>(const __half *, const __half *, __half *, const Shape &, cudaStream_t);
+template int rows_backward_input<__nv_bfloat16>(const __nv_bfloat16 *, const __nv_bfloat16 *, __nv_bfloat16 *, const Shape &, cudaStream_t);
 template int rows_backward_input<double>(const double *, const double *, double *, const Shape &, cudaStream_t);
 
 }  // namespace dwb

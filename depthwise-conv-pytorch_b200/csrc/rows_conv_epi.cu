@@ -25,6 +25,7 @@ int rows_conv_epi_take_error() { return conv_take_error_here(); }
 
 template int rows_forward_epilogue<float>(const float *, const float *, float *, const Shape &, const EpilogueArgs &, cudaStream_t);
 template int rows_forward_epilogue<__half>(const __half *, const __half *, __half *, const Shape &, const EpilogueArgs &, cudaStream_t);
+template int rows_forward_epilogue<__nv_bfloat16>(const __nv_bfloat16 *, const __nv_bfloat16 *, __nv_bfloat16 *, const Shape &, const EpilogueArgs &, cudaStream_t);
 template int rows_forward_epilogue<double>(const double *, const double *, double *, const Shape &, const EpilogueArgs &, cudaStream_t);
 
 }  // namespace dwb

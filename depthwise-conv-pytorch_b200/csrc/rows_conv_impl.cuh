@@ -20,6 +20,7 @@ thread_local int *t_plan_out = nullptr;
 template <typename T> struct RowsDtype { static constexpr bool ok = false; };
 template <> struct RowsDtype<float> { static constexpr bool ok = true; };
 template <> struct RowsDtype<__half> { static constexpr bool ok = true; };
+template <> struct RowsDtype<__nv_bfloat16> { static constexpr bool ok = true; };
 
 constexpr int conv_minb(int K) { return K <= 5 ? 2 : 1; }  // 49 tap registers: one CTA per SM
 

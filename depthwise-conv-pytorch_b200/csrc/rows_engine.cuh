@@ -236,30 +236,34 @@ template <> struct SmemLd<float, 4> {
                  : "r"(a));
   }
 };
-template <> struct SmemLd<__half, 1> {
+// 16-bit types (fp16, bf16): the same loads, converted through Pack16<T>.
+template <typename T, int V> struct SmemLd16;
+template <typename T> struct SmemLd16<T, 1> {
   static __device__ __forceinline__ void ld(uint32_t a, float (&v)[1]) {
     unsigned short h;
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(a));
-    v[0] = __half2float(__ushort_as_half(h));
+    v[0] = Pack16<T>::from_bits(h);
   }
 };
-template <> struct SmemLd<__half, 2> {
+template <typename T> struct SmemLd16<T, 2> {
   static __device__ __forceinline__ void ld(uint32_t a, float (&v)[2]) {
     uint32_t r;
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(r) : "r"(a));
-    const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(&r));
+    const float2 t = Pack16<T>::unpack(r);
     v[0] = t.x; v[1] = t.y;
   }
 };
-template <> struct SmemLd<__half, 4> {
+template <typename T> struct SmemLd16<T, 4> {
   static __device__ __forceinline__ void ld(uint32_t a, float (&v)[4]) {
     uint32_t r0, r1;
     asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(a));
-    const float2 x = __half22float2(*reinterpret_cast<const __half2 *>(&r0));
-    const float2 y = __half22float2(*reinterpret_cast<const __half2 *>(&r1));
+    const float2 x = Pack16<T>::unpack(r0);
+    const float2 y = Pack16<T>::unpack(r1);
     v[0] = x.x; v[1] = x.y; v[2] = y.x; v[3] = y.y;
   }
 };
+template <int V> struct SmemLd<__half, V> : SmemLd16<__half, V> {};
+template <int V> struct SmemLd<__nv_bfloat16, V> : SmemLd16<__nv_bfloat16, V> {};
 
 // V fp32 registers to global memory as one vector store of T.  The stores are streaming
 // (evict-first): an output map is not read again by the kernel that writes it, and keeping it from
@@ -278,27 +282,27 @@ template <> struct GmemSt<float, 4> {
     __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
   }
 };
-template <> struct GmemSt<__half, 1> {
-  static __device__ __forceinline__ void st(__half *p, const float (&v)[1]) {
-    __stcs(reinterpret_cast<unsigned short *>(p), __half_as_ushort(__float2half_rn(v[0])));
+template <typename T, int V> struct GmemSt16;
+template <typename T> struct GmemSt16<T, 1> {
+  static __device__ __forceinline__ void st(T *p, const float (&v)[1]) {
+    __stcs(reinterpret_cast<unsigned short *>(p), Pack16<T>::to_bits(v[0]));
   }
 };
-template <> struct GmemSt<__half, 2> {
-  static __device__ __forceinline__ void st(__half *p, const float (&v)[2]) {
-    __half2 a = __halves2half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
-    __stcs(reinterpret_cast<unsigned int *>(p), *reinterpret_cast<unsigned int *>(&a));
+template <typename T> struct GmemSt16<T, 2> {
+  static __device__ __forceinline__ void st(T *p, const float (&v)[2]) {
+    __stcs(reinterpret_cast<unsigned int *>(p), Pack16<T>::pack(v[0], v[1]));
   }
 };
-template <> struct GmemSt<__half, 4> {
-  static __device__ __forceinline__ void st(__half *p, const float (&v)[4]) {
-    __half2 a = __halves2half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
-    __half2 b = __halves2half2(__float2half_rn(v[2]), __float2half_rn(v[3]));
+template <typename T> struct GmemSt16<T, 4> {
+  static __device__ __forceinline__ void st(T *p, const float (&v)[4]) {
     uint2 raw;
-    raw.x = *reinterpret_cast<uint32_t *>(&a);
-    raw.y = *reinterpret_cast<uint32_t *>(&b);
+    raw.x = Pack16<T>::pack(v[0], v[1]);
+    raw.y = Pack16<T>::pack(v[2], v[3]);
     __stcs(reinterpret_cast<uint2 *>(p), raw);
   }
 };
+template <int V> struct GmemSt<__half, V> : GmemSt16<__half, V> {};
+template <int V> struct GmemSt<__nv_bfloat16, V> : GmemSt16<__nv_bfloat16, V> {};
 
 // Shared-memory bookkeeping: stages, then full[], empty[] barriers, the abort flag and a
 // scratch area for cross-warp sums.

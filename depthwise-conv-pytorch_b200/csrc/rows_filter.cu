@@ -180,6 +180,7 @@ int launch_filter(const FilterPlan &f, cudaStream_t st) {
 template <typename T> struct RowsDtype { static constexpr bool ok = false; };
 template <> struct RowsDtype<float> { static constexpr bool ok = true; };
 template <> struct RowsDtype<__half> { static constexpr bool ok = true; };
+template <> struct RowsDtype<__nv_bfloat16> { static constexpr bool ok = true; };
 
 }  // namespace
 
@@ -240,9 +241,11 @@ int rows_take_device_error() {
 
 template int rows_backward_filter_slices<float>(const Shape &);
 template int rows_backward_filter_slices<__half>(const Shape &);
+template int rows_backward_filter_slices<__nv_bfloat16>(const Shape &);
 template int rows_backward_filter_slices<double>(const Shape &);
 template int rows_backward_filter<float>(const float *, const float *, float *, const Shape &, cudaStream_t, int *);
 template int rows_backward_filter<__half>(const __half *, const __half *, float *, const Shape &, cudaStream_t, int *);
+template int rows_backward_filter<__nv_bfloat16>(const __nv_bfloat16 *, const __nv_bfloat16 *, float *, const Shape &, cudaStream_t, int *);
 template int rows_backward_filter<double>(const double *, const double *, double *, const Shape &, cudaStream_t, int *);
 
 // Tiling the backward-filter first pass would use, for inspection: the test-suite models the
