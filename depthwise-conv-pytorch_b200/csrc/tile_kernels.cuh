@@ -206,11 +206,17 @@ tile_conv_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restric
     float tap[K][K];
     {
       const T *tp = w + (size_t)chan * KK;
+      if (p.flip) {  // (two copies of the loop: constant offsets in each, no select per tap)
 #pragma unroll
-      for (int ky = 0; ky < K; ++ky)
+        for (int ky = 0; ky < K; ++ky)
 #pragma unroll
-        for (int kx = 0; kx < K; ++kx)
-          tap[ky][kx] = Elem<T>::ld(tp + (p.flip ? KK - 1 - (ky * K + kx) : ky * K + kx));
+          for (int kx = 0; kx < K; ++kx) tap[ky][kx] = Elem<T>::ld(tp + (KK - 1 - (ky * K + kx)));
+      } else {
+#pragma unroll
+        for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) tap[ky][kx] = Elem<T>::ld(tp + (ky * K + kx));
+      }
     }
     __syncthreads();
     float acc[TILE_R];

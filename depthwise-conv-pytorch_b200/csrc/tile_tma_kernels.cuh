@@ -91,11 +91,17 @@ tile_tma_conv_kernel(const __grid_constant__ CUtensorMap in_map, const T *__rest
     T tap[K][K];  // taps and staged values stay in the storage type: fma_mix multiplies them as they are
     {
       const T *tp = w + (size_t)chan * KK;
+      if (p.flip) {  // (two copies of the loop: constant offsets in each, no select per tap)
 #pragma unroll
-      for (int ky = 0; ky < K; ++ky)
+        for (int ky = 0; ky < K; ++ky)
 #pragma unroll
-        for (int kx = 0; kx < K; ++kx)
-          tap[ky][kx] = __ldg(tp + (p.flip ? KK - 1 - (ky * K + kx) : ky * K + kx));
+          for (int kx = 0; kx < K; ++kx) tap[ky][kx] = __ldg(tp + (KK - 1 - (ky * K + kx)));
+      } else {
+#pragma unroll
+        for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) tap[ky][kx] = __ldg(tp + (ky * K + kx));
+      }
     }
     if (!gave_up) {
       if (mbar_wait_bounded(&full[s], (it >> 1) & 1)) {
