@@ -90,3 +90,55 @@ def test_channels_last_outside_the_nhwc_kernels_is_copied():
     s = make_shape((2, 8, 12, 12), (3, 5), 1, (1, 2))
     assert _lib.lib.dwconv_b200_forward_nhwc(xl.data_ptr(), w.data_ptr(), y.data_ptr(), _lib.F32, s, None,
                                              None) == 6
+
+
+@pytest.mark.parametrize("layout", ["nhwc", "wide_nchw"])
+def test_tensor_copy_kernels_replay_in_a_cuda_graph(layout):
+    """The kernels whose tiles arrive by tensor copies take their tensor maps as launch
+    arguments, so a captured launch keeps them: after one eager call (one-time set-up), forward
+    and both gradients are captured into a CUDA graph and replayed on new values in the same
+    buffers; results equal the eager ones bit for bit."""
+    if layout == "nhwc":
+        N, C, H, W, k, s, p = 6, 64, 28, 28, 3, 1, 1
+    else:
+        N, C, H, W, k, s, p = 2, 8, 40, 160, 5, 1, 2   # wider than 128 columns: the tile kernels
+    dt = torch.float32
+    x, w, dy = seeded((N, C, H, W), (k, k), s, p, dt, seed=21)
+    sh = make_shape((N, C, H, W), (k, k), s, p)
+    fmt = torch.channels_last if layout == "nhwc" else torch.contiguous_format
+    xs, dys = x.contiguous(memory_format=fmt), dy.contiguous(memory_format=fmt)
+    y, dx, dw = torch.empty_like(dys), torch.empty_like(xs), torch.empty_like(w)
+    L = _lib.lib
+    nbytes = L.dwconv_b200_backward_filter_workspace_bytes(CODE[dt], sh)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+
+    def ops(st):
+        if layout == "nhwc":
+            a = L.dwconv_b200_forward_nhwc(xs.data_ptr(), w.data_ptr(), y.data_ptr(), CODE[dt], sh, None, st)
+            b = L.dwconv_b200_backward_input_nhwc(dys.data_ptr(), w.data_ptr(), dx.data_ptr(), CODE[dt], sh, st)
+            c = L.dwconv_b200_backward_filter_nhwc(xs.data_ptr(), dys.data_ptr(), dw.data_ptr(), ws.data_ptr(),
+                                                   nbytes, CODE[dt], sh, st)
+        else:
+            a = L.dwconv_b200_forward(xs.data_ptr(), w.data_ptr(), y.data_ptr(), CODE[dt], sh, st)
+            b = L.dwconv_b200_backward_input(dys.data_ptr(), w.data_ptr(), dx.data_ptr(), CODE[dt], sh, st)
+            c = L.dwconv_b200_backward_filter(xs.data_ptr(), dys.data_ptr(), dw.data_ptr(), ws.data_ptr(),
+                                              nbytes, CODE[dt], sh, st)
+        assert (a, b, c) == (0, 0, 0)
+
+    ops(torch.cuda.current_stream().cuda_stream)   # eager: one-time set-up of every kernel
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        ops(torch.cuda.current_stream().cuda_stream)
+    for seed in (31, 32):
+        x2, _, dy2 = seeded((N, C, H, W), (k, k), s, p, dt, seed=seed)
+        xs.copy_(x2.contiguous(memory_format=fmt))
+        dys.copy_(dy2.contiguous(memory_format=fmt))
+        y.fill_(float("nan")); dx.fill_(float("nan")); dw.fill_(float("nan"))
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y.cpu(), oracle.forward_seq(x2, w, s, p))
+        assert torch.equal(dx.cpu(), oracle.backward_input_seq(dy2, w, (H, W), s, p))
+        assert_dw_close(dw, oracle.backward_filter(x2, dy2, (k, k), s, p), dt, "replayed dW")
+    assert L.dwconv_b200_device_status() == 0
