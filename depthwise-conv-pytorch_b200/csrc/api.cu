@@ -736,6 +736,29 @@ int nhwc_call_t(int op, const void *a, const void *b, void *c, void *ws, size_t 
   return launch_status();
 }
 
+// Both gradients on channels-last maps: one pass over dy where the fused kernel serves the
+// geometry, the two operators otherwise.
+template <typename T>
+int nhwc_backward_t(const void *x, const void *dy, const void *w, void *dx, void *dw, void *ws,
+                    size_t ws_bytes, const Shape &s, cudaStream_t st) {
+  using A = typename Elem<T>::acc_t;
+  if (ws_bytes < filter_workspace_t<T>(s)) return DWCONV_B200_WORKSPACE_TOO_SMALL;
+  int S = 0;
+  if (nhwc_backward<T>((const T *)x, (const T *)dy, (const T *)w, (T *)dx, (A *)ws, s, st, &S) == ROWS_SERVED) {
+    int e = launch_status();
+    if (e != DWCONV_B200_OK) return e;
+    const int kk = s.kh * s.kw;
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t cfg = finalize_config(finalize_blocks(s.C, kk), st, attr);
+    (void)cudaLaunchKernelEx(&cfg, backward_filter_finalize_kernel<T>, (const A *)ws, (T *)dw, s.C, kk, S);
+    return launch_status();
+  }
+  const EpilogueArgs none{nullptr, nullptr, 0, 0};
+  int e = nhwc_call_t<T>(1, dy, w, dx, nullptr, 0, s, none, st);
+  if (e != DWCONV_B200_OK) return e;
+  return nhwc_call_t<T>(2, x, dy, dw, ws, ws_bytes, s, none, st);
+}
+
 int nhwc_call(int op, const void *a, const void *b, void *c, void *ws, size_t ws_bytes, int dtype,
               const dwconv_b200_shape *shape, const EpilogueArgs &ep, void *stream) {
   int e = check_ptrs(dtype, a, b, c);
@@ -784,6 +807,28 @@ int dwconv_b200_backward_filter_nhwc(const void *x, const void *dy, void *dw, vo
                                      const dwconv_b200_shape *shape, void *stream) {
   return nhwc_call(2, x, dy, dw, workspace, workspace_bytes, dtype, shape,
                    EpilogueArgs{nullptr, nullptr, 0, 0}, stream);
+}
+
+int dwconv_b200_backward_nhwc(const void *x, const void *dy, const void *w, void *dx, void *dw,
+                              void *workspace, size_t workspace_bytes, int dtype,
+                              const dwconv_b200_shape *shape, void *stream) {
+  int e = check_ptrs(dtype, x, dy, w);
+  if (e) return e;
+  e = check_ptrs(dtype, dx, dw, workspace);
+  if (e) return e;
+  e = check_shape(shape);
+  if (e) return e;
+  if (!aligned_to(workspace, 16)) return DWCONV_B200_MISALIGNED;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case DWCONV_B200_F32:
+      return nhwc_backward_t<float>(x, dy, w, dx, dw, workspace, workspace_bytes, *shape, st);
+    case DWCONV_B200_F16:
+      return nhwc_backward_t<__half>(x, dy, w, dx, dw, workspace, workspace_bytes, *shape, st);
+    case DWCONV_B200_BF16:
+      return nhwc_backward_t<__nv_bfloat16>(x, dy, w, dx, dw, workspace, workspace_bytes, *shape, st);
+    default: return DWCONV_B200_UNSUPPORTED_SHAPE;  // fp64: make the maps contiguous NCHW
+  }
 }
 
 int dwconv_b200_use_dwconv2d_small(int in_h, int in_w, int kh, int kw, int up_h, int up_w,

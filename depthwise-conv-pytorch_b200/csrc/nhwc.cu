@@ -10,6 +10,9 @@ int nhwc_tma_conv(const T *in, const T *w, T *out, const NhwcParams &p, int K, i
 template <typename T>
 int nhwc_tma_bwd2(const T *dy, const T *w, T *dx, const NhwcParams &p, int K, cudaStream_t st);
 template <typename T>
+int nhwc_tma_backward(const T *x, const T *dy, const T *w, T *dx, float *partial, const NhwcFilterParams &p,
+                      int K, cudaStream_t st);
+template <typename T>
 int nhwc_tma_filter(const T *x, const T *dy, float *partial, const NhwcFilterParams &p, int K, int S,
                     cudaStream_t st);
 
@@ -136,12 +139,31 @@ int nhwc_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *parti
   }
 }
 
+// dx and the first pass of the filter gradient from one pass over dy (stride 1, 3x3 / 5x5, tensors
+// the copy engine can address); ROWS_DECLINED otherwise: the caller runs the two operators.
+template <typename T>
+int nhwc_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<T>::acc_t *partial,
+                  const Shape &s, cudaStream_t st, int *slices_out) {
+  if constexpr (!NhwcDtype<T>::ok) {
+    return ROWS_DECLINED;
+  } else {
+    if (!nhwc_filter_ok(s) || s.sh != 1 || s.ph > s.kh - 1 || s.pw > s.kw - 1) return ROWS_DECLINED;
+    NhwcFilterParams p{};
+    p.N = s.N; p.C = s.C; p.H = s.H; p.W = s.W; p.Ho = s.Ho; p.Wo = s.Wo;
+    p.pt = s.kh - 1 - s.ph; p.pl = s.kw - 1 - s.pw; p.SL = nhwc_filter_slices(s);
+    *slices_out = p.SL;
+    return nhwc_tma_backward<T>(x, dy, w, dx, partial, p, s.kh, st);
+  }
+}
+
 #define DWB_NHWC_INSTANTIATE(T)                                                                   \
   template int nhwc_forward<T>(const T *, const T *, T *, const Shape &, const EpilogueArgs &,    \
                                cudaStream_t);                                                      \
   template int nhwc_backward_input<T>(const T *, const T *, T *, const Shape &, cudaStream_t);     \
   template int nhwc_backward_filter<T>(const T *, const T *, typename Elem<T>::acc_t *,            \
-                                       const Shape &, cudaStream_t, int *);
+                                       const Shape &, cudaStream_t, int *);                        \
+  template int nhwc_backward<T>(const T *, const T *, const T *, T *, typename Elem<T>::acc_t *,   \
+                                const Shape &, cudaStream_t, int *);
 DWB_NHWC_INSTANTIATE(float)
 DWB_NHWC_INSTANTIATE(__half)
 DWB_NHWC_INSTANTIATE(__nv_bfloat16)

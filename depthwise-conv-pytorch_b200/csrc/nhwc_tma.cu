@@ -122,7 +122,41 @@ int launch_filter(const T *x, const T *dy, float *partial, NhwcFilterParams p, c
   return ROWS_SERVED;
 }
 
+template <typename T, int K>
+int launch_backward(const T *x, const T *dy, const T *w, T *dx, float *partial, NhwcFilterParams p,
+                    cudaStream_t st) {
+  using G = NhwcGeo<K, 1, true>;
+  using TG = NhwcTmaGeo<T, K, 1, true>;
+  int *flag = error_flag_ptr();
+  if (flag == nullptr) return ROWS_DECLINED;
+  if (prepare<nhwc_tma_backward_kernel<T, K>>(G::THREADS, TG::SMEM_BYTES) < 1) return ROWS_DECLINED;
+  alignas(64) CUtensorMap dy_map, x_map;
+  if (!encode_nhwc<T>(&dy_map, dy, p.C, p.Wo, p.Ho, p.N, G::IW, G::IH)) return ROWS_DECLINED;
+  if (!encode_nhwc<T>(&x_map, x, p.C, p.W, p.H, p.N, G::TW, G::R)) return ROWS_DECLINED;
+  p.tiles_x = ceil_div(p.W, G::TW);  // tiles of the x / dx map
+  p.tiles_y = ceil_div(p.H, G::R);
+  p.cblocks = ceil_div(p.C, NHWC_CB);
+  nhwc_tma_backward_kernel<T, K><<<p.cblocks * p.SL, G::THREADS, TG::SMEM_BYTES, st>>>(dy_map, x_map, w, dx,
+                                                                                       partial, p, flag);
+  return ROWS_SERVED;
+}
+
 }  // namespace
+
+// dx and the first pass of the filter gradient at stride 1 from one pass over dy; p: H x W = x,
+// Ho x Wo = dy, pt / pl = k-1-padding, SL slices per channel block.
+template <typename T>
+int nhwc_tma_backward(const T *x, const T *dy, const T *w, T *dx, float *partial, const NhwcFilterParams &p,
+                      int K, cudaStream_t st) {
+  if (!tensor_ok(x, p.C, p.W, p.H) || !tensor_ok(dy, p.C, p.Wo, p.Ho) ||
+      (reinterpret_cast<uintptr_t>(dx) & 15) != 0)
+    return ROWS_DECLINED;
+  switch (K) {
+    case 3: return launch_backward<T, 3>(x, dy, w, dx, partial, p, st);
+    case 5: return launch_backward<T, 5>(x, dy, w, dx, partial, p, st);
+    default: return ROWS_DECLINED;
+  }
+}
 
 // Forward (stride 1 or 2) or stride-1 backward-input on channels-last maps; ROWS_DECLINED when
 // the tensors do not meet the copy engine's rules or the driver offers no encoder.
@@ -170,6 +204,8 @@ int nhwc_tma_filter(const T *x, const T *dy, float *partial, const NhwcFilterPar
 
 #define DWB_NHWC_TMA_INSTANTIATE(T)                                                               \
   template int nhwc_tma_conv<T>(const T *, const T *, T *, const NhwcParams &, int, int, cudaStream_t); \
+  template int nhwc_tma_backward<T>(const T *, const T *, const T *, T *, float *, const NhwcFilterParams &, \
+                                    int, cudaStream_t);                                                  \
   template int nhwc_tma_bwd2<T>(const T *, const T *, T *, const NhwcParams &, int, cudaStream_t);      \
   template int nhwc_tma_filter<T>(const T *, const T *, float *, const NhwcFilterParams &, int, int,    \
                                   cudaStream_t);

@@ -413,4 +413,153 @@ nhwc_tma_filter_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_c
   }
 }
 
+// Both gradients at stride 1 from ONE pass over dy (the channels-last counterpart of the fused
+// backward of rows_backward.cuh).  A step is a tile of R x TW positions of x / dx for 32 channels;
+// it needs the dy box around it (halo k-1: the box backward-input reads) and the plain x box.
+// Thread (channel, column) walks the dy box rows once; a value v = dy[r][col + kx] serves
+//   dx[o]       += v * w[K-1-ky][K-1-kx]      (ky = r - o: backward-input, same order, same bits)
+//   dW'[ky][kx] += x[o] * v                   (the gradient of tap (K-1-ky, K-1-kx))
+// Block (channel block, slice) walks its share of the (image, tile) list as the filter kernel does
+// and reduces dW' over its columns at the end.  p: H x W = x / dx, Ho x Wo = dy, pt / pl =
+// k-1-padding.
+template <typename T, int K>
+__global__ void __launch_bounds__(NhwcGeo<K, 1, true>::THREADS, K == 3 ? 2 : 1)
+nhwc_tma_backward_kernel(const __grid_constant__ CUtensorMap dy_map, const __grid_constant__ CUtensorMap x_map,
+                         const T *__restrict__ w, T *__restrict__ dx, float *__restrict__ partial,
+                         const NhwcFilterParams p, int *error_flag) {
+  using G = NhwcGeo<K, 1, true>;
+  using TG = NhwcTmaGeo<T, K, 1, true>;  // "X" slot: the box with halo (dy here); "DY" slot: the plain box (x here)
+  constexpr int KK = K * K;
+  static_assert(TG::STAGE_BYTES >= G::TW * K * NHWC_CB * (int)sizeof(float),
+                "a stage doubles as the reduction buffer");
+  extern __shared__ __align__(128) unsigned char nhwc_smem[];
+  uint64_t *full = reinterpret_cast<uint64_t *>(nhwc_smem + 2 * TG::STAGE_BYTES);
+  pdl_launch_dependents();  // the second pass may take its place on the SMs early
+  const int lane = threadIdx.x & 31, col = threadIdx.x >> 5;
+  const int cb = blockIdx.x / p.SL;
+  const int slice = blockIdx.x - cb * p.SL;
+  const int c0 = cb * NHWC_CB, c = c0 + lane;
+  const int per_img = p.tiles_y * p.tiles_x;
+  const long long total = (long long)p.N * per_img;
+  const long long t_begin = slice * total / p.SL, t_end = (slice + 1) * total / p.SL;
+  const int steps = (int)(t_end - t_begin);
+  if (threadIdx.x == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  // thread 0: the next tile to ask for; all threads: the tile being worked on (for the dx stores)
+  int an = (int)(t_begin / per_img);
+  int aty = (int)(t_begin - (long long)an * per_img) / p.tiles_x;
+  int atx = (int)(t_begin - (long long)an * per_img) - aty * p.tiles_x;
+  int n = an, ty = aty, tx = atx;
+  int asked = 0, landed0 = 0, landed1 = 0;
+  auto ask = [&](int s) {
+    const int y0 = aty * G::R, x0 = atx * G::TW;
+    unsigned char *stage = nhwc_smem + s * TG::STAGE_BYTES;
+    mbar_arrive_expect_tx(&full[s], TG::X_BYTES + TG::DY_BYTES);
+    tma_load_4d(stage, &dy_map, c0, x0 - p.pl, y0 - p.pt, an, &full[s]);
+    tma_load_4d(stage + TG::X_SLOT, &x_map, c0, x0, y0, an, &full[s]);
+    ++asked;
+    if (++atx == p.tiles_x) {
+      atx = 0;
+      if (++aty == p.tiles_y) { aty = 0; ++an; }
+    }
+  };
+  if (threadIdx.x == 0) {
+    if (steps > 0) ask(0);
+    if (steps > 1) ask(1);
+  }
+  T tapf[K][K];  // the flipped filter
+#pragma unroll
+  for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+    for (int kx = 0; kx < K; ++kx)
+      tapf[ky][kx] = c < p.C ? __ldg(w + (size_t)c * KK + (KK - 1 - (ky * K + kx))) : Elem<T>::from_acc(0.f);
+  float acc[K][K];
+#pragma unroll
+  for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+    for (int kx = 0; kx < K; ++kx) acc[ky][kx] = 0.f;
+  bool gave_up = false;
+  for (int it = 0; it < steps; ++it) {
+    const int s = it & 1;
+    if (!gave_up) {
+      if (mbar_wait_bounded(&full[s], (it >> 1) & 1)) {
+        landed0 += 1 - s;
+        landed1 += s;
+      } else {
+        gave_up = true;
+        atomicOr(error_flag, 3);
+      }
+    }
+    const T *sdy = reinterpret_cast<const T *>(nhwc_smem + s * TG::STAGE_BYTES);
+    const T *sx = reinterpret_cast<const T *>(nhwc_smem + s * TG::STAGE_BYTES + TG::X_SLOT);
+    T xs[G::R];
+#pragma unroll
+    for (int o = 0; o < G::R; ++o) xs[o] = sx[(o * G::TW + col) * NHWC_CB + lane];
+    float dxa[G::R];
+#pragma unroll
+    for (int o = 0; o < G::R; ++o) dxa[o] = 0.f;
+#pragma unroll
+    for (int r = 0; r < G::IH; ++r) {
+      T v[K];
+#pragma unroll
+      for (int kx = 0; kx < K; ++kx) v[kx] = sdy[(r * G::IW + col + kx) * NHWC_CB + lane];
+#pragma unroll
+      for (int o = 0; o < G::R; ++o) {
+        const int ky = r - o;
+        if (ky >= 0 && ky < K) {
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) {
+            dxa[o] = fma_mix(v[kx], tapf[ky][kx], dxa[o]);
+            acc[ky][kx] = fma_mix(xs[o], v[kx], acc[ky][kx]);
+          }
+        }
+      }
+    }
+    const int y0 = ty * G::R, ox = tx * G::TW + col;
+    if (ox < p.W && c < p.C) {
+      T *op = dx + (((size_t)n * p.H + y0) * p.W + ox) * p.C + c;
+      const size_t row_stride = (size_t)p.W * p.C;
+      const int rows = p.H - y0;
+#pragma unroll
+      for (int o = 0; o < G::R; ++o) {
+        if (o < rows) *op = Elem<T>::from_acc(dxa[o]);
+        op += row_stride;
+      }
+    }
+    if (++tx == p.tiles_x) {
+      tx = 0;
+      if (++ty == p.tiles_y) { ty = 0; ++n; }
+    }
+    __syncthreads();  // every thread has read stage s: it may be refilled
+    if (threadIdx.x == 0 && !gave_up && asked < steps) ask(s);
+  }
+  if (threadIdx.x == 0 && gave_up) {
+    const int asked0 = (asked + 1) / 2, asked1 = asked / 2;
+    while (landed0 < asked0 && mbar_wait_bounded(&full[0], landed0 & 1)) ++landed0;
+    while (landed1 < asked1 && mbar_wait_bounded(&full[1], landed1 & 1)) ++landed1;
+  }
+  // stage 0 now holds, per tap row, [column][kx][channel]; the columns are added in order, and
+  // dW'[ky][kx] is the gradient of tap (K-1-ky, K-1-kx)
+  float *red = reinterpret_cast<float *>(nhwc_smem);
+#pragma unroll
+  for (int ky = 0; ky < K; ++ky) {
+    __syncthreads();
+#pragma unroll
+    for (int kx = 0; kx < K; ++kx) red[(col * K + kx) * NHWC_CB + lane] = acc[ky][kx];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < K * NHWC_CB; idx += G::THREADS) {
+      const int kx = idx / NHWC_CB, ln = idx - kx * NHWC_CB;
+      float sum = 0.f;
+#pragma unroll
+      for (int q = 0; q < G::TW; ++q) sum += red[(q * K + kx) * NHWC_CB + ln];
+      if (c0 + ln < p.C)
+        partial[((size_t)(c0 + ln) * p.SL + slice) * KK + (K - 1 - ky) * K + (K - 1 - kx)] = sum;
+    }
+  }
+}
+
 }  // namespace dwb

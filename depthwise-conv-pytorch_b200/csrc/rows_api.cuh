@@ -54,6 +54,11 @@ int nhwc_backward_input(const T *dy, const T *w, T *dx, const Shape &s, cudaStre
 template <typename T>
 int nhwc_backward_filter(const T *x, const T *dy, typename Elem<T>::acc_t *partial, const Shape &s,
                          cudaStream_t st, int *slices_out);
+// Both gradients from one pass over dy where the channels-last tensor-copy kernels can (stride 1,
+// 3x3 / 5x5); ROWS_DECLINED otherwise.
+template <typename T>
+int nhwc_backward(const T *x, const T *dy, const T *w, T *dx, typename Elem<T>::acc_t *partial,
+                  const Shape &s, cudaStream_t st, int *slices_out);
 
 // Reads and clears the flags kernels raise when a bounded wait expires (synchronises the
 // device).  Bit 0: forward/backward-input kernels, bit 1: backward-filter kernels.

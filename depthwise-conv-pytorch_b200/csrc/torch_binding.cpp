@@ -164,7 +164,12 @@ std::tuple<c10::optional<at::Tensor>, c10::optional<at::Tensor>> backward(
     dx = at::empty_like(input, nhwc ? at::MemoryFormat::ChannelsLast : at::MemoryFormat::Contiguous);
   c10::cuda::CUDAGuard guard(input.device());
   void *stream = stream_of(input);
-  if (nhwc) {
+  if (nhwc && want_dx && want_dw) {
+    check_status(dwconv_b200_backward_nhwc(input.data_ptr(), grad_output.data_ptr(), kernel.data_ptr(),
+                                           dx->data_ptr(), dw->data_ptr(), ws.data_ptr(), nbytes, code, &s,
+                                           stream),
+                 "backward_nhwc");
+  } else if (nhwc) {
     if (want_dx)
       check_status(dwconv_b200_backward_input_nhwc(grad_output.data_ptr(), kernel.data_ptr(),
                                                    dx->data_ptr(), code, &s, stream),

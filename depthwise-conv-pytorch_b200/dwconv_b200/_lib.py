@@ -52,6 +52,7 @@ def _load():
         "dwconv_b200_forward_nhwc": (ci, [vp, vp, vp, ci, sp, ctypes.POINTER(Epilogue), vp]),
         "dwconv_b200_backward_input_nhwc": (ci, [vp, vp, vp, ci, sp, vp]),
         "dwconv_b200_backward_filter_nhwc": (ci, [vp, vp, vp, vp, sz, ci, sp, vp]),
+        "dwconv_b200_backward_nhwc": (ci, [vp, vp, vp, vp, vp, vp, sz, ci, sp, vp]),
         "dwconv_b200_backward_filter_workspace_bytes": (sz, [ci, sp]),
         "dwconv_b200_backward_filter": (ci, [vp, vp, vp, vp, sz, ci, sp, vp]),
         "dwconv_b200_backward": (ci, [vp, vp, vp, vp, vp, vp, sz, ci, sp, vp]),
@@ -129,6 +130,7 @@ EXPORTS = (
     "dwconv_b200_forward", "dwconv_b200_forward_epilogue", "dwconv_b200_backward_input",
     "dwconv_b200_backward_filter_workspace_bytes", "dwconv_b200_backward_filter",
     "dwconv_b200_forward_nhwc", "dwconv_b200_backward_input_nhwc", "dwconv_b200_backward_filter_nhwc",
+    "dwconv_b200_backward_nhwc",
     "dwconv_b200_backward", "dwconv_b200_backward_accumulate", "dwconv_b200_backward_exchange",
     "dwconv_b200_backward_filter_allreduce", "dwconv_b200_backward_allreduce",
     "dwconv_b200_use_dwconv2d_small", "dwconv_b200_dwconv2d", "dwconv_b200_dwconv2d_small",

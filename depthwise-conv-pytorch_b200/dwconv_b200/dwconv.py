@@ -176,6 +176,18 @@ class DepthwiseConv2dFunction(Function):
         grad_input = grad_kernel = None
         with _C._on_device(input):
             stream = _C._stream(input)
+            if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
+                nbytes = _workspace_bytes(code, shape)
+                ws = torch.empty(nbytes, dtype=torch.uint8, device=input.device)
+                grad_input = torch.empty_like(input, memory_format=torch.channels_last)
+                grad_kernel = torch.empty_like(kernel)
+                st = _lib.lib.dwconv_b200_backward_nhwc(
+                    input.data_ptr(), grad_output.data_ptr(), kernel.data_ptr(), grad_input.data_ptr(),
+                    grad_kernel.data_ptr(), ws.data_ptr(), nbytes, code, shape, stream)
+                _lib.check(st, "backward_nhwc")
+                if _lib.CHECK_STATUS:
+                    _lib.check_device_status("backward")
+                return grad_input, grad_kernel, None, None, None
             if ctx.needs_input_grad[0]:
                 grad_input = torch.empty_like(input, memory_format=torch.channels_last)
                 st = _lib.lib.dwconv_b200_backward_input_nhwc(

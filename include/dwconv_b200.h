@@ -198,6 +198,14 @@ DWCONV_B200_API int dwconv_b200_backward_input_nhwc(const void *dy, const void *
 DWCONV_B200_API int dwconv_b200_backward_filter_nhwc(const void *x, const void *dy, void *dw,
                                                      void *workspace, size_t workspace_bytes, int dtype,
                                                      const dwconv_b200_shape *shape, void *stream);
+/* Both gradients of channels-last maps in one call (what the reference's backward computes,
+ * torch_dwconv/dwconv.py:56-68, for NHWC tensors): dx as dwconv_b200_backward_input_nhwc (bit for
+ * bit), dw as dwconv_b200_backward_filter_nhwc to rounding.  At stride 1 with a 3x3 or 5x5 filter
+ * both come from ONE pass over dy; other geometries run the two operators.  Workspace as for
+ * dwconv_b200_backward_filter. */
+DWCONV_B200_API int dwconv_b200_backward_nhwc(const void *x, const void *dy, const void *w, void *dx,
+                                              void *dw, void *workspace, size_t workspace_bytes,
+                                              int dtype, const dwconv_b200_shape *shape, void *stream);
 
 /* Both gradients from ONE pass over dy: dx as dwconv_b200_backward_input (bit for bit),
  * dw as dwconv_b200_backward_filter (same two-pass reduction; the partial sums are

@@ -51,6 +51,18 @@ def test_channels_last_through_the_c_abi(cfg, dtn):
     assert torch.equal(y.cpu(), oracle.forward_seq(x, w, s, p))
     assert torch.equal(dx.cpu(), oracle.backward_input_seq(dy, w, (H, W), s, p))
     assert_dw_close(dw, oracle.backward_filter(x, dy, (k, k), s, p), dt, "NHWC dW")
+    # both gradients in one call (one pass over dy at stride 1 with 3x3 / 5x5 filters, the two
+    # operators otherwise): dx the same bits, dW the same sums in another order
+    dx2 = torch.full_like(xl, float("nan"))
+    dw2 = torch.full_like(w, float("nan"))
+    ws.fill_(0xA5)
+    assert L.dwconv_b200_backward_nhwc(xl.data_ptr(), dyl.data_ptr(), w.data_ptr(), dx2.data_ptr(),
+                                       dw2.data_ptr(), ws.data_ptr(), nbytes, CODE[dt], sh, st0) == 0
+    torch.cuda.synchronize()
+    assert bool((ws[nbytes:] == 0xA5).all()), "wrote past the workspace"
+    assert torch.equal(dx2, dx), "fused dx differs from backward-input's"
+    assert not torch.isnan(dw2).any()
+    assert_dw_close(dw2, oracle.backward_filter(x, dy, (k, k), s, p), dt, "NHWC fused dW")
     assert L.dwconv_b200_device_status() == 0, "a bounded wait expired in a kernel"
 
 
